@@ -1,0 +1,454 @@
+// C ABI of the sampler (include/hs_sampler.h): handle management, launch planning and
+// the host-buffer convenience call.  No torch types, no exceptions across the boundary.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/hs_sampler.h"
+#include "hs_common.cuh"
+#include "hs_row_kernel.cuh"
+#include "hs_state.cuh"
+
+namespace {
+
+using hs::u64;
+
+constexpr int kGreedyMaxChunks = 64;
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+    if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+struct Plan {
+  int cluster;
+  int slice;
+  size_t smem;
+  bool global_stage;
+};
+
+inline size_t align16(size_t v) { return (v + 15) & ~size_t(15); }
+
+size_t fixed_smem(int cluster) {
+  size_t off = align16(sizeof(hs::Exchange));
+  off += sizeof(hs::Hist);
+  off += (sizeof(u64) + sizeof(uint32_t)) * (hs::kBins / cluster);
+  return align16(off);
+}
+
+}  // namespace
+
+struct hs_sampler {
+  int device = 0;
+  int vocab_max = 0, slots_user = 0, slots_total = 0, unique_cap = 0, batch_max = 0;
+  int sm_count = 0;
+  int smem_optin = 0;
+  int force_cluster = 0;
+  hs::Pool pool{};
+  u64* greedy_partials = nullptr;
+  float* gstage = nullptr;  // global stand-in for the on-chip row copy (very wide rows only)
+  size_t gstage_elems = 0;
+  // device + pinned staging for the host-buffer call
+  void* d_logits = nullptr;
+  size_t d_logits_bytes = 0;
+  hs_row_params* d_params = nullptr;
+  hs_row_out* d_out = nullptr;
+  int32_t* d_hist = nullptr;
+  size_t d_hist_elems = 0;
+  int32_t* d_offsets = nullptr;
+  int32_t* d_slots = nullptr;
+  hs_row_params* h_params = nullptr;  // pinned
+  int32_t* h_small = nullptr;         // pinned: offsets[batch_max+1] then slots[batch_max]
+  std::mutex mu;
+  std::string err;
+  unsigned long long launches = 0;
+};
+
+namespace {
+
+int fail(hs_sampler* h, int code, const char* what, cudaError_t e = cudaSuccess) {
+  if (h) {
+    char buf[512];
+    if (e != cudaSuccess)
+      std::snprintf(buf, sizeof buf, "%s: %s", what, cudaGetErrorString(e));
+    else
+      std::snprintf(buf, sizeof buf, "%s", what);
+    h->err = buf;
+  }
+  return code;
+}
+
+#define HS_CUDA(h, call)                                              \
+  do {                                                                \
+    cudaError_t e_ = (call);                                          \
+    if (e_ != cudaSuccess) return fail((h), HS_ERR_CUDA, #call, e_);  \
+  } while (0)
+
+bool make_plan(const hs_sampler* h, int vocab, Plan& p) {
+  static const int sizes[4] = {1, 2, 4, 8};
+  for (int k = 0; k < 4; ++k) {
+    const int c = sizes[k];
+    if (h->force_cluster && c != h->force_cluster) continue;
+    const int slice = ((vocab + c - 1) / c + 7) & ~7;
+    const size_t smem = fixed_smem(c) + (size_t)slice * sizeof(float);
+    if (smem <= (size_t)h->smem_optin && slice <= hs::kMaxSliceElems) {
+      p = Plan{c, slice, smem, false};
+      return true;
+    }
+  }
+  const int c = hs::kMaxCluster;
+  const int slice = ((vocab + c - 1) / c + 7) & ~7;
+  if (slice > hs::kMaxSliceElems) return false;
+  p = Plan{c, slice, fixed_smem(c), true};
+  return true;
+}
+
+int check_common(hs_sampler* h, const void* logits, int dtype, int batch, int vocab) {
+  if (!h) return HS_ERR_INVALID;
+  if (!logits && batch > 0) return fail(h, HS_ERR_INVALID, "logits is null");
+  if (dtype != HS_DTYPE_F32 && dtype != HS_DTYPE_BF16) return fail(h, HS_ERR_INVALID, "unknown dtype");
+  if (batch < 0 || vocab < 1) return fail(h, HS_ERR_INVALID, "batch must be >= 0 and vocab >= 1");
+  if (vocab > h->vocab_max) return fail(h, HS_ERR_CAPACITY, "vocab exceeds vocab_max given to hs_create");
+  if (batch > h->batch_max) return fail(h, HS_ERR_CAPACITY, "batch exceeds batch_max given to hs_create");
+  return HS_OK;
+}
+
+int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch, int vocab,
+                const hs_row_params* params, hs_row_out* out, const float* noise, float* scores_out,
+                uint32_t flags, cudaStream_t stream) {
+  Plan plan;
+  if (!make_plan(h, vocab, plan)) return fail(h, HS_ERR_CAPACITY, "vocabulary too wide for the row kernel");
+  if (plan.global_stage) {
+    const size_t need = (size_t)batch * plan.slice * plan.cluster;
+    if (need > h->gstage_elems) return fail(h, HS_ERR_CAPACITY, "global stage too small for this batch x vocab");
+  }
+  hs::RowKernelArgs a{};
+  a.logits = logits;
+  a.dtype = dtype;
+  a.row_stride = row_stride;
+  a.vocab = vocab;
+  a.slice = plan.slice;
+  a.params = params;
+  a.out = out;
+  a.noise = noise;
+  a.scores_out = scores_out;
+  a.gstage = plan.global_stage ? h->gstage : nullptr;
+  a.pool_ids = h->pool.ids;
+  a.pool_cnts = h->pool.cnts;
+  a.pool_n = h->pool.n;
+  a.pool_pos = h->pool.pos;
+  a.unique_cap = h->pool.unique_cap;
+  a.pos_stride = h->pool.pos_stride;
+  a.flags = flags;
+
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)plan.cluster, (unsigned)batch, 1);
+  cfg.blockDim = dim3(hs::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = plan.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)plan.cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  HS_CUDA(h, cudaLaunchKernelEx(&cfg, hs::row_kernel, a));
+  h->launches += 1;
+  return HS_OK;
+}
+
+int launch_greedy(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch, int vocab,
+                  int32_t* tokens_out, cudaStream_t stream) {
+  int chunks = (2 * h->sm_count + batch - 1) / batch;
+  chunks = std::max(1, std::min(chunks, kGreedyMaxChunks));
+  int chunk = ((vocab + chunks - 1) / chunks + 7) & ~7;
+  chunks = (vocab + chunk - 1) / chunk;
+  hs::greedy_partial_kernel<<<dim3((unsigned)chunks, (unsigned)batch), hs::kGreedyThreads, 0, stream>>>(
+      logits, dtype, row_stride, vocab, chunk, h->greedy_partials);
+  HS_CUDA(h, cudaGetLastError());
+  hs::greedy_final_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(h->greedy_partials, chunks, batch, tokens_out);
+  HS_CUDA(h, cudaGetLastError());
+  h->launches += 2;
+  return HS_OK;
+}
+
+int launch_append(hs_sampler* h, const int32_t* tokens, const int32_t* offsets, const int32_t* slots,
+                  int n_slots, int vocab, int max_tokens, cudaStream_t stream) {
+  if (n_slots == 0 || max_tokens <= 0) return HS_OK;
+  const int threads = 256;
+  int bx = std::max(1, std::min((max_tokens + threads - 1) / threads, 64));
+  dim3 grid((unsigned)bx, (unsigned)n_slots);
+  hs::slots_register_kernel<<<grid, threads, 0, stream>>>(h->pool, tokens, offsets, slots, n_slots, vocab);
+  HS_CUDA(h, cudaGetLastError());
+  hs::slots_count_kernel<<<grid, threads, 0, stream>>>(h->pool, tokens, offsets, slots, n_slots, vocab);
+  HS_CUDA(h, cudaGetLastError());
+  h->launches += 2;
+  return HS_OK;
+}
+
+void release(hs_sampler* h) {
+  cudaFree(h->pool.ids); cudaFree(h->pool.cnts); cudaFree(h->pool.n); cudaFree(h->pool.pos);
+  cudaFree(h->pool.error); cudaFree(h->greedy_partials); cudaFree(h->gstage); cudaFree(h->d_logits);
+  cudaFree(h->d_params); cudaFree(h->d_out); cudaFree(h->d_hist); cudaFree(h->d_offsets); cudaFree(h->d_slots);
+  if (h->h_params) cudaFreeHost(h->h_params);
+  if (h->h_small) cudaFreeHost(h->h_small);
+}
+
+}  // namespace
+
+extern "C" {
+
+int hs_abi_version(void) { return 1; }
+
+const char* hs_status_string(int status) {
+  switch (status) {
+    case HS_OK: return "ok";
+    case HS_ERR_INVALID: return "invalid argument";
+    case HS_ERR_CAPACITY: return "capacity exceeded";
+    case HS_ERR_CUDA: return "CUDA error";
+    case HS_ERR_UNSUPPORTED: return "unsupported";
+    default: return "unknown status";
+  }
+}
+
+const char* hs_last_error(hs_sampler* h) { return h ? h->err.c_str() : "null sampler"; }
+
+int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batch_max, hs_sampler** out) {
+  if (!out) return HS_ERR_INVALID;
+  *out = nullptr;
+  if (vocab_max < 1 || slots_max < 0 || batch_max < 1 || unique_cap < 0) return HS_ERR_INVALID;
+  if (batch_max > 65535) return HS_ERR_CAPACITY;
+  hs_sampler* h = new (std::nothrow) hs_sampler();
+  if (!h) return HS_ERR_INVALID;
+  DeviceGuard guard(device);
+  if (!guard.ok) { delete h; return HS_ERR_CUDA; }
+  h->device = device;
+  h->vocab_max = vocab_max;
+  h->slots_user = slots_max;
+  h->slots_total = slots_max + batch_max;  // the tail serves per-call (stateless) histories
+  h->unique_cap = unique_cap == 0 ? vocab_max : std::min(unique_cap, vocab_max);
+  h->batch_max = batch_max;
+  if (const char* fc = std::getenv("HS_FORCE_CLUSTER")) {
+    const int v = std::atoi(fc);
+    if (v == 1 || v == 2 || v == 4 || v == 8) h->force_cluster = v;
+  }
+  auto bail = [&](int code) { release(h); delete h; return code; };
+  if (cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return bail(HS_ERR_CUDA);
+  if (cudaDeviceGetAttribute(&h->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess) return bail(HS_ERR_CUDA);
+  if (cudaFuncSetAttribute(hs::row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_optin) != cudaSuccess) return bail(HS_ERR_CUDA);
+
+  const size_t st = (size_t)h->slots_total;
+  h->pool.slots_total = h->slots_total;
+  h->pool.unique_cap = h->unique_cap;
+  h->pool.pos_stride = vocab_max;
+  bool ok = true;
+  ok = ok && cudaMalloc(&h->pool.ids, st * h->unique_cap * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->pool.cnts, st * h->unique_cap * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->pool.n, st * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->pool.pos, st * (size_t)vocab_max * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->pool.error, sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->greedy_partials, (size_t)batch_max * kGreedyMaxChunks * sizeof(u64)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->d_params, (size_t)batch_max * sizeof(hs_row_params)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->d_out, (size_t)batch_max * sizeof(hs_row_out)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->d_offsets, ((size_t)batch_max + 1) * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->d_slots, (size_t)batch_max * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMallocHost(&h->h_params, (size_t)batch_max * sizeof(hs_row_params)) == cudaSuccess;
+  ok = ok && cudaMallocHost(&h->h_small, (2 * (size_t)batch_max + 1) * sizeof(int32_t)) == cudaSuccess;
+  if (!ok) return bail(HS_ERR_CUDA);
+  ok = ok && cudaMemset(h->pool.n, 0, st * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMemset(h->pool.pos, 0, st * (size_t)vocab_max * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMemset(h->pool.error, 0, sizeof(int32_t)) == cudaSuccess;
+  if (!ok) return bail(HS_ERR_CUDA);
+  Plan plan;
+  if (!make_plan(h, vocab_max, plan)) return bail(HS_ERR_CAPACITY);
+  if (plan.global_stage) {
+    h->gstage_elems = (size_t)batch_max * plan.slice * plan.cluster;
+    if (cudaMalloc(&h->gstage, h->gstage_elems * sizeof(float)) != cudaSuccess) return bail(HS_ERR_CUDA);
+  }
+  if (cudaDeviceSynchronize() != cudaSuccess) return bail(HS_ERR_CUDA);
+  *out = h;
+  return HS_OK;
+}
+
+int hs_destroy(hs_sampler* h) {
+  if (!h) return HS_ERR_INVALID;
+  {
+    DeviceGuard guard(h->device);
+    cudaDeviceSynchronize();
+    release(h);
+  }
+  delete h;
+  return HS_OK;
+}
+
+int hs_slots_reset(hs_sampler* h, const int32_t* slots, int n_slots, void* stream) {
+  if (!h || n_slots < 0 || (!slots && n_slots)) return HS_ERR_INVALID;
+  if (n_slots == 0) return HS_OK;
+  DeviceGuard guard(h->device);
+  hs::slots_reset_kernel<<<n_slots, 256, 0, (cudaStream_t)stream>>>(h->pool, slots, n_slots);
+  HS_CUDA(h, cudaGetLastError());
+  h->launches += 1;
+  return HS_OK;
+}
+
+int hs_slots_append(hs_sampler* h, const int32_t* tokens, const int32_t* offsets, const int32_t* slots,
+                    int n_slots, int vocab, int max_tokens_per_slot, void* stream) {
+  if (!h || n_slots < 0 || (n_slots && (!offsets || !slots))) return HS_ERR_INVALID;
+  if (vocab < 1 || vocab > h->vocab_max) return fail(h, HS_ERR_CAPACITY, "vocab exceeds vocab_max");
+  if (n_slots > 65535) return fail(h, HS_ERR_CAPACITY, "too many slots in one call");
+  DeviceGuard guard(h->device);
+  return launch_append(h, tokens, offsets, slots, n_slots, vocab, max_tokens_per_slot, (cudaStream_t)stream);
+}
+
+int hs_slot_unique_count(hs_sampler* h, int slot, void* stream, int* out) {
+  if (!h || !out || slot < 0 || slot >= h->slots_total) return HS_ERR_INVALID;
+  DeviceGuard guard(h->device);
+  int32_t v = 0;
+  HS_CUDA(h, cudaMemcpyAsync(&v, h->pool.n + slot, sizeof v, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  HS_CUDA(h, cudaStreamSynchronize((cudaStream_t)stream));
+  *out = v;
+  return HS_OK;
+}
+
+int hs_sample(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch, int vocab,
+              const hs_row_params* params, hs_row_out* out, const float* noise, float* scores_out,
+              uint32_t flags, void* stream) {
+  int rc = check_common(h, logits, dtype, batch, vocab);
+  if (rc != HS_OK) return rc;
+  if (batch == 0) return HS_OK;
+  if (!params || !out) return fail(h, HS_ERR_INVALID, "params / out is null");
+  if (row_stride < vocab) return fail(h, HS_ERR_INVALID, "row_stride smaller than vocab");
+  DeviceGuard guard(h->device);
+  return launch_rows(h, logits, dtype, row_stride, batch, vocab, params, out, noise, scores_out, flags,
+                     (cudaStream_t)stream);
+}
+
+int hs_greedy(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch, int vocab,
+              int32_t* tokens_out, void* stream) {
+  int rc = check_common(h, logits, dtype, batch, vocab);
+  if (rc != HS_OK) return rc;
+  if (batch == 0) return HS_OK;
+  if (!tokens_out) return fail(h, HS_ERR_INVALID, "tokens_out is null");
+  if (row_stride < vocab) return fail(h, HS_ERR_INVALID, "row_stride smaller than vocab");
+  DeviceGuard guard(h->device);
+  return launch_greedy(h, logits, dtype, row_stride, batch, vocab, tokens_out, (cudaStream_t)stream);
+}
+
+int hs_sample_host(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch, int vocab,
+                   hs_row_params* params, hs_row_out* out, const int32_t* hist_tokens,
+                   const int32_t* hist_offsets, uint32_t flags, void* stream_) {
+  int rc = check_common(h, logits, dtype, batch, vocab);
+  if (rc != HS_OK) return rc;
+  if (batch == 0) return HS_OK;
+  if (!params || !out) return fail(h, HS_ERR_INVALID, "params / out is null");
+  if (row_stride < vocab) return fail(h, HS_ERR_INVALID, "row_stride smaller than vocab");
+  cudaStream_t stream = (cudaStream_t)stream_;
+  std::lock_guard<std::mutex> lock(h->mu);  // one user of the staging buffers at a time
+  DeviceGuard guard(h->device);
+
+  const size_t esz = dtype == HS_DTYPE_BF16 ? 2 : 4;
+  const size_t need = (size_t)batch * vocab * esz;
+  if (need > h->d_logits_bytes) {
+    HS_CUDA(h, cudaStreamSynchronize(stream));
+    cudaFree(h->d_logits);
+    h->d_logits = nullptr;
+    h->d_logits_bytes = 0;
+    HS_CUDA(h, cudaMalloc(&h->d_logits, need));
+    h->d_logits_bytes = need;
+  }
+  HS_CUDA(h, cudaMemcpy2DAsync(h->d_logits, (size_t)vocab * esz, logits, (size_t)row_stride * esz,
+                               (size_t)vocab * esz, (size_t)batch, cudaMemcpyHostToDevice, stream));
+
+  // Rows marked slot == -2 are penalised with the history passed in this call: it is
+  // counted into a per-row scratch slot on the device (the reference's stateless form).
+  int32_t* h_offsets = h->h_small;
+  int32_t* h_slots = h->h_small + (h->batch_max + 1);
+  int n_temp = 0;
+  int max_len = 0;
+  long long total = 0;
+  for (int r = 0; r < batch; ++r) {
+    h->h_params[r] = params[r];
+    if (params[r].slot == -2) {
+      if (!hist_tokens || !hist_offsets) return fail(h, HS_ERR_INVALID, "slot -2 needs hist_tokens / hist_offsets");
+      const int len = hist_offsets[r + 1] - hist_offsets[r];
+      if (len < 0) return fail(h, HS_ERR_INVALID, "hist_offsets must not decrease");
+      h_slots[n_temp] = h->slots_user + r;
+      h->h_params[r].slot = h->slots_user + r;
+      ++n_temp;
+      max_len = std::max(max_len, len);
+      total += len;
+    } else if (params[r].slot >= h->slots_user || params[r].slot < -2) {
+      return fail(h, HS_ERR_INVALID, "params.slot out of range");
+    }
+  }
+  if (n_temp) {
+    if ((size_t)total > h->d_hist_elems) {
+      HS_CUDA(h, cudaStreamSynchronize(stream));
+      cudaFree(h->d_hist);
+      h->d_hist = nullptr;
+      h->d_hist_elems = 0;
+      HS_CUDA(h, cudaMalloc(&h->d_hist, (size_t)total * sizeof(int32_t)));
+      h->d_hist_elems = (size_t)total;
+    }
+    // The append kernels index offsets by position in `slots`, so the participants'
+    // tokens are packed back to back.
+    long long cursor = 0;
+    std::vector<int32_t> packed;
+    packed.reserve((size_t)total);
+    int idx = 0;
+    for (int r = 0; r < batch; ++r) {
+      if (params[r].slot != -2) continue;
+      h_offsets[idx++] = (int32_t)cursor;
+      const int b = hist_offsets[r], e = hist_offsets[r + 1];
+      packed.insert(packed.end(), hist_tokens + b, hist_tokens + e);
+      cursor += e - b;
+    }
+    h_offsets[idx] = (int32_t)cursor;
+    if (cursor) HS_CUDA(h, cudaMemcpyAsync(h->d_hist, packed.data(), (size_t)cursor * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+    HS_CUDA(h, cudaMemcpyAsync(h->d_offsets, h_offsets, ((size_t)n_temp + 1) * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+    HS_CUDA(h, cudaMemcpyAsync(h->d_slots, h_slots, (size_t)n_temp * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+    if (cursor) HS_CUDA(h, cudaStreamSynchronize(stream));  // `packed` is pageable and about to go away
+    hs::slots_reset_kernel<<<n_temp, 256, 0, stream>>>(h->pool, h->d_slots, n_temp);
+    HS_CUDA(h, cudaGetLastError());
+    h->launches += 1;
+    rc = launch_append(h, h->d_hist, h->d_offsets, h->d_slots, n_temp, vocab, max_len, stream);
+    if (rc != HS_OK) return rc;
+  }
+  HS_CUDA(h, cudaMemcpyAsync(h->d_params, h->h_params, (size_t)batch * sizeof(hs_row_params), cudaMemcpyHostToDevice, stream));
+  rc = launch_rows(h, h->d_logits, dtype, vocab, batch, vocab, h->d_params, h->d_out, nullptr, nullptr, flags, stream);
+  if (rc != HS_OK) return rc;
+  HS_CUDA(h, cudaMemcpyAsync(out, h->d_out, (size_t)batch * sizeof(hs_row_out), cudaMemcpyDeviceToHost, stream));
+  HS_CUDA(h, cudaStreamSynchronize(stream));
+  return HS_OK;
+}
+
+int hs_query(hs_sampler* h, int what, int vocab, int dtype) {
+  (void)dtype;
+  if (!h) return HS_ERR_INVALID;
+  Plan plan;
+  switch (what) {
+    case 0: return make_plan(h, vocab, plan) ? plan.cluster : HS_ERR_CAPACITY;
+    case 1: return make_plan(h, vocab, plan) ? (plan.global_stage ? 0 : 1) : HS_ERR_CAPACITY;
+    case 2: return h->sm_count;
+    case 3: return (int)(h->launches & 0x7fffffffull);
+    default: return HS_ERR_INVALID;
+  }
+}
+
+}  // extern "C"

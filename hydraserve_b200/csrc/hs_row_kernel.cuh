@@ -1,0 +1,711 @@
+// The fused per-row sampling kernel (general path).
+//
+// One thread-block cluster owns one logits row.  The row is read from HBM once with
+// 128-bit loads, widened to fp32 and kept on chip, a slice per CTA, for the rest of the
+// kernel (a global scratch slice stands in when the row is too wide for the cluster's
+// shared memory).  Everything after the load works on that resident copy:
+//
+//   penalties    scatter from the row's sparse (token id, count) list into the slices
+//                (distributed shared memory), three separately rounded fp32 steps
+//   temperature  true fp32 division, written back; row max / argmax in the same pass
+//   top-k        radix descent over order-preserving keys by COUNT (ties at the k-th kept)
+//   min-p        threshold test in probability space, relative to the top-k soft-max
+//   top-p        radix descent by probability MASS (bucketed prefix sums), ties at the cut
+//                resolved towards the lowest token ids
+//   draw         Philox4x32-10 inverse CDF over exact integer masses, or the supplied
+//                Exp(1) variates (arg max of p / q)
+//   logprobs     log soft-max over the kept set, top-N by another count descent
+//
+// Probability mass is an integer multiple of 2^-40 (hs::mass_of), so every sum is exact
+// and independent of accumulation order: the same row always yields the same cut.
+#pragma once
+
+#include "hs_common.cuh"
+#include "../../include/hs_sampler.h"
+
+namespace hs {
+
+struct RowKernelArgs {
+  const void* logits;
+  int dtype;
+  long long row_stride;
+  int vocab;
+  int slice;            // elements per CTA slice (multiple of 8)
+  const hs_row_params* params;
+  hs_row_out* out;
+  const float* noise;   // [batch, vocab] or null
+  float* scores_out;    // [batch, vocab] or null
+  float* gstage;        // [batch, slice * cluster] global stage, or null = shared memory
+  // token-count histogram pool
+  int32_t* pool_ids;
+  int32_t* pool_cnts;
+  int32_t* pool_n;
+  int32_t* pool_pos;
+  int unique_cap;
+  long long pos_stride;
+  uint32_t flags;
+};
+
+struct Hist {
+  uint32_t cnt[kBins];  // after the merge: full_cnt
+  uint32_t l0[kBins];   // after the merge: full_mass (u64) spans l0 and l1
+  uint32_t l1[kBins];
+  uint32_t l2[kBins];
+};
+
+struct Selection {
+  uint32_t key;
+  u64 above_cnt, above_mass;  // over elements with key > this key
+  u64 bin_cnt, bin_mass;      // over elements with key == this key
+  u64 total_cnt, total_mass;  // over all elements with key >= lo
+  u64 target;                 // the count / mass that was searched for
+  bool ok;
+};
+
+struct RowCtx {
+  cg::cluster_group cluster;
+  unsigned rank, nranks;
+  int row;
+  int vocab;
+  int slice;
+  int base;      // global index of the first element of this CTA's slice
+  int n_local;   // elements in this CTA's slice
+  int seg;       // elements per warp in the id-ordered walks (multiple of 32)
+  float* stage;  // this CTA's slice
+  float* smem_stage;
+  float* gstage_row;
+  Hist* hist;
+  uint32_t* red_cnt;
+  u64* red_mass;
+  Exchange* x;
+
+  __device__ __forceinline__ void sync_all() {
+    if (nranks > 1) cluster.sync(); else __syncthreads();
+  }
+  __device__ __forceinline__ float* slice_of(unsigned r) {
+    if (gstage_row) return gstage_row + (size_t)r * slice;
+    return nranks > 1 ? cluster.map_shared_rank(smem_stage, r) : smem_stage;
+  }
+};
+
+// Smallest integer mass A with float(A / total) > top_p, i.e. the cumulative mass at which
+// the reference's `cumulative > top_p` first becomes true (sampling.py:136).
+__device__ __forceinline__ u64 top_p_target(u64 total, float top_p) {
+  const double tot = (double)total;
+  const float up = __uint_as_float(__float_as_uint(top_p) + 1u);
+  const double mid = 0.5 * ((double)top_p + (double)up);
+  double guess = floor(mid * tot) - 2.0;
+  u64 a = guess < 1.0 ? 1ull : (u64)guess;
+  for (int i = 0; i < 8; ++i) {
+    if ((float)((double)a / tot) > top_p) break;
+    ++a;
+  }
+  if (a > total) a = total;
+  if (a < 1) a = 1;
+  return a;
+}
+
+// Radix descent over the resident row: finds the key at which, walking scores downwards
+// from the top, the running count (BY_MASS = false) or probability mass (BY_MASS = true)
+// first reaches the target.  Only elements with key >= lo_key take part.
+template <bool BY_MASS, bool WITH_MASS>
+__device__ Selection descend(RowCtx& c, uint32_t lo_key, u64 target_cnt, float top_p, float m) {
+  static_assert(WITH_MASS || !BY_MASS, "a mass descent needs masses");
+  Hist& h = *c.hist;
+  u64* full_mass = reinterpret_cast<u64*>(h.l0);
+  uint32_t* full_cnt = h.cnt;
+  Selection sel;
+  sel.above_cnt = sel.above_mass = 0;
+  sel.total_cnt = sel.total_mass = 0;
+  sel.target = target_cnt;
+  sel.ok = true;
+  uint32_t prefix = 0;
+  const int per = kBins / (int)c.nranks;
+  const int tid = threadIdx.x;
+
+  for (int level = 0; level < 3; ++level) {
+    const int shift = level == 0 ? 21 : (level == 1 ? 10 : 0);
+    const int bits = level < 2 ? 11 : 10;
+    const uint32_t mask = (1u << bits) - 1u;
+    for (int b = tid; b < kBins; b += kThreads) {
+      h.cnt[b] = 0;
+      if (WITH_MASS) { h.l0[b] = 0; h.l1[b] = 0; h.l2[b] = 0; }
+    }
+    __syncthreads();
+    for (int i = tid; i < c.n_local; i += kThreads) {
+      const float s = c.stage[i];
+      const uint32_t k = key_of(s);
+      if (k < lo_key) continue;
+      if (level > 0 && (k >> (shift + bits)) != prefix) continue;
+      const uint32_t bin = (k >> shift) & mask;
+      atomicAdd(&h.cnt[bin], 1u);
+      if (WITH_MASS) {
+        const u64 q = mass_of(s, m);
+        if (q) {
+          atomicAdd(&h.l0[bin], (uint32_t)q & kLimbMask);
+          atomicAdd(&h.l1[bin], (uint32_t)(q >> kLimbBits) & kLimbMask);
+          atomicAdd(&h.l2[bin], (uint32_t)(q >> (2 * kLimbBits)));
+        }
+      }
+    }
+    c.sync_all();
+    // reduce-scatter: this CTA sums bins [rank*per, (rank+1)*per) over the cluster
+    for (int b = tid; b < per; b += kThreads) {
+      const int gb = (int)c.rank * per + b;
+      uint32_t cn = 0;
+      u64 ms = 0;
+      for (unsigned r = 0; r < c.nranks; ++r) {
+        const Hist* rh = c.nranks > 1 ? c.cluster.map_shared_rank(c.hist, r) : c.hist;
+        cn += rh->cnt[gb];
+        if (WITH_MASS)
+          ms += (u64)rh->l0[gb] + ((u64)rh->l1[gb] << kLimbBits) + ((u64)rh->l2[gb] << (2 * kLimbBits));
+      }
+      c.red_cnt[b] = cn;
+      c.red_mass[b] = ms;
+    }
+    c.sync_all();
+    // all-gather the merged bins into this CTA (over the now unused local arrays)
+    for (int gb = tid; gb < kBins; gb += kThreads) {
+      const unsigned r = (unsigned)(gb / per);
+      const int b = gb - (int)r * per;
+      const uint32_t* rc = c.nranks > 1 ? c.cluster.map_shared_rank(c.red_cnt, r) : c.red_cnt;
+      const u64* rm = c.nranks > 1 ? c.cluster.map_shared_rank(c.red_mass, r) : c.red_mass;
+      full_cnt[gb] = rc[b];
+      full_mass[gb] = WITH_MASS ? rm[b] : 0ull;
+    }
+    if (tid == 0) c.x->bcast[7] = 0;
+    __syncthreads();
+    // scan bins from the top: thread t owns bins hi = kBins-1-2t and hi-1
+    const int hi = kBins - 1 - 2 * tid;
+    const u64 c_hi = full_cnt[hi], c_lo = full_cnt[hi - 1];
+    const u64 m_hi = full_mass[hi], m_lo = full_mass[hi - 1];
+    u64 ia = warp_scan_u64(c_hi + c_lo);
+    u64 ib = warp_scan_u64(m_hi + m_lo);
+    u64 pa, pb, ta, tb;
+    block_warp_prefix2(*c.x, shfl_u64(ia, 31), shfl_u64(ib, 31), pa, pb, ta, tb);
+    const u64 ex_cnt = pa + ia - (c_hi + c_lo);   // exclusive prefix over bins above `hi`
+    const u64 ex_mass = pb + ib - (m_hi + m_lo);
+    if (level == 0) {
+      sel.total_cnt = ta;
+      sel.total_mass = tb;
+      if (BY_MASS) sel.target = top_p_target(tb, top_p);
+    }
+    const u64 want = sel.target - (BY_MASS ? sel.above_mass : sel.above_cnt);
+    const u64 ex = BY_MASS ? ex_mass : ex_cnt;
+    const u64 v_hi = BY_MASS ? m_hi : c_hi;
+    const u64 v_lo = BY_MASS ? m_lo : c_lo;
+    if (ex < want && want <= ex + v_hi + v_lo) {
+      const bool first = want <= ex + v_hi;
+      c.x->bcast[0] = (u64)(first ? hi : hi - 1);
+      c.x->bcast[1] = ex_cnt + (first ? 0 : c_hi);
+      c.x->bcast[2] = ex_mass + (first ? 0 : m_hi);
+      c.x->bcast[3] = first ? c_hi : c_lo;
+      c.x->bcast[4] = first ? m_hi : m_lo;
+      c.x->bcast[7] = 1;
+    }
+    __syncthreads();
+    if (c.x->bcast[7] == 0) {  // nothing reaches the target (non-finite input)
+      sel.ok = false;
+      sel.key = lo_key;
+      sel.bin_cnt = sel.bin_mass = 0;
+      __syncthreads();
+      return sel;
+    }
+    const uint32_t bin = (uint32_t)c.x->bcast[0];
+    sel.above_cnt += c.x->bcast[1];
+    sel.above_mass += c.x->bcast[2];
+    sel.bin_cnt = c.x->bcast[3];
+    sel.bin_mass = c.x->bcast[4];
+    prefix = (prefix << bits) | bin;
+    __syncthreads();  // bcast and the aliased arrays are reused by the next level
+  }
+  sel.key = prefix;
+  return sel;
+}
+
+// Count and mass of all elements with key >= lo_key, cluster wide.
+__device__ void totals_above(RowCtx& c, uint32_t lo_key, float m, bool with_mass, u64& cnt, u64& mass) {
+  u64 a = 0, b = 0;
+  for (int i = threadIdx.x; i < c.n_local; i += kThreads) {
+    const float s = c.stage[i];
+    if (key_of(s) >= lo_key) {
+      ++a;
+      if (with_mass) b += mass_of(s, m);
+    }
+  }
+  block_sum2(*c.x, a, b);
+  u64 vals[2] = {a, b};
+  u64 all[kMaxCluster][2];
+  cluster_allgather<2>(c.cluster, *c.x, vals, all);
+  cnt = mass = 0;
+  for (unsigned r = 0; r < c.nranks; ++r) { cnt += all[r][0]; mass += all[r][1]; }
+}
+
+struct KeptSet {
+  uint32_t cut_key;  // kept: key > cut_key, or key == cut_key and global id <= tie_limit
+  int tie_limit;
+  __device__ __forceinline__ bool has(uint32_t k, int gid) const {
+    return k > cut_key || (k == cut_key && gid <= tie_limit);
+  }
+};
+
+// Global id of the t-th (1-based) element, in ascending id order, whose key equals `key`.
+__device__ int find_tth_equal(RowCtx& c, uint32_t key, u64 t) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int w0 = warp * c.seg;
+  const int w1 = min(w0 + c.seg, c.n_local);
+  u64 mine = 0;
+  for (int i = w0 + lane; i < w1; i += 32) mine += key_of(c.stage[i]) == key;
+  const u64 wtot = warp_sum_u64(mine);
+  u64 pre, pre_unused, tot, tot_unused;
+  block_warp_prefix2(*c.x, wtot, 0, pre, pre_unused, tot, tot_unused);
+  u64 vals[1] = {tot};
+  u64 all[kMaxCluster][1];
+  cluster_allgather<1>(c.cluster, *c.x, vals, all);
+  u64 cta_pre = 0;
+  for (unsigned r = 0; r < c.rank; ++r) cta_pre += all[r][0];
+  if (threadIdx.x == 0) c.x->bcast[6] = 0;
+  __syncthreads();
+  const u64 before = cta_pre + pre;
+  if (before < t && t <= before + wtot) {  // this warp holds the t-th
+    u64 running = before;
+    for (int i0 = w0; i0 < w1; i0 += 32) {
+      const int i = i0 + lane;
+      const bool hit = i < w1 && key_of(c.stage[i]) == key;
+      const uint32_t ballot = __ballot_sync(0xffffffffu, hit);
+      const u64 n = __popc(ballot);
+      if (running + n >= t) {
+        const int nth = (int)(t - running);  // 1-based among set bits
+        const int pos = __fns(ballot, 0, nth);
+        if (lane == 0) c.x->bcast[6] = (u64)(c.base + i0 + pos) + 1;
+        break;
+      }
+      running += n;
+    }
+  }
+  __syncthreads();
+  u64 v2[1] = {c.x->bcast[6]};
+  cluster_allgather<1>(c.cluster, *c.x, v2, all);
+  int result = 0x7fffffff;
+  for (unsigned r = 0; r < c.nranks; ++r)
+    if (all[r][0]) result = (int)(all[r][0] - 1);
+  return result;
+}
+
+// Inverse CDF over the kept set in ascending id order: the first kept element at which
+// the running integer mass exceeds `target` (0 <= target < total kept mass).
+__device__ int draw_inverse_cdf(RowCtx& c, const KeptSet& kept, float m, u64 target) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int w0 = warp * c.seg;
+  const int w1 = min(w0 + c.seg, c.n_local);
+  u64 mine = 0;
+  for (int i = w0 + lane; i < w1; i += 32) {
+    const float s = c.stage[i];
+    if (kept.has(key_of(s), c.base + i)) mine += mass_of(s, m);
+  }
+  const u64 wtot = warp_sum_u64(mine);
+  u64 pre, pre_unused, tot, tot_unused;
+  block_warp_prefix2(*c.x, wtot, 0, pre, pre_unused, tot, tot_unused);
+  u64 vals[1] = {tot};
+  u64 all[kMaxCluster][1];
+  cluster_allgather<1>(c.cluster, *c.x, vals, all);
+  u64 cta_pre = 0;
+  for (unsigned r = 0; r < c.rank; ++r) cta_pre += all[r][0];
+  if (threadIdx.x == 0) c.x->bcast[6] = 0;
+  __syncthreads();
+  const u64 before = cta_pre + pre;
+  if (before <= target && target < before + wtot) {
+    u64 running = before;
+    for (int i0 = w0; i0 < w1; i0 += 32) {
+      const int i = i0 + lane;
+      u64 q = 0;
+      if (i < w1) {
+        const float s = c.stage[i];
+        if (kept.has(key_of(s), c.base + i)) q = mass_of(s, m);
+      }
+      const u64 incl = warp_scan_u64(q);
+      const uint32_t ballot = __ballot_sync(0xffffffffu, running + incl > target);
+      if (ballot) {
+        const int pos = __ffs(ballot) - 1;
+        if (lane == 0) c.x->bcast[6] = (u64)(c.base + i0 + pos) + 1;
+        break;
+      }
+      running += shfl_u64(incl, 31);
+    }
+  }
+  __syncthreads();
+  u64 v2[1] = {c.x->bcast[6]};
+  cluster_allgather<1>(c.cluster, *c.x, v2, all);
+  int result = -1;
+  for (unsigned r = 0; r < c.nranks; ++r)
+    if (all[r][0]) result = (int)(all[r][0] - 1);
+  return result;
+}
+
+// arg max over the kept set of fl(fl(e / z) / noise), lowest id on ties: what
+// torch.multinomial(p, 1) computes on CPU from its Exp(1) variates.
+__device__ int draw_with_noise(RowCtx& c, const KeptSet& kept, float m, float zf,
+                               const float* noise_row) {
+  u64 best = 0;
+  for (int i = threadIdx.x; i < c.n_local; i += kThreads) {
+    const float s = c.stage[i];
+    const int gid = c.base + i;
+    if (!kept.has(key_of(s), gid)) continue;
+    const float p = __fdiv_rn(expf(s - m), zf);
+    const float ratio = __fdiv_rn(p, noise_row[gid]);
+    const u64 packed = ((u64)__float_as_uint(ratio) << 32) | (uint32_t)(~(uint32_t)gid);
+    best = packed > best ? packed : best;
+  }
+  best = block_max_u64(*c.x, best);
+  u64 vals[1] = {best};
+  u64 all[kMaxCluster][1];
+  cluster_allgather<1>(c.cluster, *c.x, vals, all);
+  for (unsigned r = 0; r < c.nranks; ++r) best = all[r][0] > best ? all[r][0] : best;
+  return (int)(~(uint32_t)(best & 0xffffffffu));
+}
+
+// Writes the n_want highest kept scores (ties: lowest ids) as log-probabilities, sorted by
+// (value descending, id ascending), into out->top_ids / out->top_logprobs.
+__device__ void write_top_logprobs(RowCtx& c, const KeptSet& kept, uint32_t key_n, u64 above_n,
+                                   int n_want, float m, float log_z, hs_row_out* out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int w0 = warp * c.seg;
+  const int w1 = min(w0 + c.seg, c.n_local);
+  const u64 need_ties = (u64)n_want - above_n;
+  u64 gt = 0, eq = 0;
+  for (int i = w0 + lane; i < w1; i += 32) {
+    const uint32_t k = key_of(c.stage[i]);
+    gt += k > key_n;
+    eq += (k == key_n) && kept.has(k, c.base + i);
+  }
+  const u64 wgt = warp_sum_u64(gt), weq = warp_sum_u64(eq);
+  u64 pgt, peq, tgt, teq;
+  block_warp_prefix2(*c.x, wgt, weq, pgt, peq, tgt, teq);
+  u64 vals[2] = {tgt, teq};
+  u64 all[kMaxCluster][2];
+  cluster_allgather<2>(c.cluster, *c.x, vals, all);
+  u64 run_gt = pgt, run_eq = peq;
+  for (unsigned r = 0; r < c.rank; ++r) { run_gt += all[r][0]; run_eq += all[r][1]; }
+  for (int i0 = w0; i0 < w1; i0 += 32) {
+    const int i = i0 + lane;
+    bool is_gt = false, is_eq = false;
+    float s = 0.f;
+    if (i < w1) {
+      s = c.stage[i];
+      const uint32_t k = key_of(s);
+      is_gt = k > key_n;
+      is_eq = (k == key_n) && kept.has(k, c.base + i);
+    }
+    const uint32_t bg = __ballot_sync(0xffffffffu, is_gt);
+    const uint32_t be = __ballot_sync(0xffffffffu, is_eq);
+    const uint32_t lt = (1u << lane) - 1u;
+    int slot = -1;
+    if (is_gt) slot = (int)(run_gt + __popc(bg & lt));
+    if (is_eq) {
+      const u64 r = run_eq + __popc(be & lt);
+      if (r < need_ties) slot = (int)(above_n + r);
+    }
+    if (slot >= 0 && slot < HS_MAX_LOGPROBS) {
+      out->top_ids[slot] = c.base + i;
+      out->top_logprobs[slot] = (s - m) - log_z;
+    }
+    run_gt += __popc(bg);
+    run_eq += __popc(be);
+  }
+  __threadfence();
+  c.sync_all();
+  if (c.rank == 0 && warp == 0) {  // n_want <= 20 entries: rank sort inside one warp
+    int id = 0x7fffffff;
+    float v = 0.f;
+    if (lane < n_want) {
+      id = *((volatile int32_t*)&out->top_ids[lane]);
+      v = *((volatile float*)&out->top_logprobs[lane]);
+    }
+    const uint32_t kv = key_of(v);
+    int pos = 0;
+    for (int j = 0; j < n_want; ++j) {
+      const uint32_t kj = __shfl_sync(0xffffffffu, kv, j);
+      const int idj = __shfl_sync(0xffffffffu, id, j);
+      if (kj > kv || (kj == kv && idj < id)) ++pos;
+    }
+    __syncwarp();
+    if (lane < n_want) {
+      out->top_ids[pos] = id;
+      out->top_logprobs[pos] = v;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) row_kernel(const RowKernelArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  RowCtx c{cg::this_cluster()};
+  c.rank = c.cluster.block_rank();
+  c.nranks = c.cluster.num_blocks();
+  c.row = blockIdx.y;
+  c.vocab = a.vocab;
+  c.slice = a.slice;
+  c.base = (int)c.rank * a.slice;
+  c.n_local = max(0, min(a.slice, a.vocab - c.base));
+  c.seg = ((c.n_local + kThreads - 1) / kThreads) * 32;
+
+  size_t off = 0;
+  c.x = reinterpret_cast<Exchange*>(smem_raw + off);
+  off += (sizeof(Exchange) + 15) & ~size_t(15);
+  c.hist = reinterpret_cast<Hist*>(smem_raw + off);
+  off += sizeof(Hist);
+  const int per = kBins / (int)c.nranks;
+  c.red_mass = reinterpret_cast<u64*>(smem_raw + off);
+  off += sizeof(u64) * per;
+  c.red_cnt = reinterpret_cast<uint32_t*>(smem_raw + off);
+  off += sizeof(uint32_t) * per;
+  off = (off + 15) & ~size_t(15);
+  c.smem_stage = reinterpret_cast<float*>(smem_raw + off);
+  c.gstage_row = a.gstage ? a.gstage + (size_t)c.row * ((size_t)a.slice * c.nranks) : nullptr;
+  c.stage = c.gstage_row ? c.gstage_row + c.base : c.smem_stage;
+  if (threadIdx.x == 0) c.x->ring_phase = 0;
+
+  const int tid = threadIdx.x;
+  const hs_row_params P = a.params[c.row];
+  hs_row_out* out = a.out + c.row;
+  const bool greedy = P.temperature == 0.0f;
+
+  // ---- A. the one read of the row from HBM -----------------------------------------
+  {
+    const long long gofs = (long long)c.row * a.row_stride + c.base;
+    if (a.dtype == HS_DTYPE_BF16) {
+      const unsigned short* src = reinterpret_cast<const unsigned short*>(a.logits) + gofs;
+      const bool vec = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+      const int nvec = vec ? c.n_local / 8 : 0;
+      const uint4* src4 = reinterpret_cast<const uint4*>(src);
+      for (int i = tid; i < nvec; i += kThreads) {
+        const uint4 w = __ldcs(src4 + i);
+        float4 lo, hi;
+        lo.x = canonical(__uint_as_float(w.x << 16)); lo.y = canonical(__uint_as_float(w.x & 0xffff0000u));
+        lo.z = canonical(__uint_as_float(w.y << 16)); lo.w = canonical(__uint_as_float(w.y & 0xffff0000u));
+        hi.x = canonical(__uint_as_float(w.z << 16)); hi.y = canonical(__uint_as_float(w.z & 0xffff0000u));
+        hi.z = canonical(__uint_as_float(w.w << 16)); hi.w = canonical(__uint_as_float(w.w & 0xffff0000u));
+        float4* dst = reinterpret_cast<float4*>(c.stage + 8 * i);
+        dst[0] = lo;
+        dst[1] = hi;
+      }
+      for (int i = nvec * 8 + tid; i < c.n_local; i += kThreads)
+        c.stage[i] = canonical(__uint_as_float((uint32_t)src[i] << 16));
+    } else {
+      const float* src = reinterpret_cast<const float*>(a.logits) + gofs;
+      const bool vec = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+      const int nvec = vec ? c.n_local / 4 : 0;
+      const float4* src4 = reinterpret_cast<const float4*>(src);
+      for (int i = tid; i < nvec; i += kThreads) {
+        float4 w = __ldcs(src4 + i);
+        w.x = canonical(w.x); w.y = canonical(w.y); w.z = canonical(w.z); w.w = canonical(w.w);
+        reinterpret_cast<float4*>(c.stage)[i] = w;
+      }
+      for (int i = nvec * 4 + tid; i < c.n_local; i += kThreads) c.stage[i] = canonical(src[i]);
+    }
+  }
+  c.sync_all();
+
+  // ---- B. penalties from the row's resident (id, count) list -------------------------
+  const bool penalised = P.slot >= 0 && (P.repetition_penalty != 1.0f || P.presence_penalty != 0.0f ||
+                                          P.frequency_penalty != 0.0f);
+  if (penalised) {
+    const int n_unique = a.pool_n[P.slot];
+    const int32_t* ids = a.pool_ids + (size_t)P.slot * a.unique_cap;
+    const int32_t* cnts = a.pool_cnts + (size_t)P.slot * a.unique_cap;
+    for (int j = (int)c.rank * kThreads + tid; j < n_unique; j += (int)c.nranks * kThreads) {
+      const int id = ids[j];
+      if (id < 0 || id >= a.vocab) continue;
+      const unsigned r = (unsigned)(id / a.slice);
+      float* p = c.slice_of(r) + (id - (int)r * a.slice);
+      float v = *p;
+      v = v < 0.0f ? __fmul_rn(v, P.repetition_penalty) : __fdiv_rn(v, P.repetition_penalty);
+      v = __fsub_rn(v, P.presence_penalty);
+      v = __fsub_rn(v, __fmul_rn(P.frequency_penalty, (float)cnts[j]));
+      *p = canonical(v);
+    }
+    if (c.gstage_row) __threadfence();
+    c.sync_all();
+  }
+
+  // ---- C. temperature, row max, arg max ----------------------------------------------
+  u64 best = 0;
+  for (int i = tid; i < c.n_local; i += kThreads) {
+    float v = c.stage[i];
+    if (!greedy) {
+      v = canonical(__fdiv_rn(v, P.temperature));
+      c.stage[i] = v;
+    }
+    const u64 packed = ((u64)key_of(v) << 32) | (uint32_t)(~(uint32_t)(c.base + i));
+    best = packed > best ? packed : best;
+  }
+  best = block_max_u64(*c.x, best);
+  {
+    u64 vals[1] = {best};
+    u64 all[kMaxCluster][1];
+    cluster_allgather<1>(c.cluster, *c.x, vals, all);
+    for (unsigned r = 0; r < c.nranks; ++r) best = all[r][0] > best ? all[r][0] : best;
+  }
+  const uint32_t max_key = (uint32_t)(best >> 32);
+  const int argmax_id = (int)(~(uint32_t)(best & 0xffffffffu));
+  const float m = score_of(max_key);
+
+  KeptSet kept{0u, 0x7fffffff};
+  int token = argmax_id;
+  int status = 0;
+  u64 n_topk = (u64)a.vocab, n_minp = (u64)a.vocab, n_kept = (u64)a.vocab;
+  u64 q_kept = 0;
+  bool have_totals = false;
+  long long cut_ties = -1;
+
+  if (!greedy) {
+    u64 cnt = 0, mass = 0;
+    if (P.top_k > 0 && P.top_k < a.vocab) {
+      Selection sk = descend<false, true>(c, 0u, (u64)P.top_k, 1.0f, m);
+      if (!sk.ok) status |= 1;
+      kept.cut_key = sk.key;
+      cnt = sk.above_cnt + sk.bin_cnt;
+      mass = sk.above_mass + sk.bin_mass;
+      have_totals = sk.ok;
+      n_topk = cnt;
+    }
+    if (P.min_p > 0.0f) {
+      if (!have_totals) totals_above(c, kept.cut_key, m, true, cnt, mass);
+      const float z1 = mass_to_float(mass);
+      const float thr = __fmul_rn(__fdiv_rn(1.0f, z1), P.min_p);
+      uint32_t lowest = 0xffffffffu;
+      for (int i = tid; i < c.n_local; i += kThreads) {
+        const float s = c.stage[i];
+        const uint32_t k = key_of(s);
+        if (k >= kept.cut_key && !(__fdiv_rn(expf(s - m), z1) < thr)) lowest = min(lowest, k);
+      }
+      lowest = ~block_max_u32(*c.x, ~lowest);
+      u64 vals[1] = {(u64)lowest};
+      u64 all[kMaxCluster][1];
+      cluster_allgather<1>(c.cluster, *c.x, vals, all);
+      for (unsigned r = 0; r < c.nranks; ++r) lowest = min(lowest, (uint32_t)all[r][0]);
+      if (lowest != 0xffffffffu && lowest > kept.cut_key) {
+        kept.cut_key = lowest;
+        have_totals = false;
+      }
+    }
+    if (P.top_p < 1.0f) {
+      Selection sp = descend<true, true>(c, kept.cut_key, 0, P.top_p, m);
+      n_minp = sp.total_cnt;
+      if (sp.ok && sp.bin_cnt > 0) {
+        const u64 qv = sp.bin_mass / sp.bin_cnt;  // all elements of the bin share one score
+        u64 t = sp.bin_cnt;
+        if (qv > 0) {
+          const u64 want = sp.target - sp.above_mass;
+          t = (want + qv - 1) / qv;
+          if (t < 1) t = 1;
+          if (t > sp.bin_cnt) t = sp.bin_cnt;
+        }
+        kept.cut_key = sp.key;
+        cnt = sp.above_cnt + t;
+        mass = sp.above_mass + t * qv;
+        cut_ties = (long long)t;
+        have_totals = true;
+        if (t < sp.bin_cnt) kept.tie_limit = find_tth_equal(c, sp.key, t);
+      } else {
+        status |= 1;
+        cnt = sp.total_cnt;
+        mass = sp.total_mass;
+        have_totals = true;
+      }
+    } else {
+      if (!have_totals) totals_above(c, kept.cut_key, m, true, cnt, mass);
+      have_totals = true;
+      n_minp = cnt;
+    }
+    n_kept = cnt;
+    q_kept = mass;
+
+    // ---- draw ------------------------------------------------------------------------
+    if (q_kept == 0) {
+      token = argmax_id;
+      status |= 1;
+    } else if (a.noise) {
+      token = draw_with_noise(c, kept, m, mass_to_float(q_kept), a.noise + (size_t)c.row * a.vocab);
+    } else {
+      const Philox4 r = philox4x32_10(0u, 0u, 0u, 0u, (uint32_t)P.seed, (uint32_t)(P.seed >> 32));
+      const u64 r64 = ((u64)r.v[0] << 32) | r.v[1];
+      const u64 target = __umul64hi(r64, q_kept);
+      token = draw_inverse_cdf(c, kept, m, target);
+      if (token < 0) { token = argmax_id; status |= 1; }
+    }
+  } else if (P.n_logprobs >= 0) {
+    u64 cnt;
+    totals_above(c, 0u, m, true, cnt, q_kept);
+  }
+
+  // ---- D. log-probabilities ----------------------------------------------------------
+  float log_z = 0.f;
+  if (P.n_logprobs >= 0) {
+    log_z = (float)(log((double)q_kept) - (double)kMassShift * 0.6931471805599453);
+    const unsigned owner = (unsigned)(token / a.slice);
+    if (c.rank == owner && tid == 0) {
+      const float s = c.stage[token - (int)owner * a.slice];
+      out->logprob = (s - m) - log_z;
+    }
+    int n_want = min(P.n_logprobs, a.vocab);
+    if ((u64)n_want > n_kept) n_want = (int)n_kept;
+    if (n_want > 0) {
+      Selection sn = descend<false, false>(c, kept.cut_key, (u64)n_want, 1.0f, m);
+      if (sn.ok) {
+        write_top_logprobs(c, kept, sn.key, sn.above_cnt, n_want, m, log_z, out);
+      } else {
+        n_want = 0;
+        status |= 1;
+      }
+    }
+    if (c.rank == 0 && tid == 0) out->n_top = n_want;
+  } else if (c.rank == 0 && tid == 0) {
+    out->n_top = 0;
+    out->logprob = 0.f;
+  }
+
+  // ---- E. optional dump of the final scores (parity tests) ----------------------------
+  if (a.scores_out) {
+    float* dst = a.scores_out + (size_t)c.row * a.vocab + c.base;
+    for (int i = tid; i < c.n_local; i += kThreads) {
+      const float s = c.stage[i];
+      dst[i] = (greedy || kept.has(key_of(s), c.base + i)) ? s : __int_as_float(0xff800000);
+    }
+  }
+
+  if (c.rank == 0 && tid == 0) {
+    out->token = token;
+    out->status = status;
+    out->n_kept = (int32_t)n_kept;
+    out->n_after_topk = (int32_t)n_topk;
+    out->n_after_minp = (int32_t)n_minp;
+    out->n_after_topp = (int32_t)n_kept;
+    out->cut_bits = __float_as_uint(score_of(kept.cut_key));
+    out->n_cut_ties = (int32_t)cut_ties;
+    out->row_max = m;
+    out->log_z = log_z;
+    if ((a.flags & HS_SAMPLE_APPEND_TOKEN) && P.slot >= 0 && token >= 0 && token < a.vocab) {
+      int32_t* pos = a.pool_pos + (size_t)P.slot * a.pos_stride;
+      int32_t* ids = a.pool_ids + (size_t)P.slot * a.unique_cap;
+      int32_t* cnts = a.pool_cnts + (size_t)P.slot * a.unique_cap;
+      const int p = pos[token];
+      if (p > 0) {
+        cnts[p - 1] += 1;
+      } else {
+        const int n = a.pool_n[P.slot];
+        if (n < a.unique_cap) {
+          ids[n] = token;
+          cnts[n] = 1;
+          pos[token] = n + 1;
+          a.pool_n[P.slot] = n + 1;
+        } else {
+          out->status = status | 2;
+        }
+      }
+    }
+  }
+  // No CTA may leave while a peer can still read its shared memory.
+  c.sync_all();
+}
+
+}  // namespace hs

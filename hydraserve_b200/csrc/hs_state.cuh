@@ -1,0 +1,160 @@
+// Device-resident token-count histograms (one per request slot) and the plain-greedy
+// arg-max kernels.
+//
+// A slot holds the sparse form of the `counts` dict the reference builds per row per step
+// (sampling.py:106-110): parallel lists ids[] / cnts[] of the distinct token ids seen so
+// far, plus a dense index pos[token] = 1 + position in the lists (0 = unseen) that is
+// touched only when tokens are appended.  The sampling kernel reads just the lists
+// (8 bytes per distinct id, coalesced).
+#pragma once
+
+#include "hs_common.cuh"
+#include "../../include/hs_sampler.h"
+
+namespace hs {
+
+struct Pool {
+  int32_t* ids;    // [slots_total, unique_cap]
+  int32_t* cnts;   // [slots_total, unique_cap]
+  int32_t* n;      // [slots_total]
+  int32_t* pos;    // [slots_total, pos_stride]
+  int32_t* error;  // [1] sticky: 1 = a slot overflowed unique_cap
+  int slots_total;
+  int unique_cap;
+  long long pos_stride;
+};
+
+// Empties each listed slot by walking its id list (no dense clear).
+__global__ void slots_reset_kernel(Pool p, const int32_t* slots, int n_slots) {
+  const int s = blockIdx.x < n_slots ? slots[blockIdx.x] : -1;
+  if (s < 0 || s >= p.slots_total) return;
+  const int n = min(p.n[s], p.unique_cap);
+  const int32_t* ids = p.ids + (size_t)s * p.unique_cap;
+  int32_t* pos = p.pos + (size_t)s * p.pos_stride;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    const int id = ids[j];
+    if (id >= 0 && id < p.pos_stride) pos[id] = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) p.n[s] = 0;
+}
+
+// Pass 1 of an append: give every token id not yet in the slot a list position.
+__global__ void slots_register_kernel(Pool p, const int32_t* tokens, const int32_t* offsets,
+                                      const int32_t* slots, int n_slots, int vocab) {
+  const int row = blockIdx.y;
+  const int s = row < n_slots ? slots[row] : -1;
+  if (s < 0 || s >= p.slots_total) return;
+  const int t0 = offsets[row], t1 = offsets[row + 1];
+  int32_t* ids = p.ids + (size_t)s * p.unique_cap;
+  int32_t* cnts = p.cnts + (size_t)s * p.unique_cap;
+  int32_t* pos = p.pos + (size_t)s * p.pos_stride;
+  for (int j = t0 + blockIdx.x * blockDim.x + threadIdx.x; j < t1; j += gridDim.x * blockDim.x) {
+    const int t = tokens[j];
+    if (t < 0 || t >= vocab || t >= p.pos_stride) continue;  // ignored, as in the reference
+    if (atomicCAS(&pos[t], 0, -1) == 0) {
+      const int idx = atomicAdd(&p.n[s], 1);
+      if (idx < p.unique_cap) {
+        ids[idx] = t;
+        cnts[idx] = 0;
+        pos[t] = idx + 1;
+      } else {
+        atomicSub(&p.n[s], 1);
+        pos[t] = 0;
+        *p.error = 1;
+      }
+    }
+  }
+}
+
+// Pass 2 of an append: count.
+__global__ void slots_count_kernel(Pool p, const int32_t* tokens, const int32_t* offsets,
+                                   const int32_t* slots, int n_slots, int vocab) {
+  const int row = blockIdx.y;
+  const int s = row < n_slots ? slots[row] : -1;
+  if (s < 0 || s >= p.slots_total) return;
+  const int t0 = offsets[row], t1 = offsets[row + 1];
+  int32_t* cnts = p.cnts + (size_t)s * p.unique_cap;
+  const int32_t* pos = p.pos + (size_t)s * p.pos_stride;
+  for (int j = t0 + blockIdx.x * blockDim.x + threadIdx.x; j < t1; j += gridDim.x * blockDim.x) {
+    const int t = tokens[j];
+    if (t < 0 || t >= vocab || t >= p.pos_stride) continue;
+    const int q = pos[t];
+    if (q > 0) atomicAdd(&cnts[q - 1], 1);
+  }
+}
+
+// ---- plain greedy: arg max per row, lowest id on ties (reference sampling.py:69-73) ---
+constexpr int kGreedyThreads = 512;
+
+// Each CTA scans one chunk of one row and leaves (key << 32 | ~id) of its best element.
+__global__ void __launch_bounds__(kGreedyThreads) greedy_partial_kernel(
+    const void* logits, int dtype, long long row_stride, int vocab, int chunk, u64* partials) {
+  __shared__ u64 warp_best[kGreedyThreads / 32];
+  const int row = blockIdx.y;
+  const int begin = blockIdx.x * chunk;
+  const int n = max(0, min(chunk, vocab - begin));
+  const int tid = threadIdx.x;
+  u64 best = 0;
+  auto consider = [&](float f, int gid) {
+    const u64 packed = ((u64)key_of(canonical(f)) << 32) | (uint32_t)(~(uint32_t)gid);
+    best = packed > best ? packed : best;
+  };
+  const long long gofs = (long long)row * row_stride + begin;
+  if (dtype == HS_DTYPE_BF16) {
+    const unsigned short* src = reinterpret_cast<const unsigned short*>(logits) + gofs;
+    const bool vec = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+    const int nvec = vec ? n / 8 : 0;
+    const uint4* src4 = reinterpret_cast<const uint4*>(src);
+    for (int i = tid; i < nvec; i += kGreedyThreads) {
+      const uint4 w = __ldcs(src4 + i);
+      const int g = begin + 8 * i;
+      consider(__uint_as_float(w.x << 16), g + 0); consider(__uint_as_float(w.x & 0xffff0000u), g + 1);
+      consider(__uint_as_float(w.y << 16), g + 2); consider(__uint_as_float(w.y & 0xffff0000u), g + 3);
+      consider(__uint_as_float(w.z << 16), g + 4); consider(__uint_as_float(w.z & 0xffff0000u), g + 5);
+      consider(__uint_as_float(w.w << 16), g + 6); consider(__uint_as_float(w.w & 0xffff0000u), g + 7);
+    }
+    for (int i = nvec * 8 + tid; i < n; i += kGreedyThreads)
+      consider(__uint_as_float((uint32_t)src[i] << 16), begin + i);
+  } else {
+    const float* src = reinterpret_cast<const float*>(logits) + gofs;
+    const bool vec = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+    const int nvec = vec ? n / 4 : 0;
+    const float4* src4 = reinterpret_cast<const float4*>(src);
+    for (int i = tid; i < nvec; i += kGreedyThreads) {
+      const float4 w = __ldcs(src4 + i);
+      const int g = begin + 4 * i;
+      consider(w.x, g); consider(w.y, g + 1); consider(w.z, g + 2); consider(w.w, g + 3);
+    }
+    for (int i = nvec * 4 + tid; i < n; i += kGreedyThreads) consider(src[i], begin + i);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const u64 t = __shfl_xor_sync(0xffffffffu, best, o);
+    best = t > best ? t : best;
+  }
+  if ((tid & 31) == 0) warp_best[tid >> 5] = best;
+  __syncthreads();
+  if (tid < 32) {
+    best = tid < kGreedyThreads / 32 ? warp_best[tid] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const u64 t = __shfl_xor_sync(0xffffffffu, best, o);
+      best = t > best ? t : best;
+    }
+    if (tid == 0) partials[(size_t)row * gridDim.x + blockIdx.x] = best;
+  }
+}
+
+__global__ void greedy_final_kernel(const u64* partials, int chunks, int batch, int32_t* tokens_out) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= batch) return;
+  u64 best = 0;
+  for (int g = 0; g < chunks; ++g) {
+    const u64 t = partials[(size_t)row * chunks + g];
+    best = t > best ? t : best;
+  }
+  tokens_out[row] = (int32_t)(~(uint32_t)(best & 0xffffffffu));
+}
+
+}  // namespace hs

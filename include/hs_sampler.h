@@ -1,0 +1,134 @@
+/*
+ * hs_sampler.h -- C ABI of the B200 (sm_100a) per-step token sampler.
+ *
+ * The reference (HydraServe) has no FFI: its boundary for this path is the Python
+ * module hydraserve/engine/sampling.py.  Each entry point below names the piece of that
+ * module it stands in for.  Plain C types only; every function returns an hs_status
+ * (0 = ok, negative = error) and never throws or aborts.  Unless a parameter says
+ * "host", pointers are DEVICE pointers valid on the sampler's device, and work is
+ * enqueued on the given CUDA stream (a cudaStream_t passed as void*) without
+ * synchronising it.
+ */
+#ifndef HS_SAMPLER_H
+#define HS_SAMPLER_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HS_MAX_LOGPROBS 20 /* reference sampling.py:38 */
+
+typedef enum {
+  HS_OK = 0,
+  HS_ERR_INVALID = -1,   /* bad argument (null pointer, negative size, unknown dtype) */
+  HS_ERR_CAPACITY = -2,  /* vocabulary, batch, slot or history beyond what hs_create sized */
+  HS_ERR_CUDA = -3,      /* a CUDA runtime call failed; see hs_last_error */
+  HS_ERR_UNSUPPORTED = -4
+} hs_status;
+
+typedef enum { HS_DTYPE_F32 = 0, HS_DTYPE_BF16 = 1 } hs_dtype;
+
+/* Bits of hs_row_params.flags. */
+#define HS_ROW_PLAIN_GREEDY 1u /* temperature 0, no penalties, no logprobs: argmax only */
+
+/* Bits of the `flags` argument of hs_sample. */
+#define HS_SAMPLE_APPEND_TOKEN 1u /* after sampling, count the sampled token in the row's slot */
+
+/* One row's sampling parameters: the numeric fields of SamplingParams
+ * (reference sampling.py:8-19) in the fp32 precision the reference computes in. */
+typedef struct hs_row_params {
+  float temperature;        /* 0 = greedy (sampling.py:122) */
+  float top_p;              /* (0,1]; 1 = off */
+  float min_p;              /* [0,1]; 0 = off */
+  float repetition_penalty; /* 1 = off */
+  float presence_penalty;   /* 0 = off */
+  float frequency_penalty;  /* 0 = off */
+  int32_t top_k;            /* 0 = off */
+  int32_t n_logprobs;       /* -1 = none, else 0..20 (sampling.py:152-155) */
+  uint64_t seed;            /* (seed + (step+1)*0x1E3779B97F4A7C15) mod 2^63 (sampling.py:148) */
+  uint32_t flags;           /* HS_ROW_* */
+  int32_t slot;             /* token-count histogram to penalise with, or -1 for none */
+} hs_row_params;
+
+/* One row's result: the fields of TokenSample (reference sampling.py:47-51) plus what the
+ * parity tests need to compare candidate sets. */
+typedef struct hs_row_out {
+  int32_t token;         /* sampled / argmax token id */
+  float logprob;         /* log-probability of `token` (valid when n_logprobs >= 0) */
+  int32_t n_top;         /* number of valid entries in top_ids / top_logprobs */
+  int32_t status;        /* 0 ok; bit 0: selection fell back (non-finite input) */
+  int32_t n_kept;        /* size of the final candidate set */
+  int32_t n_after_topk;  /* candidates left by top-k (ties at the k-th value kept) */
+  int32_t n_after_minp;  /* ... and by min-p */
+  int32_t n_after_topp;  /* ... and by top-p (== n_kept) */
+  uint32_t cut_bits;     /* fp32 bits of the lowest kept score */
+  int32_t n_cut_ties;    /* how many tokens scoring exactly the cut are kept (lowest ids) */
+  float row_max;         /* largest score after penalties and temperature */
+  float log_z;           /* log of the soft-max denominator over the kept set, relative to row_max */
+  int32_t top_ids[HS_MAX_LOGPROBS];
+  float top_logprobs[HS_MAX_LOGPROBS];
+} hs_row_out;
+
+typedef struct hs_sampler hs_sampler;
+
+/* Create a sampler on `device`.  vocab_max: largest vocabulary any call will pass.
+ * slots_max: number of resident token-count histograms (one per request in flight).
+ * unique_cap: most distinct token ids one histogram can hold (<= vocab_max; 0 = vocab_max).
+ * batch_max: most rows per call.  Allocates all device memory the sampler will ever use. */
+int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batch_max,
+              hs_sampler** out);
+int hs_destroy(hs_sampler* h);
+
+/* Token-count histograms: the device-resident form of the `counts` dict the reference
+ * rebuilds per row per step (sampling.py:106-110).
+ * hs_slots_reset empties the listed slots.  hs_slots_append counts tokens
+ * tokens[offsets[i] .. offsets[i+1]) into slot slots[i]; ids outside [0, vocab) are
+ * ignored as in the reference (sampling.py:108).  slots must not repeat within a call. */
+int hs_slots_reset(hs_sampler* h, const int32_t* slots, int n_slots, void* stream);
+int hs_slots_append(hs_sampler* h, const int32_t* tokens, const int32_t* offsets,
+                    const int32_t* slots, int n_slots, int vocab, int max_tokens_per_slot,
+                    void* stream);
+/* Host-side count of distinct ids in a slot (synchronises the stream); for tests. */
+int hs_slot_unique_count(hs_sampler* h, int slot, void* stream, int* out);
+
+/* sample_logits (reference sampling.py:54-83) for rows of one batch.
+ * logits: [batch, vocab] of `dtype`, row r starting at logits + r*row_stride elements.
+ * noise: NULL, or [batch, vocab] fp32 Exp(1) variates; when given, the draw is
+ *   argmax(p / noise) as torch.multinomial does on CPU (sampling.py:150) instead of the
+ *   Philox stream.  For parity tests.
+ * scores_out: NULL, or [batch, vocab] fp32 that receives the reference's final `scores`
+ *   (penalised, temperature-scaled, -inf where filtered).  For parity tests. */
+int hs_sample(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch,
+              int vocab, const hs_row_params* params, hs_row_out* out, const float* noise,
+              float* scores_out, uint32_t flags, void* stream);
+
+/* The all-rows-plain-greedy fast path (reference sampling.py:69-73): argmax per row,
+ * lowest id on ties, int32 token ids to tokens_out[batch]. */
+int hs_greedy(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch,
+              int vocab, int32_t* tokens_out, void* stream);
+
+/* Same as hs_sample but every pointer is a HOST pointer; copies in and out on `stream`
+ * through pinned staging buffers owned by the sampler and synchronises before returning.
+ * hist_tokens/hist_offsets: flat per-row histories (offsets has batch+1 entries), or NULL;
+ * rows whose params.slot is -2 are penalised with their history from these arrays
+ * (rebuilt on the device for this call, the reference's stateless behaviour). */
+int hs_sample_host(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch,
+                   int vocab, hs_row_params* params, hs_row_out* out,
+                   const int32_t* hist_tokens, const int32_t* hist_offsets, uint32_t flags,
+                   void* stream);
+
+/* Introspection. */
+const char* hs_last_error(hs_sampler* h);
+const char* hs_status_string(int status);
+int hs_abi_version(void);
+/* what: 0 = CTAs per row (cluster size) hs_sample would use for (vocab, dtype),
+ *       1 = 1 if that row would be staged in shared memory, 0 if in global scratch,
+ *       2 = number of SMs, 3 = kernels launched by this sampler so far (low 31 bits) */
+int hs_query(hs_sampler* h, int what, int vocab, int dtype);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HS_SAMPLER_H */

@@ -1,0 +1,93 @@
+"""Named, seeded test inputs shared by the golden-fixture script, the checker tests and
+the GPU parity tests.  A case is a function of its name only."""
+from __future__ import annotations
+
+import numpy as np
+
+from hydraserve_b200 import workloads
+from hydraserve_b200.engine.sampling import SamplingParams
+from hydraserve_b200.workloads import Workload, f32_to_bf16_bits
+
+
+def small_mixed(seed: int, batch: int, vocab: int, dtype: str) -> Workload:
+    """Rows over a small vocabulary that walk through every parameter combination the
+    sampler has, with quantised logits so exact ties are everywhere."""
+    rng = np.random.default_rng(seed)
+    logits = np.empty((batch, vocab), np.float32)
+    params, histories, steps = [], [], []
+    for r in range(batch):
+        scale = float(rng.choice([0.05, 0.5, 2.0, 4.0, 8.0]))
+        row = rng.standard_normal(vocab).astype(np.float32) * np.float32(scale)
+        style = r % 4
+        if style == 1:  # few distinct levels: many ties
+            row = np.round(row * 4) / 4
+        elif style == 2:  # a dominant spike
+            row[rng.integers(0, vocab)] += np.float32(15.0)
+        elif style == 3:  # all equal but a handful
+            row[:] = np.float32(rng.normal())
+            row[rng.choice(vocab, size=min(5, vocab), replace=False)] += np.float32(1.5)
+        logits[r] = row
+        temperature = float(rng.choice([0.0, 0.3, 0.7, 1.0, 1.5, 2.0]))
+        top_k = int(rng.choice([0, 0, 1, 5, 50, vocab, vocab + 10]))
+        top_p = float(rng.choice([1.0, 1.0, 0.99, 0.9, 0.5, 0.1]))
+        min_p = float(rng.choice([0.0, 0.0, 0.01, 0.1, 0.5, 1.0]))
+        rep = float(rng.choice([1.0, 1.0, 1.1, 0.8, 2.0]))
+        pres = float(rng.choice([0.0, 0.0, 0.5, -0.5, 2.0]))
+        freq = float(rng.choice([0.0, 0.0, 0.3, -0.2, 2.0]))
+        logprobs = rng.choice([-1, -1, 0, 1, 5, 20])
+        params.append(SamplingParams(
+            temperature=temperature, top_k=top_k, top_p=top_p, min_p=min_p,
+            repetition_penalty=rep, presence_penalty=pres, frequency_penalty=freq,
+            seed=int(rng.integers(0, 2**63 - 1)), logprobs=None if logprobs < 0 else int(logprobs)))
+        n_hist = int(rng.choice([0, 1, 17, 300, 4000]))
+        history = rng.integers(-3, vocab + 3, n_hist).astype(np.int32)  # some ids out of range
+        histories.append(history)
+        steps.append(int(rng.integers(0, 10_000)))
+    if dtype == "bf16":
+        return Workload(f"small_{dtype}", f32_to_bf16_bits(logits), "bf16", histories, params, steps)
+    return Workload(f"small_{dtype}", logits, "f32", histories, params, steps)
+
+
+def tiny(vocab: int) -> Workload:
+    """Vocabularies of a few entries: unaligned rows, top_k >= V, logprobs > V."""
+    rng = np.random.default_rng(100 + vocab)
+    batch = 6
+    logits = (rng.standard_normal((batch, vocab)) * 2).astype(np.float32)
+    params = [
+        SamplingParams(),
+        SamplingParams(logprobs=20),
+        SamplingParams(temperature=1.0, seed=1, logprobs=3),
+        SamplingParams(temperature=0.5, top_k=2, seed=2, logprobs=20),
+        SamplingParams(temperature=1.3, top_p=0.6, min_p=0.2, seed=3, frequency_penalty=1.0, logprobs=2),
+        SamplingParams(temperature=2.0, top_k=1, top_p=0.5, seed=4, repetition_penalty=1.5),
+    ]
+    histories = [rng.integers(0, vocab, 5).astype(np.int32) for _ in range(batch)]
+    return Workload(f"tiny_v{vocab}", logits, "f32", histories, params, list(range(batch)))
+
+
+_CASES = {
+    "config1": lambda: workloads.config1(),
+    "config2_8rows": lambda: workloads.config2(batch=8),
+    "config3_4rows": lambda: workloads.config3(batch=4),
+    "config4_8rows": lambda: workloads.config4(batch=8),
+    "config5_4rows": lambda: workloads.config5(batch=4),
+    "small_f32": lambda: small_mixed(11, 48, 2048, "f32"),
+    "small_bf16": lambda: small_mixed(12, 48, 2048, "bf16"),
+    "small_odd_f32": lambda: small_mixed(13, 24, 1003, "f32"),
+    "small_odd_bf16": lambda: small_mixed(14, 24, 1003, "bf16"),
+    "tiny_v1": lambda: tiny(1),
+    "tiny_v2": lambda: tiny(2),
+    "tiny_v3": lambda: tiny(3),
+    "tiny_v9": lambda: tiny(9),
+    "tiny_v33": lambda: tiny(33),
+}
+
+GOLDEN_CASES = tuple(_CASES)
+
+_cache: dict = {}
+
+
+def build(name: str) -> Workload:
+    if name not in _cache:
+        _cache[name] = _CASES[name]()
+    return _cache[name]

@@ -1,0 +1,89 @@
+"""The CPU checker against outputs of the unmodified reference (tests/golden) and against
+the reference's own unit-test cases.  Runs without a GPU."""
+import numpy as np
+import pytest
+
+from oracle import sampler_oracle as O
+from hydraserve_b200.engine.sampling import SamplingParams
+from tests import cases, parity
+
+GOLDEN = cases.GOLDEN_CASES
+# Relative noise of the reference's fp32 CPU soft-max denominators (measured 5e-6 on a
+# 151,936-wide row); a top-p cut closer than this to its threshold may move.
+REFERENCE_EPS = 2e-5
+
+
+@pytest.mark.parametrize("name", GOLDEN)
+def test_checker_matches_reference_outputs(name):
+    from pathlib import Path
+
+    g = np.load(Path(__file__).parent / "golden" / f"{name}.npz")
+    w = cases.build(name)
+    x = w.logits_f32()
+    report = parity.Report()
+    for r in range(w.batch):
+        o = O.sample_row(x[r], w.histories[r], w.params[r], w.steps[r])
+        a, b = int(g["top_off"][r]), int(g["top_off"][r + 1])
+        top = list(zip(g["top_ids"][a:b].tolist(), g["top_vals"][a:b].tolist()))
+        ka, kb = int(g["kept_off"][r]), int(g["kept_off"][r + 1])
+        kept_n = int(g["kept_n"][r])
+        kept_ids = g["kept_ids"][ka:kb] if (kb - ka) == kept_n and kept_n >= 0 else None
+        parity.compare_with_oracle(
+            report, r, o,
+            token=int(g["tokens"][r]),
+            logprob=float(g["logprobs"][r]) if g["has_logprob"][r] else None,
+            top=top, kept_n=kept_n, kept_ids=kept_ids, kept_sum=int(g["kept_sum"][r]),
+            cut_value=None if kept_n < 0 else g["kept_min"][r],
+            eps=REFERENCE_EPS, exact_ties=False)
+    report.assert_ok()
+
+
+def test_reference_unit_case_greedy_penalties_logprobs():
+    # reference tests/test_sampling.py:17-30
+    o = O.sample_row(np.array([0.0, 5.0, 4.0], np.float32), (1, 1),
+                     SamplingParams(frequency_penalty=2.0, logprobs=2), 0)
+    assert o.token == 2
+    assert o.logprob is not None and len(o.top_logprobs) == 2
+    assert o.penalised.tolist() == [0.0, 1.0, 4.0]
+
+
+def test_reference_unit_case_plain_greedy_rows():
+    # reference tests/test_sampling.py:33-48
+    rows = np.array([[0.0, 5.0, 4.0], [9.0, 2.0, 3.0]], np.float32)
+    got = [O.sample_row(rows[i], h, SamplingParams(), s).token for i, (h, s) in enumerate((((1, 1), 0), ((2,), 4)))]
+    assert got == [1, 0]
+
+
+def test_reference_unit_case_penalty_without_logprobs():
+    # reference tests/test_sampling.py:76-90
+    o = O.sample_row(np.array([0.0, 5.0, 4.0], np.float32), (1,), SamplingParams(frequency_penalty=1.0), 0)
+    assert o.token == 1
+
+
+def test_out_of_range_history_ids_are_ignored():
+    o = O.sample_row(np.array([1.0, 2.0, 3.0], np.float32), (-1, 3, 99, 2, 2),
+                     SamplingParams(frequency_penalty=1.0, logprobs=1), 0)
+    assert o.scores.tolist() == [1.0, 2.0, 1.0]
+
+
+def test_top_k_keeps_ties_at_the_kth_value():
+    x = np.zeros(1000, np.float32)
+    x[[3, 10, 500]] = 5.0
+    x[[4, 600, 700, 800]] = 4.0
+    o = O.sample_row(x, (), SamplingParams(temperature=1.0, top_k=4, seed=1, logprobs=1), 0)
+    assert o.kept.tolist() == [3, 4, 10, 500, 600, 700, 800]
+
+
+def test_mixed_seed_known_answers():
+    assert O.mixed_seed(0, 0) == 2177342782468422677
+    assert O.mixed_seed(123, 3) == 8709371129873690831
+    assert O.mixed_seed(2**63 - 1, 10**6) == 1969814971929979732
+
+
+def test_rows_do_not_depend_on_batch_position():
+    # reference tests/test_sampling.py:93-111
+    rows = np.array([[1.0, 2.0, 3.0], [3.0, 1.0, 2.0]], np.float32)
+    ps = (SamplingParams(temperature=1.0, top_p=0.9, seed=123), SamplingParams(temperature=0.8, top_k=2, seed=456))
+    a = [r.token for r in O.sample_batch(rows, ((), ()), ps, (3, 7))]
+    b = [r.token for r in O.sample_batch(rows[::-1], ((), ()), ps[::-1], (7, 3))]
+    assert a == b[::-1]
