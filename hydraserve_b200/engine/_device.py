@@ -65,7 +65,7 @@ def history_array(history, vocab: int) -> np.ndarray:
 class DeviceSampler:
     """One C-ABI sampler handle on one GPU plus the torch buffers around it."""
 
-    def __init__(self, device, vocab_max: int, batch_max: int = 256, resident_slots: int = 1024):
+    def __init__(self, device, vocab_max: int, batch_max: int = 256, resident_slots: int = 256):
         import torch
 
         if not torch.cuda.is_available():

@@ -1,0 +1,230 @@
+"""GPU parity: the CUDA sampler, called through its C ABI, against the CPU checker on
+the same seeded inputs.  Integer results (tokens, candidate sets) are compared exactly;
+floating-point results within 1e-5 relative (tests/parity.py states the tie rules)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+from oracle import sampler_oracle as O  # noqa: E402
+from tests import cases, parity  # noqa: E402
+
+# The CUDA sampler accumulates probability mass exactly (integers of 2^-40) and uses a
+# 2-ulp expf whose errors average out over a row; a cut closer than this (relative) to
+# its threshold may move by an element.
+GPU_EPS = 2e-7
+
+PARITY_CASES = [
+    "tiny_v1", "tiny_v2", "tiny_v3", "tiny_v9", "tiny_v33",
+    "small_f32", "small_bf16", "small_odd_f32", "small_odd_bf16",
+    "config1", "config2_8rows", "config3_4rows", "config4_8rows", "config5_4rows",
+]
+
+
+@pytest.fixture(scope="module")
+def sampler(built_library):
+    from hydraserve_b200.engine import _device
+
+    s = _device.DeviceSampler("cuda:0", vocab_max=420_000, batch_max=64, resident_slots=64)
+    yield s
+    s.close()
+
+
+def device_logits(w):
+    if w.dtype == "bf16":
+        return torch.from_numpy(w.logits.view(np.int16)).view(torch.bfloat16).cuda()
+    return torch.from_numpy(w.logits).cuda()
+
+
+def oracle_rows(w, draws=True):
+    x = w.logits_f32()
+    rows, noise = [], np.ones((w.batch, w.vocab), np.float32)
+    for r in range(w.batch):
+        p = w.params[r]
+        q = None
+        if p.temperature != 0.0:
+            q = O.exponential_draws(O.mixed_seed(p.seed, w.steps[r]), w.vocab)
+            noise[r] = q
+        rows.append(O.sample_row(x[r], w.histories[r], p, w.steps[r], draws=q, want_probabilities=False))
+    return rows, noise
+
+
+def compare_case(sampler, w, report=None, request_ids=None):
+    rows, noise = oracle_rows(w)
+    records, scores = sampler.sample(device_logits(w), w.histories, w.params, w.steps, request_ids,
+                                     noise=torch.from_numpy(noise), want_scores=True)
+    scores = scores.cpu().numpy()
+    report = report or parity.Report()
+    for r, o in enumerate(rows):
+        rec = records[r]
+        assert rec["status"] == 0, f"row {r} status {rec['status']}"
+        kept = np.nonzero(np.isfinite(scores[r]))[0]
+        n_top = int(rec["n_top"])
+        top = list(zip(rec["top_ids"][:n_top].tolist(), rec["top_logprobs"][:n_top].tolist()))
+        if w.params[r].logprobs is not None:
+            want = min(w.params[r].logprobs, w.vocab)
+            taken, i = {t for t, _ in top}, 0
+            while len(top) < want:
+                if i not in taken:
+                    top.append((i, float("-inf")))
+                i += 1
+        before = len(report.failures)
+        parity.compare_with_oracle(
+            report, r, o, token=int(rec["token"]),
+            logprob=float(rec["logprob"]) if w.params[r].logprobs is not None else None,
+            top=top, kept_n=int(rec["n_kept"]), kept_ids=kept, eps=GPU_EPS, exact_ties=True)
+        sensitive = parity.allowed_count_slack(o.margins, GPU_EPS) > 0
+        if len(report.failures) == before and not sensitive:
+            if int(rec["n_kept"]) != kept.size:
+                report.fail(r, f"n_kept {rec['n_kept']} disagrees with the score dump {kept.size}")
+            # kept scores (penalised, temperature-scaled) are IEEE-exact steps: bit for bit
+            if not np.array_equal(scores[r][o.kept], o.scores[o.kept]):
+                bad = np.nonzero(scores[r][o.kept] != o.scores[o.kept])[0]
+                report.fail(r, f"{bad.size} kept scores differ, first id {o.kept[bad[0]]}: "
+                               f"{scores[r][o.kept][bad[0]]!r} vs {o.scores[o.kept][bad[0]]!r}")
+            if w.params[r].temperature != 0.0:
+                if int(rec["n_after_topk"]) != o.n_after_topk:
+                    report.fail(r, f"n_after_topk {rec['n_after_topk']} != {o.n_after_topk}")
+                if int(rec["n_after_minp"]) != o.n_after_minp:
+                    report.fail(r, f"n_after_minp {rec['n_after_minp']} != {o.n_after_minp}")
+    return report
+
+
+@pytest.mark.parametrize("name", PARITY_CASES)
+def test_rows_match_checker(sampler, name):
+    report = compare_case(sampler, cases.build(name))
+    report.assert_ok(max_sensitive_fraction=0.5)
+
+
+def test_penalised_logits_bit_exact(sampler):
+    """Greedy rows dump the penalised logits themselves (no temperature, no filter)."""
+    from hydraserve_b200.engine.sampling import SamplingParams
+
+    w = cases.build("config2_8rows")
+    params = [SamplingParams(repetition_penalty=1.3, presence_penalty=-0.7, frequency_penalty=0.9, logprobs=0)
+              for _ in range(w.batch)]
+    records, scores = sampler.sample(device_logits(w), w.histories, params, w.steps, None, want_scores=True)
+    x = w.logits_f32()
+    for r in range(w.batch):
+        want = O.penalise(x[r], w.histories[r], params[r])
+        np.testing.assert_array_equal(scores[r].cpu().numpy(), np.where(want == 0, np.float32(0), want))
+        assert int(records[r]["token"]) == int(np.argmax(want))
+
+
+def test_greedy_fast_path_lowest_id_on_ties(sampler):
+    rng = np.random.default_rng(7)
+    for vocab, dtype in ((151_936, "bf16"), (248_320, "bf16"), (1003, "f32"), (5, "bf16"), (1, "f32")):
+        x = (rng.standard_normal((9, vocab)) * 3).astype(np.float32)
+        if dtype == "bf16":
+            from hydraserve_b200.workloads import bf16_bits_to_f32, f32_to_bf16_bits
+
+            bits = f32_to_bf16_bits(x)
+            x = bf16_bits_to_f32(bits)
+            # duplicate the maximum of some rows at a higher id
+            for r in range(0, 9, 2):
+                j = int(np.argmax(x[r]))
+                if j + 1 < vocab:
+                    bits[r, vocab - 1] = bits[r, j]
+                    x[r, vocab - 1] = x[r, j]
+            t = torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16).cuda()
+        else:
+            t = torch.from_numpy(x).cuda()
+        got = sampler.greedy(t).cpu().numpy()
+        np.testing.assert_array_equal(got, np.argmax(x, axis=1))
+
+
+def test_strided_and_unaligned_rows(sampler):
+    """Rows that are a view of a wider buffer: stride != vocab and 2-byte aligned only."""
+    rng = np.random.default_rng(8)
+    base = torch.from_numpy((rng.standard_normal((6, 1200)) * 2).astype(np.float32)).cuda().bfloat16()
+    view = base[:, 3:1003]
+    got = sampler.greedy(view).cpu().numpy()
+    np.testing.assert_array_equal(got, view.float().cpu().numpy().argmax(axis=1))
+    w = cases.build("small_odd_bf16")
+    full = torch.zeros((w.batch, w.vocab + 21), dtype=torch.bfloat16, device="cuda")
+    full[:, 5:5 + w.vocab] = device_logits(w)
+    rows, noise = oracle_rows(w)
+    records, _ = sampler.sample(full[:, 5:5 + w.vocab], w.histories, w.params, w.steps, None,
+                                noise=torch.from_numpy(noise))
+    ref_records, _ = sampler.sample(device_logits(w), w.histories, w.params, w.steps, None,
+                                    noise=torch.from_numpy(noise))
+    np.testing.assert_array_equal(records["token"], ref_records["token"])
+    np.testing.assert_array_equal(records["n_kept"], ref_records["n_kept"])
+
+
+def test_resident_histograms_match_stateless(sampler):
+    """request_ids keep the histogram on the device and upload only the new tokens."""
+    w = cases.build("config4_8rows")
+    rows, noise = oracle_rows(w)
+    ids = [f"req-{i}" for i in range(w.batch)]
+    # first call: histories cut short; second call: full histories (delta upload)
+    short = [h[: max(1, h.size // 2)] for h in w.histories]
+    sampler.sample(device_logits(w), short, w.params, w.steps, ids)
+    records, scores = sampler.sample(device_logits(w), w.histories, w.params, w.steps, ids,
+                                     noise=torch.from_numpy(noise), want_scores=True)
+    stateless, scores2 = sampler.sample(device_logits(w), w.histories, w.params, w.steps, None,
+                                        noise=torch.from_numpy(noise), want_scores=True)
+    np.testing.assert_array_equal(records["token"], stateless["token"])
+    assert torch.equal(scores, scores2)
+    # a shrunken history (preempt / replay) rebuilds the slot
+    records3, scores3 = sampler.sample(device_logits(w), short, w.params, w.steps, ids, want_scores=True)
+    stateless3, scores4 = sampler.sample(device_logits(w), short, w.params, w.steps, None, want_scores=True)
+    assert torch.equal(scores3, scores4)
+    for i in ids:
+        sampler.release_request(i)
+
+
+def test_global_stage_fallback_for_very_wide_rows(sampler):
+    """A row too wide for the cluster's shared memory is staged in global scratch."""
+    from hydraserve_b200.engine.sampling import SamplingParams
+    from hydraserve_b200.workloads import Workload
+
+    vocab = 410_001
+    assert sampler.query(1, vocab) == 0 and sampler.query(1, 248_320) == 1
+    rng = np.random.default_rng(9)
+    x = (rng.standard_normal((3, vocab)) * 3).astype(np.float32)
+    params = [SamplingParams(logprobs=5, presence_penalty=0.5),
+              SamplingParams(temperature=0.9, top_k=64, top_p=0.9, seed=5, logprobs=20, frequency_penalty=0.2),
+              SamplingParams(temperature=1.0, top_p=0.95, min_p=0.001, seed=6, repetition_penalty=1.2)]
+    hist = [rng.integers(0, vocab, 3000).astype(np.int32) for _ in range(3)]
+    w = Workload("wide", x, "f32", hist, params, [1, 2, 3])
+    compare_case(sampler, w).assert_ok(max_sensitive_fraction=0.34)
+
+
+def test_philox_draws_are_reproducible_and_follow_the_distribution(sampler):
+    """Seeded Philox path: same seed -> same token; across seeds the token frequencies
+    pass a chi-square test against the checker's filtered distribution."""
+    from scipy import stats
+
+    from hydraserve_b200.engine.sampling import SamplingParams
+
+    rng = np.random.default_rng(10)
+    vocab, draws = 4096, 64
+    x = (rng.standard_normal(vocab) * 2.0).astype(np.float32)
+    base = SamplingParams(temperature=0.9, top_k=40, top_p=0.95, seed=0)
+    o = O.sample_row(x, (), base, 0, draws=np.ones(vocab, np.float32))
+    probs = o.probabilities[o.kept]
+    logits = torch.from_numpy(np.tile(x, (draws, 1))).cuda()
+    counts = np.zeros(vocab, np.int64)
+    total = 0
+    first = None
+    for rep in range(320):
+        params = [base.with_seed(rep * draws + i) for i in range(draws)]
+        records, _ = sampler.sample(logits, [()] * draws, params, [rep] * draws, None)
+        if rep == 0:
+            first = records["token"].copy()
+            again, _ = sampler.sample(logits, [()] * draws, params, [rep] * draws, None)
+            np.testing.assert_array_equal(first, again["token"])
+        np.add.at(counts, records["token"], 1)
+        total += draws
+    assert counts.sum() == counts[o.kept].sum(), "a token outside the candidate set was drawn"
+    expected = probs * total
+    big = expected >= 5
+    obs = np.append(counts[o.kept][big], counts[o.kept][~big].sum())
+    exp = np.append(expected[big], expected[~big].sum())
+    if exp[-1] == 0:
+        obs, exp = obs[:-1], exp[:-1]
+    chi2, pvalue = stats.chisquare(obs, exp * obs.sum() / exp.sum())
+    assert pvalue > 1e-4, f"chi-square p={pvalue:.3g} over {total} draws"

@@ -1,0 +1,124 @@
+"""Host-side logic and the C-ABI surface; no GPU needed."""
+import ctypes as C
+import pickle
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from hydraserve_b200.engine import SamplingParams, TokenSample
+from hydraserve_b200.engine import sampling
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_sampling_params_validate_production_bounds():
+    # reference tests/test_sampling.py:6-14
+    with pytest.raises(ValueError, match="temperature"):
+        SamplingParams(temperature=-0.1)
+    with pytest.raises(ValueError, match="top_p"):
+        SamplingParams(top_p=0)
+    with pytest.raises(ValueError, match="logprobs"):
+        SamplingParams(logprobs=21)
+    with pytest.raises(ValueError, match="stop"):
+        SamplingParams(stop_token_sequences=((),))
+
+
+@pytest.mark.parametrize("kwargs,word", [
+    (dict(temperature=2.1), "temperature"), (dict(top_p=1.01), "top_p"), (dict(top_k=-1), "top_k"),
+    (dict(min_p=-0.1), "min_p"), (dict(min_p=1.1), "min_p"), (dict(repetition_penalty=0.0), "repetition_penalty"),
+    (dict(repetition_penalty=2.5), "repetition_penalty"), (dict(presence_penalty=-2.1), "presence_penalty"),
+    (dict(frequency_penalty=2.1), "frequency_penalty"), (dict(seed=-1), "seed"), (dict(seed=2**63), "seed"),
+    (dict(logprobs=-1), "logprobs"),
+])
+def test_sampling_params_reject_out_of_range(kwargs, word):
+    with pytest.raises(ValueError, match=word):
+        SamplingParams(**kwargs)
+
+
+def test_sampling_params_are_frozen_slotted_picklable():
+    p = SamplingParams(temperature=0.7, top_k=5, seed=3, logprobs=2, stop_token_sequences=((1, 2),))
+    with pytest.raises(Exception):
+        p.temperature = 1.0
+    assert not hasattr(p, "__dict__")
+    assert pickle.loads(pickle.dumps(p)) == p
+    assert p.with_seed(9).seed == 9 and p.with_seed(9).top_k == 5
+    s = TokenSample(4, -0.5, ((4, -0.5),))
+    assert pickle.loads(pickle.dumps(s)) == s
+    assert TokenSample(1) == TokenSample(1, None, ())
+
+
+def test_greedy_and_penalty_predicates():
+    assert sampling._is_plain_greedy(SamplingParams())
+    assert not sampling._is_plain_greedy(SamplingParams(logprobs=0))
+    assert not sampling._is_plain_greedy(SamplingParams(temperature=0.1))
+    assert not sampling._is_plain_greedy(SamplingParams(presence_penalty=0.1))
+    assert sampling._has_penalties(SamplingParams(repetition_penalty=1.1))
+    assert sampling._has_penalties(SamplingParams(frequency_penalty=-0.1))
+    assert not sampling._has_penalties(SamplingParams(temperature=1.0, top_k=4))
+
+
+def test_metadata_mismatch_raises_before_touching_the_gpu():
+    class FakeLogits:
+        ndim = 2
+        shape = (2, 3)
+
+    with pytest.raises(ValueError, match="metadata"):
+        sampling.sample_logits(FakeLogits(), ((),), (SamplingParams(),), steps=(0,))
+    FakeLogits.ndim = 3
+    with pytest.raises(ValueError, match="shape"):
+        sampling.sample_logits(FakeLogits(), ((),), (SamplingParams(),), steps=(0,))
+
+
+def test_param_packing_matches_the_c_struct():
+    from hydraserve_b200 import _lib
+    from hydraserve_b200.engine import _device
+
+    ps = [SamplingParams(), SamplingParams(temperature=0.7, top_k=50, top_p=0.9, min_p=0.05, repetition_penalty=1.1,
+                                           presence_penalty=0.5, frequency_penalty=0.3, seed=123, logprobs=20)]
+    rec = _device.pack_params(ps, [0, 3], [-1, 4])
+    assert rec.dtype.itemsize == 48 and rec.nbytes == 96
+    assert rec["flags"].tolist() == [_lib.HS_ROW_PLAIN_GREEDY, 0]
+    assert rec["n_logprobs"].tolist() == [-1, 20]
+    assert rec["slot"].tolist() == [-1, 4]
+    assert int(rec["seed"][1]) == 8709371129873690831  # (123, step 3): reference sampling.py:148
+    assert rec["temperature"][1] == np.float32(0.7)
+    raw = rec.view(np.uint8).reshape(2, 48)
+    assert raw[1, 24:28].view(np.int32)[0] == 50 and raw[1, 32:40].view(np.uint64)[0] == 8709371129873690831
+
+
+def test_history_array_drops_out_of_range_ids():
+    from hydraserve_b200.engine import _device
+
+    h = _device.history_array((-1, 3, 99, 2, 2), 3)
+    assert h.dtype == np.int32 and h.tolist() == [2, 2]
+    assert _device.history_array((), 5).size == 0
+    assert _device.history_array(iter([1, 2, 3]), 5).tolist() == [1, 2, 3]
+    assert _device.history_array(np.array([4, 5, 0]), 5).tolist() == [4, 0]
+
+
+def test_library_builds_and_exports_every_declared_symbol(built_library):
+    """Every function include/hs_sampler.h declares is exported by the built library and
+    bound in hydraserve_b200._lib (no compute call: that needs a GPU)."""
+    from hydraserve_b200 import _lib
+
+    header = (ROOT / "include" / "hs_sampler.h").read_text()
+    declared = set(re.findall(r"^\s*(?:int|const char\*)\s+(hs_[a-z_]+)\s*\(", header, flags=re.M))
+    assert declared, "no declarations parsed"
+    assert declared == set(_lib.EXPORTS), declared ^ set(_lib.EXPORTS)
+    lib = C.CDLL(str(built_library))
+    for name in declared:
+        assert hasattr(lib, name), f"{name} not exported"
+    lib.hs_abi_version.restype = C.c_int
+    assert lib.hs_abi_version() == 1
+    lib.hs_status_string.restype = C.c_char_p
+    assert lib.hs_status_string(-2) == b"capacity exceeded"
+
+
+def test_missing_gpu_fails_loudly():
+    torch = pytest.importorskip("torch")
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(RuntimeError, match="no CPU sampling path"):
+        sampling.sample_logits(torch.zeros(1, 3), ((),), (SamplingParams(temperature=1.0, seed=1),), steps=(0,))

@@ -87,3 +87,32 @@ def test_rows_do_not_depend_on_batch_position():
     a = [r.token for r in O.sample_batch(rows, ((), ()), ps, (3, 7))]
     b = [r.token for r in O.sample_batch(rows[::-1], ((), ()), ps[::-1], (7, 3))]
     assert a == b[::-1]
+
+
+@pytest.mark.parametrize("name", ["config1", "config2_8rows", "small_bf16", "tiny_v3"])
+def test_timing_port_reproduces_reference_outputs(name):
+    """oracle/reference_port.py (the CPU-baseline stand-in) issues the reference's own
+    torch operators, so on the machine that made the fixtures it must agree exactly on
+    tokens and candidate counts wherever the cut is not rounding-sensitive."""
+    from pathlib import Path
+
+    import torch
+
+    from oracle import reference_port
+
+    g = np.load(Path(__file__).parent / "golden" / f"{name}.npz")
+    w = cases.build(name)
+    x = torch.from_numpy(w.logits_f32().copy())
+    out = reference_port.sample_batch(x, [h.tolist() for h in w.histories], w.params, w.steps)
+    agree = 0
+    for r, (token, logprob, top) in enumerate(out):
+        o = O.sample_row(w.logits_f32()[r], w.histories[r], w.params[r], w.steps[r])
+        if parity.allowed_count_slack(o.margins, REFERENCE_EPS) or o.margins.get("top_p_splits_tie"):
+            continue
+        agree += 1
+        assert token == int(g["tokens"][r]), (r, token, int(g["tokens"][r]))
+        if g["has_logprob"][r]:
+            assert parity.close(logprob, float(g["logprobs"][r]))
+            a, b = int(g["top_off"][r]), int(g["top_off"][r + 1])
+            assert np.allclose([v for _, v in top], g["top_vals"][a:b], rtol=1e-5, atol=2e-6, equal_nan=True)
+    assert agree > 0
