@@ -264,10 +264,10 @@ def run_ours(args, world, rank, local_rank):
     value = world * batch * args.steps / (elapsed_ms * 1e-3)
 
     # ---- end to end through the drop-in Python API, logits in pinned host memory -------
-    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    e2e_steps = 0 if args.kernel_only else max(1, min(args.steps, args.e2e_steps))
     histories = [h.tolist() for h in w.histories]
     request_ids = [f"bench-{rank}-{i}" for i in range(batch)]
-    e2e_sampler = _device.sampler_for(device, vocab, batch)
+    e2e_sampler = _device.sampler_for(device, vocab, batch) if e2e_steps else None
     steps_now = list(w.steps)
     h2d = host_logits.numel() * 2 + batch * _lib.ROW_PARAMS.itemsize + batch * 4 * 3
     d2h = batch * _lib.ROW_OUT.itemsize
@@ -278,14 +278,16 @@ def run_ours(args, world, rank, local_rank):
             histories[i].append(s.token_id)
             steps_now[i] += 1
 
-    for _ in range(2):
-        e2e_step()  # the first call uploads the full histories; later calls only the new token
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+    e2e_s = float("inf")
+    if e2e_steps:
+        for _ in range(2):
+            e2e_step()  # the first call uploads the full histories; later calls only the new token
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
     if dist is not None:
         t = torch.tensor([e2e_s], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -313,7 +315,7 @@ def run_ours(args, world, rank, local_rank):
         "logits_only_gbs": logits_bytes / (ms_per_step * 1e-3) / 1e9,
     }
     cpu = None
-    if world == 1 and not args.no_cpu:
+    if world == 1 and not args.no_cpu and not args.kernel_only:
         rows = args.cpu_rows
         v, threads, dt = time_cpu_single(w, rows)
         cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
@@ -349,6 +351,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=8)
     ap.add_argument("--cpu-rows", type=int, default=64)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="time only the device-resident steps (for profiler runs): no e2e, no CPU baseline")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
