@@ -49,6 +49,7 @@ EXPORTS = {
     "hs_sample_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int,
                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "hs_query": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "hs_debug_phase_clocks": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
 }
 
 _lib = None

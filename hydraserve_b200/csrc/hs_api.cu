@@ -14,6 +14,7 @@
 #include "../../include/hs_sampler.h"
 #include "hs_common.cuh"
 #include "hs_row_kernel.cuh"
+#include "hs_row_bf16.cuh"
 #include "hs_state.cuh"
 
 namespace {
@@ -59,6 +60,10 @@ struct hs_sampler {
   int sm_count = 0;
   int smem_optin = 0;
   int force_cluster = 0;
+  int force_general = 0;  // route bf16 rows through the general (fp32-stage) kernel too
+  int2* side_pair = nullptr;  // [batch_max, side_cap] side lists of the bf16 kernel
+  int side_cap = 0;
+  unsigned long long* phase_clocks = nullptr;  // HS_PHASE_CLOCKS=1: per-row phase timestamps
   hs::Pool pool{};
   u64* greedy_partials = nullptr;
   float* gstage = nullptr;  // global stand-in for the on-chip row copy (very wide rows only)
@@ -118,6 +123,24 @@ bool make_plan(const hs_sampler* h, int vocab, Plan& p) {
   return true;
 }
 
+// Launch shape of the bf16 kernel: the smallest cluster whose CTAs can hold their slice of
+// raw bf16 bits next to the fixed work areas.
+bool make_plan16(const hs_sampler* h, int vocab, Plan& p) {
+  if (h->force_general) return false;
+  static const int sizes[4] = {1, 2, 4, 8};
+  for (int k = 0; k < 4; ++k) {
+    const int c = sizes[k];
+    if (h->force_cluster && c != h->force_cluster) continue;
+    const int slice = ((vocab + c - 1) / c + 7) & ~7;
+    const size_t smem = hs::layout16(c).stage + (size_t)slice * sizeof(uint16_t);
+    if (smem <= (size_t)h->smem_optin && slice <= hs::kMaxSliceElems) {
+      p = Plan{c, slice, smem, false};
+      return true;
+    }
+  }
+  return false;
+}
+
 int check_common(hs_sampler* h, const void* logits, int dtype, int batch, int vocab) {
   if (!h) return HS_ERR_INVALID;
   if (!logits && batch > 0) return fail(h, HS_ERR_INVALID, "logits is null");
@@ -132,8 +155,9 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
                 const hs_row_params* params, hs_row_out* out, const float* noise, float* scores_out,
                 uint32_t flags, cudaStream_t stream) {
   Plan plan;
-  if (!make_plan(h, vocab, plan)) return fail(h, HS_ERR_CAPACITY, "vocabulary too wide for the row kernel");
-  if (plan.global_stage) {
+  const bool bf16_path = dtype == HS_DTYPE_BF16 && make_plan16(h, vocab, plan);
+  if (!bf16_path && !make_plan(h, vocab, plan)) return fail(h, HS_ERR_CAPACITY, "vocabulary too wide for the row kernel");
+  if (!bf16_path && plan.global_stage) {
     const size_t need = (size_t)batch * plan.slice * plan.cluster;
     if (need > h->gstage_elems) return fail(h, HS_ERR_CAPACITY, "global stage too small for this batch x vocab");
   }
@@ -147,9 +171,8 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
   a.out = out;
   a.noise = noise;
   a.scores_out = scores_out;
-  a.gstage = plan.global_stage ? h->gstage : nullptr;
-  a.pool_ids = h->pool.ids;
-  a.pool_cnts = h->pool.cnts;
+  a.gstage = (!bf16_path && plan.global_stage) ? h->gstage : nullptr;
+  a.pool_pairs = h->pool.pairs;
   a.pool_n = h->pool.n;
   a.pool_pos = h->pool.pos;
   a.unique_cap = h->pool.unique_cap;
@@ -168,7 +191,12 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  HS_CUDA(h, cudaLaunchKernelEx(&cfg, hs::row_kernel, a));
+  if (bf16_path) {
+    hs::Row16Args a16{a, h->side_pair, h->side_cap, h->phase_clocks};
+    HS_CUDA(h, cudaLaunchKernelEx(&cfg, hs::row_kernel_bf16, a16));
+  } else {
+    HS_CUDA(h, cudaLaunchKernelEx(&cfg, hs::row_kernel, a));
+  }
   h->launches += 1;
   return HS_OK;
 }
@@ -203,7 +231,8 @@ int launch_append(hs_sampler* h, const int32_t* tokens, const int32_t* offsets, 
 }
 
 void release(hs_sampler* h) {
-  cudaFree(h->pool.ids); cudaFree(h->pool.cnts); cudaFree(h->pool.n); cudaFree(h->pool.pos);
+  cudaFree(h->pool.pairs); cudaFree(h->pool.n); cudaFree(h->pool.pos);
+  cudaFree(h->side_pair); cudaFree(h->phase_clocks);
   cudaFree(h->pool.error); cudaFree(h->greedy_partials); cudaFree(h->gstage); cudaFree(h->d_logits);
   cudaFree(h->d_params); cudaFree(h->d_out); cudaFree(h->d_hist); cudaFree(h->d_offsets); cudaFree(h->d_slots);
   if (h->h_params) cudaFreeHost(h->h_params);
@@ -252,14 +281,15 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   if (cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaDeviceGetAttribute(&h->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_optin) != cudaSuccess) return bail(HS_ERR_CUDA);
+  if (cudaFuncSetAttribute(hs::row_kernel_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_optin) != cudaSuccess) return bail(HS_ERR_CUDA);
+  if (const char* fg = std::getenv("HS_FORCE_GENERAL")) h->force_general = std::atoi(fg) != 0;
 
   const size_t st = (size_t)h->slots_total;
   h->pool.slots_total = h->slots_total;
   h->pool.unique_cap = h->unique_cap;
   h->pool.pos_stride = vocab_max;
   bool ok = true;
-  ok = ok && cudaMalloc(&h->pool.ids, st * h->unique_cap * sizeof(int32_t)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->pool.cnts, st * h->unique_cap * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->pool.pairs, st * h->unique_cap * sizeof(int2)) == cudaSuccess;
   ok = ok && cudaMalloc(&h->pool.n, st * sizeof(int32_t)) == cudaSuccess;
   ok = ok && cudaMalloc(&h->pool.pos, st * (size_t)vocab_max * sizeof(int32_t)) == cudaSuccess;
   ok = ok && cudaMalloc(&h->pool.error, sizeof(int32_t)) == cudaSuccess;
@@ -268,8 +298,17 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   ok = ok && cudaMalloc(&h->d_out, (size_t)batch_max * sizeof(hs_row_out)) == cudaSuccess;
   ok = ok && cudaMalloc(&h->d_offsets, ((size_t)batch_max + 1) * sizeof(int32_t)) == cudaSuccess;
   ok = ok && cudaMalloc(&h->d_slots, (size_t)batch_max * sizeof(int32_t)) == cudaSuccess;
+  h->side_cap = (vocab_max + 7) & ~7;
+  ok = ok && cudaMalloc(&h->side_pair, (size_t)batch_max * h->side_cap * sizeof(int2)) == cudaSuccess;
   ok = ok && cudaMallocHost(&h->h_params, (size_t)batch_max * sizeof(hs_row_params)) == cudaSuccess;
   ok = ok && cudaMallocHost(&h->h_small, (2 * (size_t)batch_max + 1) * sizeof(int32_t)) == cudaSuccess;
+  if (const char* pc = std::getenv("HS_PHASE_CLOCKS")) {
+    if (std::atoi(pc) != 0) {
+      const size_t bytes = (size_t)batch_max * hs::kPhaseSlots * sizeof(unsigned long long);
+      ok = ok && cudaMalloc(&h->phase_clocks, bytes) == cudaSuccess;
+      ok = ok && cudaMemset(h->phase_clocks, 0, bytes) == cudaSuccess;
+    }
+  }
   if (!ok) return bail(HS_ERR_CUDA);
   ok = ok && cudaMemset(h->pool.n, 0, st * sizeof(int32_t)) == cudaSuccess;
   ok = ok && cudaMemset(h->pool.pos, 0, st * (size_t)vocab_max * sizeof(int32_t)) == cudaSuccess;
@@ -438,13 +477,23 @@ int hs_sample_host(hs_sampler* h, const void* logits, int dtype, int64_t row_str
   return HS_OK;
 }
 
+int hs_debug_phase_clocks(hs_sampler* h, int batch, unsigned long long* out_host) {
+  if (!h || !out_host || batch < 0 || batch > h->batch_max) return HS_ERR_INVALID;
+  if (!h->phase_clocks) return fail(h, HS_ERR_UNSUPPORTED, "create the sampler with HS_PHASE_CLOCKS=1");
+  DeviceGuard guard(h->device);
+  HS_CUDA(h, cudaMemcpy(out_host, h->phase_clocks, (size_t)batch * hs::kPhaseSlots * sizeof(unsigned long long),
+                        cudaMemcpyDeviceToHost));
+  return HS_OK;
+}
+
 int hs_query(hs_sampler* h, int what, int vocab, int dtype) {
-  (void)dtype;
   if (!h) return HS_ERR_INVALID;
   Plan plan;
+  const bool bf16_path = dtype == HS_DTYPE_BF16 && make_plan16(h, vocab, plan);
   switch (what) {
-    case 0: return make_plan(h, vocab, plan) ? plan.cluster : HS_ERR_CAPACITY;
-    case 1: return make_plan(h, vocab, plan) ? (plan.global_stage ? 0 : 1) : HS_ERR_CAPACITY;
+    case 0: return (bf16_path || make_plan(h, vocab, plan)) ? plan.cluster : HS_ERR_CAPACITY;
+    case 1: return (bf16_path || make_plan(h, vocab, plan)) ? (plan.global_stage ? 0 : 1) : HS_ERR_CAPACITY;
+    case 4: return bf16_path ? 1 : 0;
     case 2: return h->sm_count;
     case 3: return (int)(h->launches & 0x7fffffffull);
     default: return HS_ERR_INVALID;

@@ -11,7 +11,7 @@ namespace cg = cooperative_groups;
 
 namespace hs {
 
-constexpr int kThreads = 1024;          // threads per CTA of the row kernel
+constexpr int kThreads = 512;           // threads per CTA of the row kernels (128 registers each: no spills)
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxCluster = 8;          // portable cluster limit
 constexpr int kBinBits = 11;            // radix digit of the first two select levels
@@ -112,7 +112,7 @@ __device__ __forceinline__ void block_sum2(Exchange& x, u64& a, u64& b) {
   __syncthreads();  // protects warp_a / warp_b against the previous reader
   if (lane == 0) { x.warp_a[warp] = a; x.warp_b[warp] = b; }
   __syncthreads();
-  u64 ta = x.warp_a[lane], tb = x.warp_b[lane];  // kWarps == 32
+  u64 ta = lane < kWarps ? x.warp_a[lane] : 0ull, tb = lane < kWarps ? x.warp_b[lane] : 0ull;
   a = warp_sum_u64(ta);
   b = warp_sum_u64(tb);
 }
@@ -122,7 +122,7 @@ __device__ __forceinline__ uint32_t block_max_u32(Exchange& x, uint32_t v) {
   __syncthreads();
   if (lane == 0) x.warp_a[warp] = v;
   __syncthreads();
-  return warp_max_u32((uint32_t)x.warp_a[lane]);
+  return warp_max_u32(lane < kWarps ? (uint32_t)x.warp_a[lane] : 0u);
 }
 __device__ __forceinline__ u64 block_max_u64(Exchange& x, u64 v) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -134,7 +134,7 @@ __device__ __forceinline__ u64 block_max_u64(Exchange& x, u64 v) {
   __syncthreads();
   if (lane == 0) x.warp_a[warp] = v;
   __syncthreads();
-  v = x.warp_a[lane];
+  v = lane < kWarps ? x.warp_a[lane] : 0ull;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     u64 t = __shfl_xor_sync(0xffffffffu, v, o);
@@ -150,8 +150,8 @@ __device__ __forceinline__ void block_warp_prefix2(Exchange& x, u64 wa, u64 wb, 
   __syncthreads();
   if (lane == 0) { x.warp_a[warp] = wa; x.warp_b[warp] = wb; }
   __syncthreads();
-  u64 ia = warp_scan_u64(x.warp_a[lane]);
-  u64 ib = warp_scan_u64(x.warp_b[lane]);
+  u64 ia = warp_scan_u64(lane < kWarps ? x.warp_a[lane] : 0ull);
+  u64 ib = warp_scan_u64(lane < kWarps ? x.warp_b[lane] : 0ull);
   tot_a = shfl_u64(ia, 31);
   tot_b = shfl_u64(ib, 31);
   u64 ea = shfl_u64(ia, warp) - x.warp_a[warp];
@@ -162,13 +162,11 @@ __device__ __forceinline__ void block_warp_prefix2(Exchange& x, u64 wa, u64 wb, 
 
 // ---- cluster primitives --------------------------------------------------------------
 // Every CTA of the cluster publishes up to four 64-bit values; all CTAs read all of
-// them.  One cluster barrier; the double-buffered ring makes a trailing barrier
-// unnecessary.  `vals` must be CTA-uniform.  out[rank][i].
+// them.  ring_publish, then any cluster-wide barrier, then ring_read.  The buffer is
+// double buffered, so no barrier is needed after the read.  `vals` must be CTA-uniform.
 template <int N>
-__device__ __forceinline__ void cluster_allgather(cg::cluster_group& cluster, Exchange& x,
-                                                  const u64 (&vals)[N], u64 (&out)[kMaxCluster][N]) {
+__device__ __forceinline__ uint32_t ring_publish(Exchange& x, const u64 (&vals)[N]) {
   static_assert(N <= 4, "ring holds four values");
-  const unsigned nranks = cluster.num_blocks();
   __syncthreads();
   const uint32_t phase = x.ring_phase & 1u;
   if (threadIdx.x == 0) {
@@ -176,14 +174,65 @@ __device__ __forceinline__ void cluster_allgather(cg::cluster_group& cluster, Ex
     for (int i = 0; i < N; ++i) x.ring[phase][i] = vals[i];
   }
   __syncthreads();
-  if (nranks > 1) cluster.sync();
+  if (threadIdx.x == 0) x.ring_phase = phase ^ 1u;
+  return phase;
+}
+template <int N>
+__device__ __forceinline__ void ring_read(cg::cluster_group& cluster, Exchange& x, uint32_t phase,
+                                          u64 (&out)[kMaxCluster][N]) {
+  const unsigned nranks = cluster.num_blocks();
   for (unsigned r = 0; r < nranks; ++r) {
     const Exchange* remote = nranks > 1 ? cluster.map_shared_rank(&x, r) : &x;
 #pragma unroll
     for (int i = 0; i < N; ++i) out[r][i] = remote->ring[phase][i];
   }
-  __syncthreads();
-  if (threadIdx.x == 0) x.ring_phase = phase ^ 1u;
+}
+// Reductions over the published values of all CTAs, read straight from the ring.
+enum class RingOp { Sum, Max, Min };
+template <RingOp OP>
+__device__ __forceinline__ u64 ring_reduce(cg::cluster_group& cluster, Exchange& x, uint32_t phase, int i) {
+  const unsigned nranks = cluster.num_blocks();
+  u64 acc = OP == RingOp::Min ? ~0ull : 0ull;
+#pragma unroll
+  for (unsigned r = 0; r < (unsigned)kMaxCluster; ++r) {
+    if (r >= nranks) break;
+    const Exchange* remote = nranks > 1 ? cluster.map_shared_rank(&x, r) : &x;
+    const u64 v = remote->ring[phase][i];
+    if (OP == RingOp::Sum) acc += v;
+    else if (OP == RingOp::Max) acc = v > acc ? v : acc;
+    else acc = v < acc ? v : acc;
+  }
+  return acc;
+}
+// Sum over the CTAs of rank < my_rank (exclusive prefix in rank order).
+__device__ __forceinline__ u64 ring_prefix(cg::cluster_group& cluster, Exchange& x, uint32_t phase, int i,
+                                           unsigned my_rank) {
+  const unsigned nranks = cluster.num_blocks();
+  u64 acc = 0;
+#pragma unroll
+  for (unsigned r = 0; r < (unsigned)kMaxCluster; ++r) {
+    if (r >= my_rank || r >= nranks) break;
+    const Exchange* remote = nranks > 1 ? cluster.map_shared_rank(&x, r) : &x;
+    acc += remote->ring[phase][i];
+  }
+  return acc;
+}
+// publish + one cluster barrier; returns the ring phase to reduce from.
+template <int N>
+__device__ __forceinline__ uint32_t cluster_publish(cg::cluster_group& cluster, Exchange& x,
+                                                    const u64 (&vals)[N]) {
+  const uint32_t phase = ring_publish<N>(x, vals);
+  if (cluster.num_blocks() > 1) cluster.sync();
+  return phase;
+}
+
+// publish + barrier + read in one call.  out[rank][i].
+template <int N>
+__device__ __forceinline__ void cluster_allgather(cg::cluster_group& cluster, Exchange& x,
+                                                  const u64 (&vals)[N], u64 (&out)[kMaxCluster][N]) {
+  const uint32_t phase = ring_publish<N>(x, vals);
+  if (cluster.num_blocks() > 1) cluster.sync();
+  ring_read<N>(cluster, x, phase, out);
 }
 
 }  // namespace hs

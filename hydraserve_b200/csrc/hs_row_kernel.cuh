@@ -21,6 +21,7 @@
 #pragma once
 
 #include "hs_common.cuh"
+#include "hs_select.cuh"
 #include "../../include/hs_sampler.h"
 
 namespace hs {
@@ -37,8 +38,7 @@ struct RowKernelArgs {
   float* scores_out;    // [batch, vocab] or null
   float* gstage;        // [batch, slice * cluster] global stage, or null = shared memory
   // token-count histogram pool
-  int32_t* pool_ids;
-  int32_t* pool_cnts;
+  int2* pool_pairs;     // [slots, unique_cap] (token id, count)
   int32_t* pool_n;
   int32_t* pool_pos;
   int unique_cap;
@@ -46,25 +46,7 @@ struct RowKernelArgs {
   uint32_t flags;
 };
 
-struct Hist {
-  uint32_t cnt[kBins];  // after the merge: full_cnt
-  uint32_t l0[kBins];   // after the merge: full_mass (u64) spans l0 and l1
-  uint32_t l1[kBins];
-  uint32_t l2[kBins];
-};
-
-struct Selection {
-  uint32_t key;
-  u64 above_cnt, above_mass;  // over elements with key > this key
-  u64 bin_cnt, bin_mass;      // over elements with key == this key
-  u64 total_cnt, total_mass;  // over all elements with key >= lo
-  u64 target;                 // the count / mass that was searched for
-  bool ok;
-};
-
-struct RowCtx {
-  cg::cluster_group cluster;
-  unsigned rank, nranks;
+struct RowCtx : ClusterCtx {
   int row;
   int vocab;
   int slice;
@@ -74,153 +56,42 @@ struct RowCtx {
   float* stage;  // this CTA's slice
   float* smem_stage;
   float* gstage_row;
-  Hist* hist;
-  uint32_t* red_cnt;
-  u64* red_mass;
-  Exchange* x;
 
-  __device__ __forceinline__ void sync_all() {
-    if (nranks > 1) cluster.sync(); else __syncthreads();
-  }
   __device__ __forceinline__ float* slice_of(unsigned r) {
     if (gstage_row) return gstage_row + (size_t)r * slice;
     return nranks > 1 ? cluster.map_shared_rank(smem_stage, r) : smem_stage;
   }
 };
 
-// Smallest integer mass A with float(A / total) > top_p, i.e. the cumulative mass at which
-// the reference's `cumulative > top_p` first becomes true (sampling.py:136).
-__device__ __forceinline__ u64 top_p_target(u64 total, float top_p) {
-  const double tot = (double)total;
-  const float up = __uint_as_float(__float_as_uint(top_p) + 1u);
-  const double mid = 0.5 * ((double)top_p + (double)up);
-  double guess = floor(mid * tot) - 2.0;
-  u64 a = guess < 1.0 ? 1ull : (u64)guess;
-  for (int i = 0; i < 8; ++i) {
-    if ((float)((double)a / tot) > top_p) break;
-    ++a;
+// Every element of the resident fp32 row, for descend_core.
+template <bool WITH_MASS>
+struct StageFill {
+  const float* stage;
+  int n_local;
+  float m;
+  template <class Add>
+  __device__ __forceinline__ void operator()(int level, int shift, int bits, uint32_t prefix,
+                                             uint32_t lo_key, const Add& add) const {
+    const uint32_t mask = (1u << bits) - 1u;
+    for (int i0 = threadIdx.x & ~31; i0 < n_local; i0 += kThreads) {
+      const int i = i0 + (threadIdx.x & 31);
+      bool valid = i < n_local;
+      float s = 0.f;
+      uint32_t k = 0;
+      if (valid) {
+        s = stage[i];
+        k = key_of(s);
+        valid = k >= lo_key && (level == 0 || (k >> (shift + bits)) == prefix);
+      }
+      add(valid, (k >> shift) & mask, 1u, (WITH_MASS && valid) ? mass_of(s, m) : 0ull);
+    }
   }
-  if (a > total) a = total;
-  if (a < 1) a = 1;
-  return a;
-}
+};
 
-// Radix descent over the resident row: finds the key at which, walking scores downwards
-// from the top, the running count (BY_MASS = false) or probability mass (BY_MASS = true)
-// first reaches the target.  Only elements with key >= lo_key take part.
 template <bool BY_MASS, bool WITH_MASS>
 __device__ Selection descend(RowCtx& c, uint32_t lo_key, u64 target_cnt, float top_p, float m) {
-  static_assert(WITH_MASS || !BY_MASS, "a mass descent needs masses");
-  Hist& h = *c.hist;
-  u64* full_mass = reinterpret_cast<u64*>(h.l0);
-  uint32_t* full_cnt = h.cnt;
-  Selection sel;
-  sel.above_cnt = sel.above_mass = 0;
-  sel.total_cnt = sel.total_mass = 0;
-  sel.target = target_cnt;
-  sel.ok = true;
-  uint32_t prefix = 0;
-  const int per = kBins / (int)c.nranks;
-  const int tid = threadIdx.x;
-
-  for (int level = 0; level < 3; ++level) {
-    const int shift = level == 0 ? 21 : (level == 1 ? 10 : 0);
-    const int bits = level < 2 ? 11 : 10;
-    const uint32_t mask = (1u << bits) - 1u;
-    for (int b = tid; b < kBins; b += kThreads) {
-      h.cnt[b] = 0;
-      if (WITH_MASS) { h.l0[b] = 0; h.l1[b] = 0; h.l2[b] = 0; }
-    }
-    __syncthreads();
-    for (int i = tid; i < c.n_local; i += kThreads) {
-      const float s = c.stage[i];
-      const uint32_t k = key_of(s);
-      if (k < lo_key) continue;
-      if (level > 0 && (k >> (shift + bits)) != prefix) continue;
-      const uint32_t bin = (k >> shift) & mask;
-      atomicAdd(&h.cnt[bin], 1u);
-      if (WITH_MASS) {
-        const u64 q = mass_of(s, m);
-        if (q) {
-          atomicAdd(&h.l0[bin], (uint32_t)q & kLimbMask);
-          atomicAdd(&h.l1[bin], (uint32_t)(q >> kLimbBits) & kLimbMask);
-          atomicAdd(&h.l2[bin], (uint32_t)(q >> (2 * kLimbBits)));
-        }
-      }
-    }
-    c.sync_all();
-    // reduce-scatter: this CTA sums bins [rank*per, (rank+1)*per) over the cluster
-    for (int b = tid; b < per; b += kThreads) {
-      const int gb = (int)c.rank * per + b;
-      uint32_t cn = 0;
-      u64 ms = 0;
-      for (unsigned r = 0; r < c.nranks; ++r) {
-        const Hist* rh = c.nranks > 1 ? c.cluster.map_shared_rank(c.hist, r) : c.hist;
-        cn += rh->cnt[gb];
-        if (WITH_MASS)
-          ms += (u64)rh->l0[gb] + ((u64)rh->l1[gb] << kLimbBits) + ((u64)rh->l2[gb] << (2 * kLimbBits));
-      }
-      c.red_cnt[b] = cn;
-      c.red_mass[b] = ms;
-    }
-    c.sync_all();
-    // all-gather the merged bins into this CTA (over the now unused local arrays)
-    for (int gb = tid; gb < kBins; gb += kThreads) {
-      const unsigned r = (unsigned)(gb / per);
-      const int b = gb - (int)r * per;
-      const uint32_t* rc = c.nranks > 1 ? c.cluster.map_shared_rank(c.red_cnt, r) : c.red_cnt;
-      const u64* rm = c.nranks > 1 ? c.cluster.map_shared_rank(c.red_mass, r) : c.red_mass;
-      full_cnt[gb] = rc[b];
-      full_mass[gb] = WITH_MASS ? rm[b] : 0ull;
-    }
-    if (tid == 0) c.x->bcast[7] = 0;
-    __syncthreads();
-    // scan bins from the top: thread t owns bins hi = kBins-1-2t and hi-1
-    const int hi = kBins - 1 - 2 * tid;
-    const u64 c_hi = full_cnt[hi], c_lo = full_cnt[hi - 1];
-    const u64 m_hi = full_mass[hi], m_lo = full_mass[hi - 1];
-    u64 ia = warp_scan_u64(c_hi + c_lo);
-    u64 ib = warp_scan_u64(m_hi + m_lo);
-    u64 pa, pb, ta, tb;
-    block_warp_prefix2(*c.x, shfl_u64(ia, 31), shfl_u64(ib, 31), pa, pb, ta, tb);
-    const u64 ex_cnt = pa + ia - (c_hi + c_lo);   // exclusive prefix over bins above `hi`
-    const u64 ex_mass = pb + ib - (m_hi + m_lo);
-    if (level == 0) {
-      sel.total_cnt = ta;
-      sel.total_mass = tb;
-      if (BY_MASS) sel.target = top_p_target(tb, top_p);
-    }
-    const u64 want = sel.target - (BY_MASS ? sel.above_mass : sel.above_cnt);
-    const u64 ex = BY_MASS ? ex_mass : ex_cnt;
-    const u64 v_hi = BY_MASS ? m_hi : c_hi;
-    const u64 v_lo = BY_MASS ? m_lo : c_lo;
-    if (ex < want && want <= ex + v_hi + v_lo) {
-      const bool first = want <= ex + v_hi;
-      c.x->bcast[0] = (u64)(first ? hi : hi - 1);
-      c.x->bcast[1] = ex_cnt + (first ? 0 : c_hi);
-      c.x->bcast[2] = ex_mass + (first ? 0 : m_hi);
-      c.x->bcast[3] = first ? c_hi : c_lo;
-      c.x->bcast[4] = first ? m_hi : m_lo;
-      c.x->bcast[7] = 1;
-    }
-    __syncthreads();
-    if (c.x->bcast[7] == 0) {  // nothing reaches the target (non-finite input)
-      sel.ok = false;
-      sel.key = lo_key;
-      sel.bin_cnt = sel.bin_mass = 0;
-      __syncthreads();
-      return sel;
-    }
-    const uint32_t bin = (uint32_t)c.x->bcast[0];
-    sel.above_cnt += c.x->bcast[1];
-    sel.above_mass += c.x->bcast[2];
-    sel.bin_cnt = c.x->bcast[3];
-    sel.bin_mass = c.x->bcast[4];
-    prefix = (prefix << bits) | bin;
-    __syncthreads();  // bcast and the aliased arrays are reused by the next level
-  }
-  sel.key = prefix;
-  return sel;
+  StageFill<WITH_MASS> fill{c.stage, c.n_local, m};
+  return descend_core<BY_MASS, WITH_MASS>(c, fill, lo_key, target_cnt, top_p);
 }
 
 // Count and mass of all elements with key >= lo_key, cluster wide.
@@ -438,7 +309,7 @@ __device__ void write_top_logprobs(RowCtx& c, const KeptSet& kept, uint32_t key_
 
 __global__ void __launch_bounds__(kThreads, 1) row_kernel(const RowKernelArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  RowCtx c{cg::this_cluster()};
+  RowCtx c{{cg::this_cluster()}};
   c.rank = c.cluster.block_rank();
   c.nranks = c.cluster.num_blocks();
   c.row = blockIdx.y;
@@ -510,17 +381,17 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel(const RowKernelArgs a)
                                           P.frequency_penalty != 0.0f);
   if (penalised) {
     const int n_unique = a.pool_n[P.slot];
-    const int32_t* ids = a.pool_ids + (size_t)P.slot * a.unique_cap;
-    const int32_t* cnts = a.pool_cnts + (size_t)P.slot * a.unique_cap;
+    const int2* pairs = a.pool_pairs + (size_t)P.slot * a.unique_cap;
     for (int j = (int)c.rank * kThreads + tid; j < n_unique; j += (int)c.nranks * kThreads) {
-      const int id = ids[j];
+      const int2 e = pairs[j];
+      const int id = e.x;
       if (id < 0 || id >= a.vocab) continue;
       const unsigned r = (unsigned)(id / a.slice);
       float* p = c.slice_of(r) + (id - (int)r * a.slice);
       float v = *p;
       v = v < 0.0f ? __fmul_rn(v, P.repetition_penalty) : __fdiv_rn(v, P.repetition_penalty);
       v = __fsub_rn(v, P.presence_penalty);
-      v = __fsub_rn(v, __fmul_rn(P.frequency_penalty, (float)cnts[j]));
+      v = __fsub_rn(v, __fmul_rn(P.frequency_penalty, (float)e.y));
       *p = canonical(v);
     }
     if (c.gstage_row) __threadfence();
@@ -686,16 +557,14 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel(const RowKernelArgs a)
     out->log_z = log_z;
     if ((a.flags & HS_SAMPLE_APPEND_TOKEN) && P.slot >= 0 && token >= 0 && token < a.vocab) {
       int32_t* pos = a.pool_pos + (size_t)P.slot * a.pos_stride;
-      int32_t* ids = a.pool_ids + (size_t)P.slot * a.unique_cap;
-      int32_t* cnts = a.pool_cnts + (size_t)P.slot * a.unique_cap;
+      int2* pairs = a.pool_pairs + (size_t)P.slot * a.unique_cap;
       const int p = pos[token];
       if (p > 0) {
-        cnts[p - 1] += 1;
+        pairs[p - 1].y += 1;
       } else {
         const int n = a.pool_n[P.slot];
         if (n < a.unique_cap) {
-          ids[n] = token;
-          cnts[n] = 1;
+          pairs[n] = make_int2(token, 1);
           pos[token] = n + 1;
           a.pool_n[P.slot] = n + 1;
         } else {

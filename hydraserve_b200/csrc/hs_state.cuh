@@ -3,9 +3,9 @@
 //
 // A slot holds the sparse form of the `counts` dict the reference builds per row per step
 // (sampling.py:106-110): parallel lists ids[] / cnts[] of the distinct token ids seen so
-// far, plus a dense index pos[token] = 1 + position in the lists (0 = unseen) that is
-// touched only when tokens are appended.  The sampling kernel reads just the lists
-// (8 bytes per distinct id, coalesced).
+// far, stored as (id, count) pairs, plus a dense index pos[token] = 1 + position in the
+// list (0 = unseen) that is touched only when tokens are appended.  The sampling kernel
+// reads just the list (8 bytes per distinct id, coalesced).
 #pragma once
 
 #include "hs_common.cuh"
@@ -14,8 +14,7 @@
 namespace hs {
 
 struct Pool {
-  int32_t* ids;    // [slots_total, unique_cap]
-  int32_t* cnts;   // [slots_total, unique_cap]
+  int2* pairs;     // [slots_total, unique_cap] (token id, count)
   int32_t* n;      // [slots_total]
   int32_t* pos;    // [slots_total, pos_stride]
   int32_t* error;  // [1] sticky: 1 = a slot overflowed unique_cap
@@ -29,10 +28,10 @@ __global__ void slots_reset_kernel(Pool p, const int32_t* slots, int n_slots) {
   const int s = blockIdx.x < n_slots ? slots[blockIdx.x] : -1;
   if (s < 0 || s >= p.slots_total) return;
   const int n = min(p.n[s], p.unique_cap);
-  const int32_t* ids = p.ids + (size_t)s * p.unique_cap;
+  const int2* pairs = p.pairs + (size_t)s * p.unique_cap;
   int32_t* pos = p.pos + (size_t)s * p.pos_stride;
   for (int j = threadIdx.x; j < n; j += blockDim.x) {
-    const int id = ids[j];
+    const int id = pairs[j].x;
     if (id >= 0 && id < p.pos_stride) pos[id] = 0;
   }
   __syncthreads();
@@ -46,8 +45,7 @@ __global__ void slots_register_kernel(Pool p, const int32_t* tokens, const int32
   const int s = row < n_slots ? slots[row] : -1;
   if (s < 0 || s >= p.slots_total) return;
   const int t0 = offsets[row], t1 = offsets[row + 1];
-  int32_t* ids = p.ids + (size_t)s * p.unique_cap;
-  int32_t* cnts = p.cnts + (size_t)s * p.unique_cap;
+  int2* pairs = p.pairs + (size_t)s * p.unique_cap;
   int32_t* pos = p.pos + (size_t)s * p.pos_stride;
   for (int j = t0 + blockIdx.x * blockDim.x + threadIdx.x; j < t1; j += gridDim.x * blockDim.x) {
     const int t = tokens[j];
@@ -55,8 +53,7 @@ __global__ void slots_register_kernel(Pool p, const int32_t* tokens, const int32
     if (atomicCAS(&pos[t], 0, -1) == 0) {
       const int idx = atomicAdd(&p.n[s], 1);
       if (idx < p.unique_cap) {
-        ids[idx] = t;
-        cnts[idx] = 0;
+        pairs[idx] = make_int2(t, 0);
         pos[t] = idx + 1;
       } else {
         atomicSub(&p.n[s], 1);
@@ -74,13 +71,13 @@ __global__ void slots_count_kernel(Pool p, const int32_t* tokens, const int32_t*
   const int s = row < n_slots ? slots[row] : -1;
   if (s < 0 || s >= p.slots_total) return;
   const int t0 = offsets[row], t1 = offsets[row + 1];
-  int32_t* cnts = p.cnts + (size_t)s * p.unique_cap;
+  int2* pairs = p.pairs + (size_t)s * p.unique_cap;
   const int32_t* pos = p.pos + (size_t)s * p.pos_stride;
   for (int j = t0 + blockIdx.x * blockDim.x + threadIdx.x; j < t1; j += gridDim.x * blockDim.x) {
     const int t = tokens[j];
     if (t < 0 || t >= vocab || t >= p.pos_stride) continue;
     const int q = pos[t];
-    if (q > 0) atomicAdd(&cnts[q - 1], 1);
+    if (q > 0) atomicAdd(&pairs[q - 1].y, 1);
   }
 }
 

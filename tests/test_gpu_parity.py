@@ -98,6 +98,33 @@ def test_rows_match_checker(sampler, name):
     report.assert_ok(max_sensitive_fraction=0.5)
 
 
+@pytest.fixture(scope="module")
+def general_sampler(built_library):
+    """A sampler that sends bf16 rows through the general (fp32-resident) kernel as well."""
+    import os
+
+    from hydraserve_b200.engine import _device
+
+    os.environ["HS_FORCE_GENERAL"] = "1"
+    try:
+        s = _device.DeviceSampler("cuda:0", vocab_max=250_000, batch_max=64, resident_slots=8)
+    finally:
+        del os.environ["HS_FORCE_GENERAL"]
+    assert s.query(4, 151_936) == 0
+    yield s
+    s.close()
+
+
+@pytest.mark.parametrize("name", [n for n in PARITY_CASES if "bf16" in n or n.startswith("config")])
+def test_bf16_rows_match_checker_on_the_general_kernel(general_sampler, name):
+    compare_case(general_sampler, cases.build(name)).assert_ok(max_sensitive_fraction=0.5)
+
+
+def test_bf16_kernel_is_the_one_used_for_bf16(sampler):
+    assert sampler.query(4, 151_936, 1) == 1 and sampler.query(4, 248_320, 1) == 1
+    assert sampler.query(4, 151_936, 0) == 0
+
+
 def test_penalised_logits_bit_exact(sampler):
     """Greedy rows dump the penalised logits themselves (no temperature, no filter)."""
     from hydraserve_b200.engine.sampling import SamplingParams
@@ -182,7 +209,7 @@ def test_global_stage_fallback_for_very_wide_rows(sampler):
     from hydraserve_b200.workloads import Workload
 
     vocab = 410_001
-    assert sampler.query(1, vocab) == 0 and sampler.query(1, 248_320) == 1
+    assert sampler.query(1, vocab, 0) == 0 and sampler.query(1, 248_320, 0) == 1
     rng = np.random.default_rng(9)
     x = (rng.standard_normal((3, vocab)) * 3).astype(np.float32)
     params = [SamplingParams(logprobs=5, presence_penalty=0.5),
