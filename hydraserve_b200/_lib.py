@@ -16,6 +16,7 @@ HS_MAX_LOGPROBS = 20
 HS_DTYPE_F32, HS_DTYPE_BF16 = 0, 1
 HS_ROW_PLAIN_GREEDY = 1
 HS_SAMPLE_APPEND_TOKEN = 1
+HS_NOALLOC_MAX_BATCH = 1024
 
 # Mirrors of struct hs_row_params / hs_row_out (natural C alignment, no padding needed).
 ROW_PARAMS = np.dtype([
@@ -46,6 +47,8 @@ EXPORTS = {
                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "hs_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_void_p,
                             C.c_void_p]),
+    "hs_greedy_noalloc": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "hs_greedy_noalloc_error": (C.c_char_p, []),
     "hs_sample_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int,
                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "hs_query": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int]),

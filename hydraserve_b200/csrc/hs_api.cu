@@ -241,7 +241,86 @@ void release(hs_sampler* h) {
 
 }  // namespace
 
+// ---- hs_greedy_noalloc: arg max per row with its scratch in a fixed device array --------
+namespace {
+
+constexpr int kNoAllocMaxBatch = HS_NOALLOC_MAX_BATCH;
+constexpr int kNoAllocChunks = 16;
+constexpr int kNoAllocMaxDevices = 64;
+
+// One partial result per (row, chunk).  Every GPU that loads this library holds these
+// 128 KB until the process exits.  In host code this name is only a handle for
+// cudaGetSymbolAddress; kernels get the device address obtained from it.
+static __device__ __align__(256) unsigned long long g_noalloc_partials[kNoAllocMaxBatch * kNoAllocChunks];
+
+struct NoAllocDevice {
+  u64* partials = nullptr;  // device address of g_noalloc_partials on that GPU
+  bool ready = false;
+};
+NoAllocDevice g_noalloc_devices[kNoAllocMaxDevices];
+std::mutex g_noalloc_mu;
+thread_local char g_noalloc_error[256] = "";
+
+int noalloc_fail(int code, const char* what, cudaError_t e = cudaSuccess) {
+  if (e != cudaSuccess)
+    std::snprintf(g_noalloc_error, sizeof g_noalloc_error, "%s: %s", what, cudaGetErrorString(e));
+  else
+    std::snprintf(g_noalloc_error, sizeof g_noalloc_error, "%s", what);
+  return code;
+}
+
+}  // namespace
+
 extern "C" {
+
+const char* hs_greedy_noalloc_error(void) { return g_noalloc_error; }
+
+int hs_greedy_noalloc(const void* logits, int dtype, int64_t row_stride, int batch, int vocab,
+                      int32_t* tokens_out, void* stream_) {
+  g_noalloc_error[0] = 0;
+  if (dtype != HS_DTYPE_F32 && dtype != HS_DTYPE_BF16) return noalloc_fail(HS_ERR_INVALID, "unknown dtype");
+  if (batch < 0 || vocab < 1) return noalloc_fail(HS_ERR_INVALID, "batch must be >= 0 and vocab >= 1");
+  if (batch > kNoAllocMaxBatch) {
+    std::snprintf(g_noalloc_error, sizeof g_noalloc_error,
+                  "batch %d exceeds HS_NOALLOC_MAX_BATCH (%d): split the call", batch, kNoAllocMaxBatch);
+    return HS_ERR_CAPACITY;
+  }
+  if (batch == 0) return HS_OK;
+  if (!logits || !tokens_out) return noalloc_fail(HS_ERR_INVALID, "logits / tokens_out is null");
+  if (row_stride < vocab) return noalloc_fail(HS_ERR_INVALID, "row_stride smaller than vocab");
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return noalloc_fail(HS_ERR_CUDA, "cudaGetDevice", e);
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return noalloc_fail(HS_ERR_CAPACITY, "device index beyond 63");
+  u64* partials = nullptr;
+  {
+    // Set-up, once per device, with that device current: resolve the array's device address.
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    NoAllocDevice& d = g_noalloc_devices[dev];
+    if (!d.ready) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_partials);
+      if (e != cudaSuccess) return noalloc_fail(HS_ERR_CUDA, "cudaGetSymbolAddress(g_noalloc_partials)", e);
+      d.partials = static_cast<u64*>(p);
+      d.ready = true;
+    }
+    partials = d.partials;
+  }
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int chunks = kNoAllocChunks;
+  int chunk = ((vocab + chunks - 1) / chunks + 7) & ~7;
+  chunks = (vocab + chunk - 1) / chunk;
+  // Every (row, chunk) slot that the final kernel reads is written by the partial kernel of
+  // the same call, so nothing left over from an earlier call needs clearing.
+  hs::greedy_partial_kernel<<<dim3((unsigned)chunks, (unsigned)batch), hs::kGreedyThreads, 0, stream>>>(
+      logits, dtype, row_stride, vocab, chunk, partials);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return noalloc_fail(HS_ERR_CUDA, "greedy_partial_kernel launch", e);
+  hs::greedy_final_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(partials, chunks, batch, tokens_out);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return noalloc_fail(HS_ERR_CUDA, "greedy_final_kernel launch", e);
+  return HS_OK;
+}
 
 int hs_abi_version(void) { return 1; }
 

@@ -109,6 +109,28 @@ int hs_sample(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, 
 int hs_greedy(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch,
               int vocab, int32_t* tokens_out, void* stream);
 
+/* No counterpart in the reference.  hs_greedy for callers that must not allocate device
+ * memory: a serving worker that has handed all of the GPU's memory to its framework's
+ * caching allocator (a raw cudaMalloc can fail there), or a step on the latency-critical
+ * decode path, where the device-wide synchronisation that cudaMalloc and cudaFree imply is
+ * not acceptable.  It needs no hs_sampler: it runs on the CURRENT device, calls no
+ * cudaMalloc / cudaFree / allocating library routine, and keeps its per-row partial results
+ * in a fixed 128 KB device array inside the library (each GPU that loads the library holds
+ * that array until the process exits).  Limits and rules:
+ *   - batch <= HS_NOALLOC_MAX_BATCH; a larger batch is refused with HS_ERR_CAPACITY and a
+ *     message from hs_greedy_noalloc_error() (split the call);
+ *   - the first call on each device resolves the array's address (once per device, under a
+ *     lock); make that first call before any stream capture;
+ *   - all calls on one GPU share the array: two calls whose kernels can overlap on the GPU
+ *     (different streams, no ordering) race.  Calls on one stream are fine.  Nothing needs to
+ *     start at zero: every slot a call reads is written by that same call.
+ * Results are identical to hs_greedy (lowest id on ties). */
+#define HS_NOALLOC_MAX_BATCH 1024
+int hs_greedy_noalloc(const void* logits, int dtype, int64_t row_stride, int batch, int vocab,
+                      int32_t* tokens_out, void* stream);
+/* Message for the calling thread's last failed hs_greedy_noalloc ("" after a success). */
+const char* hs_greedy_noalloc_error(void);
+
 /* Same as hs_sample but every pointer is a HOST pointer; copies in and out on `stream`
  * through pinned staging buffers owned by the sampler and synchronises before returning.
  * hist_tokens/hist_offsets: flat per-row histories (offsets has batch+1 entries), or NULL;
