@@ -13,9 +13,10 @@
 
 #include "../../include/hs_sampler.h"
 #include "hs_common.cuh"
+#include "hs_state.cuh"
 #include "hs_row_kernel.cuh"
 #include "hs_row_bf16.cuh"
-#include "hs_state.cuh"
+#include "hs_row_v3.cuh"
 
 namespace {
 
@@ -61,6 +62,7 @@ struct hs_sampler {
   int smem_optin = 0;
   int force_cluster = 0;
   int force_general = 0;  // route bf16 rows through the general (fp32-stage) kernel too
+  int force_cluster16 = 0;  // route bf16 rows through the cluster-resident bf16 kernel
   int2* side_pair = nullptr;  // [batch_max, side_cap] side lists of the bf16 kernel
   int side_cap = 0;
   unsigned long long* phase_clocks = nullptr;  // HS_PHASE_CLOCKS=1: per-row phase timestamps
@@ -155,6 +157,18 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
                 const hs_row_params* params, hs_row_out* out, const float* noise, float* scores_out,
                 uint32_t flags, cudaStream_t stream) {
   Plan plan;
+  if (dtype == HS_DTYPE_BF16 && !h->force_general && !h->force_cluster16) {
+    // one CTA per row, two CTAs per SM
+    hs::RowKernelArgs a{};
+    a.logits = logits; a.dtype = dtype; a.row_stride = row_stride; a.vocab = vocab; a.slice = 0;
+    a.params = params; a.out = out; a.noise = noise; a.scores_out = scores_out; a.gstage = nullptr;
+    a.pool = h->pool; a.flags = flags;
+    hs::RowV3Args a3{a, h->side_pair, h->side_cap, h->phase_clocks};
+    hs::row_kernel_v3<<<(unsigned)batch, hs::kThreads, hs::layout_v3().total, stream>>>(a3);
+    HS_CUDA(h, cudaGetLastError());
+    h->launches += 1;
+    return HS_OK;
+  }
   const bool bf16_path = dtype == HS_DTYPE_BF16 && make_plan16(h, vocab, plan);
   if (!bf16_path && !make_plan(h, vocab, plan)) return fail(h, HS_ERR_CAPACITY, "vocabulary too wide for the row kernel");
   if (!bf16_path && plan.global_stage) {
@@ -172,11 +186,7 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
   a.noise = noise;
   a.scores_out = scores_out;
   a.gstage = (!bf16_path && plan.global_stage) ? h->gstage : nullptr;
-  a.pool_pairs = h->pool.pairs;
-  a.pool_n = h->pool.n;
-  a.pool_pos = h->pool.pos;
-  a.unique_cap = h->pool.unique_cap;
-  a.pos_stride = h->pool.pos_stride;
+  a.pool = h->pool;
   a.flags = flags;
 
   cudaLaunchConfig_t cfg{};
@@ -226,12 +236,14 @@ int launch_append(hs_sampler* h, const int32_t* tokens, const int32_t* offsets, 
   HS_CUDA(h, cudaGetLastError());
   hs::slots_count_kernel<<<grid, threads, 0, stream>>>(h->pool, tokens, offsets, slots, n_slots, vocab);
   HS_CUDA(h, cudaGetLastError());
-  h->launches += 2;
+  hs::slots_classify_kernel<<<grid, threads, 0, stream>>>(h->pool, tokens, offsets, slots, n_slots, vocab);
+  HS_CUDA(h, cudaGetLastError());
+  h->launches += 3;
   return HS_OK;
 }
 
 void release(hs_sampler* h) {
-  cudaFree(h->pool.pairs); cudaFree(h->pool.n); cudaFree(h->pool.pos);
+  cudaFree(h->pool.pairs); cudaFree(h->pool.cls); cudaFree(h->pool.heavy); cudaFree(h->pool.n_heavy); cudaFree(h->pool.n); cudaFree(h->pool.pos);
   cudaFree(h->side_pair); cudaFree(h->phase_clocks);
   cudaFree(h->pool.error); cudaFree(h->greedy_partials); cudaFree(h->gstage); cudaFree(h->d_logits);
   cudaFree(h->d_params); cudaFree(h->d_out); cudaFree(h->d_hist); cudaFree(h->d_offsets); cudaFree(h->d_slots);
@@ -361,15 +373,21 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   if (cudaDeviceGetAttribute(&h->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_optin) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::row_kernel_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_optin) != cudaSuccess) return bail(HS_ERR_CUDA);
+  if (cudaFuncSetAttribute(hs::row_kernel_v3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_v3().total) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (const char* fg = std::getenv("HS_FORCE_GENERAL")) h->force_general = std::atoi(fg) != 0;
+  if (const char* fc16 = std::getenv("HS_FORCE_CLUSTER16")) h->force_cluster16 = std::atoi(fc16) != 0;
 
   const size_t st = (size_t)h->slots_total;
   h->pool.slots_total = h->slots_total;
   h->pool.unique_cap = h->unique_cap;
   h->pool.pos_stride = vocab_max;
+  h->pool.cls_stride = (vocab_max + 15) / 16 + 4;  // words; padded so 128-bit reads of the tail stay inside
   bool ok = true;
   ok = ok && cudaMalloc(&h->pool.pairs, st * h->unique_cap * sizeof(int2)) == cudaSuccess;
   ok = ok && cudaMalloc(&h->pool.n, st * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->pool.n_heavy, st * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->pool.heavy, st * h->unique_cap * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->pool.cls, st * (size_t)h->pool.cls_stride * sizeof(uint32_t)) == cudaSuccess;
   ok = ok && cudaMalloc(&h->pool.pos, st * (size_t)vocab_max * sizeof(int32_t)) == cudaSuccess;
   ok = ok && cudaMalloc(&h->pool.error, sizeof(int32_t)) == cudaSuccess;
   ok = ok && cudaMalloc(&h->greedy_partials, (size_t)batch_max * kGreedyMaxChunks * sizeof(u64)) == cudaSuccess;
@@ -390,6 +408,8 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   }
   if (!ok) return bail(HS_ERR_CUDA);
   ok = ok && cudaMemset(h->pool.n, 0, st * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMemset(h->pool.n_heavy, 0, st * sizeof(int32_t)) == cudaSuccess;
+  ok = ok && cudaMemset(h->pool.cls, 0, st * (size_t)h->pool.cls_stride * sizeof(uint32_t)) == cudaSuccess;
   ok = ok && cudaMemset(h->pool.pos, 0, st * (size_t)vocab_max * sizeof(int32_t)) == cudaSuccess;
   ok = ok && cudaMemset(h->pool.error, 0, sizeof(int32_t)) == cudaSuccess;
   if (!ok) return bail(HS_ERR_CUDA);
@@ -568,11 +588,12 @@ int hs_debug_phase_clocks(hs_sampler* h, int batch, unsigned long long* out_host
 int hs_query(hs_sampler* h, int what, int vocab, int dtype) {
   if (!h) return HS_ERR_INVALID;
   Plan plan;
-  const bool bf16_path = dtype == HS_DTYPE_BF16 && make_plan16(h, vocab, plan);
+  const bool v3 = dtype == HS_DTYPE_BF16 && !h->force_general && !h->force_cluster16;
+  const bool bf16_path = !v3 && dtype == HS_DTYPE_BF16 && make_plan16(h, vocab, plan);
   switch (what) {
-    case 0: return (bf16_path || make_plan(h, vocab, plan)) ? plan.cluster : HS_ERR_CAPACITY;
-    case 1: return (bf16_path || make_plan(h, vocab, plan)) ? (plan.global_stage ? 0 : 1) : HS_ERR_CAPACITY;
-    case 4: return bf16_path ? 1 : 0;
+    case 0: return v3 ? 1 : ((bf16_path || make_plan(h, vocab, plan)) ? plan.cluster : HS_ERR_CAPACITY);
+    case 1: return v3 ? 0 : ((bf16_path || make_plan(h, vocab, plan)) ? (plan.global_stage ? 0 : 1) : HS_ERR_CAPACITY);
+    case 4: return v3 ? 2 : (bf16_path ? 1 : 0);
     case 2: return h->sm_count;
     case 3: return (int)(h->launches & 0x7fffffffull);
     default: return HS_ERR_INVALID;

@@ -582,8 +582,8 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_bf16(const Row16Args a
   int n_listed = 0;
   u64 side_best = 0;  // (key << 32 | ~id) of the best S element this thread has seen
   if (penalised) {
-    n_listed = min(a.pool_n[P.slot], args.s_cap);
-    const int2* pairs = a.pool_pairs + (size_t)P.slot * a.unique_cap;  // (token id, count)
+    n_listed = min(min(a.pool.n[P.slot], a.pool.unique_cap), args.s_cap);
+    const int2* pairs = a.pool.pairs + (size_t)P.slot * a.pool.unique_cap;  // (token id, count)
     for (int j0 = tid; j0 < n_listed; j0 += 8 * kThreads) {
       int2 e[8];
 #pragma unroll
@@ -1002,21 +1002,7 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_bf16(const Row16Args a
     out->row_max = m;
     out->log_z = log_z;
     if ((a.flags & HS_SAMPLE_APPEND_TOKEN) && P.slot >= 0 && token >= 0 && token < a.vocab) {
-      int32_t* pos = a.pool_pos + (size_t)P.slot * a.pos_stride;
-      int2* pairs = a.pool_pairs + (size_t)P.slot * a.unique_cap;
-      const int p = pos[token];
-      if (p > 0) {
-        pairs[p - 1].y += 1;
-      } else {
-        const int n = a.pool_n[P.slot];
-        if (n < a.unique_cap) {
-          pairs[n] = make_int2(token, 1);
-          pos[token] = n + 1;
-          a.pool_n[P.slot] = n + 1;
-        } else {
-          out->status = status | 2;
-        }
-      }
+      if (!slot_append_one(a.pool, P.slot, token)) out->status = status | 2;
     }
   }
   // No CTA may leave while a peer can still read its shared memory.

@@ -22,6 +22,7 @@
 
 #include "hs_common.cuh"
 #include "hs_select.cuh"
+#include "hs_state.cuh"
 #include "../../include/hs_sampler.h"
 
 namespace hs {
@@ -37,12 +38,7 @@ struct RowKernelArgs {
   const float* noise;   // [batch, vocab] or null
   float* scores_out;    // [batch, vocab] or null
   float* gstage;        // [batch, slice * cluster] global stage, or null = shared memory
-  // token-count histogram pool
-  int2* pool_pairs;     // [slots, unique_cap] (token id, count)
-  int32_t* pool_n;
-  int32_t* pool_pos;
-  int unique_cap;
-  long long pos_stride;
+  Pool pool;            // token-count histograms
   uint32_t flags;
 };
 
@@ -380,8 +376,8 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel(const RowKernelArgs a)
   const bool penalised = P.slot >= 0 && (P.repetition_penalty != 1.0f || P.presence_penalty != 0.0f ||
                                           P.frequency_penalty != 0.0f);
   if (penalised) {
-    const int n_unique = a.pool_n[P.slot];
-    const int2* pairs = a.pool_pairs + (size_t)P.slot * a.unique_cap;
+    const int n_unique = min(a.pool.n[P.slot], a.pool.unique_cap);
+    const int2* pairs = a.pool.pairs + (size_t)P.slot * a.pool.unique_cap;
     for (int j = (int)c.rank * kThreads + tid; j < n_unique; j += (int)c.nranks * kThreads) {
       const int2 e = pairs[j];
       const int id = e.x;
@@ -556,21 +552,7 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel(const RowKernelArgs a)
     out->row_max = m;
     out->log_z = log_z;
     if ((a.flags & HS_SAMPLE_APPEND_TOKEN) && P.slot >= 0 && token >= 0 && token < a.vocab) {
-      int32_t* pos = a.pool_pos + (size_t)P.slot * a.pos_stride;
-      int2* pairs = a.pool_pairs + (size_t)P.slot * a.unique_cap;
-      const int p = pos[token];
-      if (p > 0) {
-        pairs[p - 1].y += 1;
-      } else {
-        const int n = a.pool_n[P.slot];
-        if (n < a.unique_cap) {
-          pairs[n] = make_int2(token, 1);
-          pos[token] = n + 1;
-          a.pool_n[P.slot] = n + 1;
-        } else {
-          out->status = status | 2;
-        }
-      }
+      if (!slot_append_one(a.pool, P.slot, token)) out->status = status | 2;
     }
   }
   // No CTA may leave while a peer can still read its shared memory.

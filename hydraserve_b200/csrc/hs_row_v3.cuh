@@ -1,0 +1,1131 @@
+// The fused per-row sampling kernel for bf16 logits (the serving default): one CTA per row.
+//
+// Everything the sampler needs to know about a bf16 row fits in COUNTS.  A token's final
+// score is a function of its raw bf16 value and of how often the request's history holds
+// it, so tokens fall into classes (count class c in {0, 1, 2}, value bin b), and all tokens
+// of a class share one score and one probability mass.  The kernel streams the row from
+// HBM once, 128 bits at a time, together with the request's dense 2-bit count classes
+// (V/4 bytes), and counts tokens per class with shared-memory atomics: three tables of
+// 6,144 one-value bins (2^-14 <= |x| < 2^10).  The few tokens that do not fit a class --
+// history count >= 3 (listed per request), or a value outside the bin window -- become
+// individual (id, score) entries of a small side list.
+//
+// Selection (top-k by count, min-p by threshold, top-p by probability mass, top-N for the
+// log-probabilities) is a radix descent over 32-bit order-preserving keys of the class
+// scores: each non-empty class contributes (count, count * mass) to a bucket, the buckets
+// are scanned from the top, and once the deciding bucket holds few members they are
+// gathered, sorted and resolved exactly.  Probability mass is an integer multiple of 2^-40,
+// so all sums are exact and order-independent.
+//
+// Token ids are only needed at the very end ("a uniformly chosen member of this class",
+// "the lowest ids of this tie group").  A large class is sampled by rejection: Philox-drawn
+// positions are probed until one belongs to the class (exactly uniform over its members,
+// a handful of random reads).  Small classes and lowest-id tie-breaks walk the row a
+// second time; that walk reads what the first pass just brought through L2.
+#pragma once
+
+#include "hs_common.cuh"
+#include "hs_select.cuh"
+#include "hs_state.cuh"
+#include "hs_row_kernel.cuh"
+#include "../../include/hs_sampler.h"
+
+namespace hs {
+
+constexpr int kV3Half = 3072;                 // 24 binades x 128 mantissas
+constexpr int kV3Bins = 2 * kV3Half;          // per count class
+constexpr int kCells = 3 * kV3Bins;           // count classes 0, 1, 2
+constexpr uint32_t kV3Base = 113u << 7;       // smallest binned magnitude: 2^-14
+constexpr int kV3ListCap = 128;               // members resolved by sorting
+constexpr int kV3RareCap = 512;               // out-of-window tokens remembered before a sweep
+constexpr int kV3PhaseSlots = 12;
+
+struct V3Entry {
+  uint32_t key;  // 32-bit key of the score
+  int32_t id;    // token id of a side element, -1 for a class
+  uint32_t cnt;  // tokens this entry stands for
+  uint32_t cell; // class index (count class * kV3Bins + bin) of a class entry
+  u64 q;         // mass of one token
+};
+
+struct LocalHist {
+  uint32_t cnt[kBins];
+  uint32_t l0[kBins], l1[kBins], l2[kBins];  // mass in 14-bit limbs: 32-bit shared atomics only
+  __device__ __forceinline__ u64 mass(int b) const {
+    return (u64)l0[b] + ((u64)l1[b] << kLimbBits) + ((u64)l2[b] << (2 * kLimbBits));
+  }
+};
+
+struct RowV3Args {
+  RowKernelArgs base;
+  int2* s_pair;   // [batch, s_cap] side lists: (token id or -1, fp32 bits of the score)
+  int s_cap;
+  unsigned long long* phase_clocks;  // [batch, kV3PhaseSlots] or null
+};
+
+struct LayoutV3 {
+  size_t x, tab, hist, gbuf, list, rare, small, total;
+};
+__host__ __device__ inline LayoutV3 layout_v3() {
+  LayoutV3 l{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off = (off + bytes + 15) & ~size_t(15);
+    return at;
+  };
+  l.x = take(sizeof(Exchange));
+  l.tab = take(sizeof(uint32_t) * kCells);
+  l.hist = take(sizeof(LocalHist));
+  l.gbuf = take(sizeof(V3Entry) * kV3ListCap);
+  l.list = take(sizeof(V3Entry) * kV3ListCap);
+  l.rare = take(sizeof(int) * kV3RareCap);
+  l.small = take(sizeof(int) * 16);
+  l.total = off;
+  return l;
+}
+
+__device__ __forceinline__ int v3_bin_of_raw(uint32_t raw) {
+  const uint32_t idx = (raw & 0x7fffu) - kV3Base;
+  if (idx >= (uint32_t)kV3Half) return -1;
+  return (raw & 0x8000u) ? kV3Half - 1 - (int)idx : kV3Half + (int)idx;
+}
+__device__ __forceinline__ uint32_t v3_raw_of_bin(int b) {
+  return b >= kV3Half ? (uint32_t)(b - kV3Half) + kV3Base
+                      : 0x8000u | ((uint32_t)(kV3Half - 1 - b) + kV3Base);
+}
+
+struct Ctx3 {
+  Exchange* x;
+  uint32_t* tab;     // [kCells] tokens per class
+  LocalHist* hist;
+  V3Entry* gbuf;     // gather buffer
+  V3Entry* list;     // sorted members
+  int* gbuf_n;
+  int row, vocab;
+  const unsigned short* logits;  // this row
+  const uint32_t* cls;           // this row's 2-bit classes, or null (no penalties)
+  bool vec;                      // row start is 16-byte aligned
+  Pool pool;
+  int slot;
+  int2* s_pair;
+  int n_s, s_cap;
+  float T, rp, pp, fp;
+  bool greedy;
+  float m;
+
+  __device__ __forceinline__ float score_of_value(float v) const {
+    return greedy ? canonical(v) : canonical(__fdiv_rn(v, T));
+  }
+  // score of a token with raw value bits `raw` that the history holds `count` times
+  __device__ __forceinline__ float score_of(uint32_t raw, int count) const {
+    float v = canonical(__uint_as_float(raw << 16));
+    if (count > 0) {
+      v = v < 0.0f ? __fmul_rn(v, rp) : __fdiv_rn(v, rp);
+      v = __fsub_rn(v, pp);
+      v = __fsub_rn(v, __fmul_rn(fp, (float)count));
+    }
+    return score_of_value(v);
+  }
+  __device__ __forceinline__ float cell_score(int cell) const {
+    const int c = cell / kV3Bins;
+    return score_of(v3_raw_of_bin(cell - c * kV3Bins), c);
+  }
+  __device__ __forceinline__ int class_of(int id) const {
+    return cls ? (int)((cls[id >> 4] >> ((id & 15) * 2)) & 3u) : 0;
+  }
+  // exact history count of a token of class 3
+  __device__ __forceinline__ int heavy_count(int id) const {
+    const int q = (pool.pos + (size_t)slot * pool.pos_stride)[id];
+    return q > 0 ? (pool.pairs + (size_t)slot * pool.unique_cap)[q - 1].y : 0;
+  }
+  // score of the token at position id, whatever population it belongs to
+  __device__ __forceinline__ float element_score(int id, uint32_t raw, int c) const {
+    return score_of(raw, c == 3 ? heavy_count(id) : c);
+  }
+};
+
+template <class F>
+__device__ __forceinline__ void for_each_side3(const Ctx3& c, F&& f) {
+  for (int j0 = threadIdx.x; j0 < c.n_s; j0 += 4 * kThreads) {
+    int2 e[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u * kThreads;
+      e[u] = j < c.n_s ? c.s_pair[j] : make_int2(-1, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (e[u].x >= 0) f(e[u].x, __int_as_float(e[u].y));
+  }
+}
+template <class F>
+__device__ __forceinline__ void for_each_cell(const Ctx3& c, F&& f) {
+  for (int cell = threadIdx.x; cell < kCells; cell += kThreads) {
+    const uint32_t n = c.tab[cell];
+    if (n) f(cell, n, c.cell_score(cell));
+  }
+}
+
+// ---- radix descent inside one CTA ----------------------------------------------------
+struct LocalAdder {
+  LocalHist* h;
+  __device__ __forceinline__ void operator()(bool valid, uint32_t bin, uint32_t count, u64 mass) const {
+    if (!valid) return;
+    atomicAdd(&h->cnt[bin], count);
+    const uint32_t a0 = (uint32_t)mass & kLimbMask;
+    const uint32_t a1 = (uint32_t)(mass >> kLimbBits) & kLimbMask;
+    const uint32_t a2 = (uint32_t)(mass >> (2 * kLimbBits));
+    if (a0) atomicAdd(&h->l0[bin], a0);
+    if (a1) atomicAdd(&h->l1[bin], a1);
+    if (a2) atomicAdd(&h->l2[bin], a2);
+  }
+};
+
+template <bool BY_MASS, class Fill>
+__device__ Selection descend_local(Ctx3& c, Fill& fill, uint32_t lo_key, u64 target_cnt, float top_p,
+                                   u64 stop_pop = 0, int first_level = 0, uint32_t prefix0 = 0) {
+  LocalHist& h = *c.hist;
+  Selection sel;
+  sel.above_cnt = sel.above_mass = 0;
+  sel.total_cnt = sel.total_mass = 0;
+  sel.bin_cnt = sel.bin_mass = 0;
+  sel.target = target_cnt;
+  sel.ok = true;
+  sel.levels = first_level;
+  uint32_t prefix = prefix0;
+  const int tid = threadIdx.x;
+  const LocalAdder add{&h};
+  for (int level = first_level; level < 3; ++level) {
+    const int shift = level_shift(level);
+    const int bits = level_bits(level);
+    for (int b = tid; b < kBins; b += kThreads) { h.cnt[b] = 0; h.l0[b] = 0; h.l1[b] = 0; h.l2[b] = 0; }
+    if (tid == 0) c.x->bcast[7] = 0;
+    __syncthreads();
+    fill(level, shift, bits, prefix, lo_key, add);
+    __syncthreads();
+    constexpr int kPer = kBins / kThreads;
+    const int hi = kBins - 1 - kPer * tid;
+    u64 c_sum = 0, m_sum = 0;
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) { c_sum += h.cnt[hi - u]; m_sum += h.mass(hi - u); }
+    const u64 ia = warp_scan_u64(c_sum);
+    const u64 ib = warp_scan_u64(m_sum);
+    u64 pa, pb, ta, tb;
+    block_warp_prefix2(*c.x, shfl_u64(ia, 31), shfl_u64(ib, 31), pa, pb, ta, tb);
+    u64 ex_cnt = pa + ia - c_sum;
+    u64 ex_mass = pb + ib - m_sum;
+    if (level == first_level) {
+      sel.total_cnt = ta;
+      sel.total_mass = tb;
+      if (BY_MASS && top_p >= 0.0f) sel.target = top_p_target(tb, top_p);
+    }
+    const u64 want = sel.target - (BY_MASS ? sel.above_mass : sel.above_cnt);
+    {
+      const u64 ex = BY_MASS ? ex_mass : ex_cnt;
+      const u64 mine = BY_MASS ? m_sum : c_sum;
+      if (ex < want && want <= ex + mine) {
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+          const u64 bc = h.cnt[hi - u], bm = h.mass(hi - u);
+          const u64 e = BY_MASS ? ex_mass : ex_cnt;
+          if (want <= e + (BY_MASS ? bm : bc)) {
+            c.x->bcast[0] = (u64)(hi - u);
+            c.x->bcast[1] = ex_cnt;
+            c.x->bcast[2] = ex_mass;
+            c.x->bcast[3] = bc;
+            c.x->bcast[4] = bm;
+            c.x->bcast[7] = 1;
+            break;
+          }
+          ex_cnt += bc;
+          ex_mass += bm;
+        }
+      }
+    }
+    __syncthreads();
+    if (c.x->bcast[7] == 0) {
+      sel.ok = false;
+      sel.key = lo_key;
+      sel.prefix = prefix;
+      sel.bin_cnt = sel.bin_mass = 0;
+      __syncthreads();
+      return sel;
+    }
+    const uint32_t bin = (uint32_t)c.x->bcast[0];
+    sel.above_cnt += c.x->bcast[1];
+    sel.above_mass += c.x->bcast[2];
+    sel.bin_cnt = c.x->bcast[3];
+    sel.bin_mass = c.x->bcast[4];
+    prefix = (prefix << bits) | bin;
+    sel.levels = level + 1;
+    __syncthreads();
+    if (stop_pop && level < 2 && sel.bin_cnt <= stop_pop) break;
+  }
+  sel.prefix = prefix;
+  sel.key = sel.levels == 3 ? prefix : (prefix << (sel.levels == 1 ? 21 : 10));
+  return sel;
+}
+
+// All tokens of the row: side elements individually, classes as (count, count * mass).
+template <bool WITH_MASS>
+struct UnionFill3 {
+  Ctx3* c;
+  template <class Add>
+  __device__ __forceinline__ void operator()(int level, int shift, int bits, uint32_t prefix,
+                                             uint32_t lo_key, const Add& add) const {
+    const uint32_t mask = (1u << bits) - 1u;
+    auto ok = [&](uint32_t k) { return k >= lo_key && (level == 0 || (k >> (shift + bits)) == prefix); };
+    for_each_side3(*c, [&](int, float s) {
+      const uint32_t k = key_of(s);
+      const bool valid = ok(k);
+      add(valid, (k >> shift) & mask, 1u, (WITH_MASS && valid) ? mass_of(s, c->m) : 0ull);
+    });
+    // classes: each thread owns consecutive classes, whose scores are neighbours, so runs
+    // that fall into one bucket are merged in registers before touching shared memory
+    constexpr int kPerCells = kCells / kThreads;
+    const int cell0 = kPerCells * threadIdx.x;
+    uint32_t run_bin = 0xffffffffu, run_cnt = 0;
+    u64 run_mass = 0;
+#pragma unroll 1
+    for (int u = 0; u < kPerCells; ++u) {
+      const uint32_t n = c->tab[cell0 + u];
+      if (!n) continue;
+      const float s = c->cell_score(cell0 + u);
+      const uint32_t k = key_of(s);
+      if (!ok(k)) continue;
+      const uint32_t bin = (k >> shift) & mask;
+      if (bin != run_bin) {
+        add(run_cnt != 0, run_bin, run_cnt, run_mass);
+        run_bin = bin; run_cnt = 0; run_mass = 0;
+      }
+      run_cnt += n;
+      if (WITH_MASS) run_mass += (u64)n * mass_of(s, c->m);
+    }
+    add(run_cnt != 0, run_bin, run_cnt, run_mass);
+  }
+};
+
+// Kept side elements keyed by ~id with their mass: the side part of the draw.
+struct SideDrawFill3 {
+  Ctx3* c;
+  uint32_t cut_key;
+  template <class Add>
+  __device__ __forceinline__ void operator()(int level, int shift, int bits, uint32_t prefix,
+                                             uint32_t, const Add& add) const {
+    const uint32_t mask = (1u << bits) - 1u;
+    for_each_side3(*c, [&](int id, float s) {
+      const uint32_t k = ~(uint32_t)id;
+      const bool valid = key_of(s) > cut_key && (level == 0 || (k >> (shift + bits)) == prefix);
+      add(valid, (k >> shift) & mask, 1u, valid ? mass_of(s, c->m) : 0ull);
+    });
+  }
+};
+
+// Gathers the members (side elements, classes) with key >= lo_key whose top `levels` radix
+// digits equal `prefix` into `list`, sorted by (key descending, classes first, id ascending).
+__device__ int gather_members3(Ctx3& c, uint32_t lo_key, int levels, uint32_t prefix) {
+  const int tid = threadIdx.x;
+  if (tid == 0) *c.gbuf_n = 0;
+  __syncthreads();
+  const int drop = levels == 1 ? 21 : (levels == 2 ? 10 : 0);
+  auto matches = [&](uint32_t k) {
+    if (k < lo_key) return false;
+    return levels == 0 || (levels == 3 ? k == prefix : (k >> drop) == prefix);
+  };
+  for_each_side3(c, [&](int id, float s) {
+    const uint32_t k = key_of(s);
+    if (!matches(k)) return;
+    const int slot = atomicAdd(c.gbuf_n, 1);
+    if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{k, id, 1u, 0u, mass_of(s, c.m)};
+  });
+  for_each_cell(c, [&](int cell, uint32_t n, float s) {
+    const uint32_t k = key_of(s);
+    if (!matches(k)) return;
+    const int slot = atomicAdd(c.gbuf_n, 1);
+    if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{k, -1, n, (uint32_t)cell, mass_of(s, c.m)};
+  });
+  __syncthreads();
+  const int n = min(*c.gbuf_n, kV3ListCap);
+  if (tid < n) {
+    const V3Entry mine = c.gbuf[tid];
+    int pos = 0;
+    for (int j = 0; j < n; ++j) {
+      const uint32_t kj = c.gbuf[j].key;
+      const int idj = c.gbuf[j].id;
+      // classes (id -1) sort before side elements of the same key; two classes of one key
+      // are ordered by their class index
+      const bool before = kj > mine.key ||
+                          (kj == mine.key && (idj < mine.id || (idj == mine.id && c.gbuf[j].cell < mine.cell)));
+      pos += before ? 1 : 0;
+    }
+    c.list[pos] = mine;
+  }
+  __syncthreads();
+  return n;
+}
+
+template <bool BY_MASS>
+__device__ Selection resolve3(Ctx3& c, Selection sel, uint32_t lo_key) {
+  if (!sel.ok || sel.levels == 3) return sel;
+  const int n = gather_members3(c, lo_key, sel.levels, sel.prefix);
+  const int tid = threadIdx.x;
+  u64 a = 0, b = 0;
+  if (tid < n) { a = c.list[tid].cnt; b = a * c.list[tid].q; }
+  const u64 ia = warp_scan_u64(a), ib = warp_scan_u64(b);
+  u64 pa, pb, tc, tm;
+  block_warp_prefix2(*c.x, shfl_u64(ia, 31), shfl_u64(ib, 31), pa, pb, tc, tm);
+  const u64 want = sel.target - (BY_MASS ? sel.above_mass : sel.above_cnt);
+  if (tid == 0) c.x->bcast[7] = 0;
+  __syncthreads();
+  if (tid < n) {
+    const u64 incl = BY_MASS ? pb + ib : pa + ia;
+    const u64 excl = incl - (BY_MASS ? b : a);
+    if (excl < want && want <= incl) { c.x->bcast[0] = c.list[tid].key; c.x->bcast[7] = 1; }
+  }
+  __syncthreads();
+  if (c.x->bcast[7] == 0) {
+    sel.ok = false;
+    __syncthreads();
+    return sel;
+  }
+  const uint32_t key = (uint32_t)c.x->bcast[0];
+  u64 ac = 0, am = 0, bc = 0, bm = 0;
+  if (tid < n) {
+    if (c.list[tid].key > key) { ac = a; am = b; }
+    if (c.list[tid].key == key) { bc = a; bm = b; }
+  }
+  block_sum2(*c.x, ac, am);
+  block_sum2(*c.x, bc, bm);
+  sel.key = key;
+  sel.prefix = key;
+  sel.levels = 3;
+  sel.above_cnt += ac;
+  sel.above_mass += am;
+  sel.bin_cnt = bc;
+  sel.bin_mass = bm;
+  __syncthreads();
+  return sel;
+}
+
+template <bool BY_MASS, bool WITH_MASS>
+__device__ Selection select_union3(Ctx3& c, uint32_t lo_key, u64 target, float top_p) {
+  UnionFill3<WITH_MASS> fill{&c};
+  Selection sel = descend_local<BY_MASS>(c, fill, lo_key, target, top_p, (u64)kV3ListCap);
+  return resolve3<BY_MASS>(c, sel, lo_key);
+}
+
+// Count and mass of all tokens with key >= lo_key.
+__device__ void totals3(Ctx3& c, uint32_t lo_key, u64& cnt, u64& mass) {
+  u64 a = 0, b = 0;
+  for_each_side3(c, [&](int, float s) {
+    if (key_of(s) >= lo_key) { ++a; b += mass_of(s, c.m); }
+  });
+  for_each_cell(c, [&](int, uint32_t n, float s) {
+    if (key_of(s) >= lo_key) { a += n; b += (u64)n * mass_of(s, c.m); }
+  });
+  block_sum2(*c.x, a, b);
+  cnt = a;
+  mass = b;
+}
+
+// ---- the tie group of a key: the classes (at most one per count class, scores grow with
+// the bin) and the side elements whose score key equals it ---------------------------------
+struct Group {
+  uint32_t key;
+  int cell[3];  // class index per count class, or -1
+};
+__device__ Group find_group(Ctx3& c, uint32_t key) {
+  if (threadIdx.x < 3) c.x->bcast[threadIdx.x] = 0;
+  __syncthreads();
+  for_each_cell(c, [&](int cell, uint32_t, float s) {
+    if (key_of(s) == key) c.x->bcast[cell / kV3Bins] = (u64)cell + 1;
+  });
+  __syncthreads();
+  Group g;
+  g.key = key;
+  for (int i = 0; i < 3; ++i) g.cell[i] = (int)c.x->bcast[i] - 1;
+  __syncthreads();
+  return g;
+}
+// Does the token at position id (raw bits, 2-bit class cc) belong to the group?
+__device__ __forceinline__ bool in_group(const Ctx3& c, const Group& g, int id, uint32_t raw, int cc) {
+  if (cc < 3) {
+    const int b = v3_bin_of_raw(raw);
+    if (b >= 0) return g.cell[cc] == cc * kV3Bins + b;
+    return key_of(c.score_of(raw, cc)) == g.key;  // outside the bin window: a side element
+  }
+  return key_of(c.score_of(raw, c.heavy_count(id))) == g.key;
+}
+
+// Loads chunk i (8 tokens) of the row and its classes.
+__device__ __forceinline__ void load_chunk(const Ctx3& c, int i, uint32_t (&raw)[8], uint32_t& cls16) {
+  const uint4 w = reinterpret_cast<const uint4*>(c.logits)[i];
+  raw[0] = w.x & 0xffffu; raw[1] = w.x >> 16; raw[2] = w.y & 0xffffu; raw[3] = w.y >> 16;
+  raw[4] = w.z & 0xffffu; raw[5] = w.z >> 16; raw[6] = w.w & 0xffffu; raw[7] = w.w >> 16;
+  cls16 = c.cls ? reinterpret_cast<const unsigned short*>(c.cls)[i] : 0u;
+}
+// Bit k set: token 8*i + k belongs to the group.
+__device__ __forceinline__ uint32_t chunk_members(const Ctx3& c, const Group& g, int i, const uint4& w,
+                                                  uint32_t cls16) {
+  const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+  uint32_t memb = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    memb |= (in_group(c, g, 8 * i + 2 * k, words[k] & 0xffffu, (cls16 >> (4 * k)) & 3) ? 1u : 0u) << (2 * k);
+    memb |= (in_group(c, g, 8 * i + 2 * k + 1, words[k] >> 16, (cls16 >> (4 * k + 2)) & 3) ? 1u : 0u) << (2 * k + 1);
+  }
+  return memb;
+}
+// Members in chunks [b, e) seen by this lane (lanes of a warp interleave), four 128-bit
+// loads in flight per lane.
+__device__ __forceinline__ u64 count_members(const Ctx3& c, const Group& g, int b, int e) {
+  const int lane = threadIdx.x & 31;
+  const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
+  const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
+  u64 mine = 0;
+  for (int i0 = b + lane; i0 < e; i0 += 4 * 32) {
+    uint4 w[4];
+    uint32_t cl[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + 32 * u;
+      if (i < e) { w[u] = src4[i]; cl[u] = cls16p ? cls16p[i] : 0u; }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + 32 * u;
+      if (i < e) mine += __popc(chunk_members(c, g, i, w[u], cl[u]));
+    }
+  }
+  return mine;
+}
+
+// Token id of the n-th (1-based, ascending id) member of the group (classes and side
+// elements whose score key is g.key), or 0x7fffffff.  The row is cut into one segment per
+// warp, members are counted, and the segment that holds the n-th is cut again until one
+// warp can rank its members with ballots.
+__device__ int nth_in_group(Ctx3& c, const Group& g, u64 n) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
+  const int n8 = c.vec ? c.vocab / 8 : 0;
+  int b = 0, e = n8;
+  u64 before = 0;
+  bool in_tail = false;
+  int result = 0x7fffffff;
+  while (true) {
+    if (e - b <= 4 * 32) break;
+    const int seg = (e - b + kWarps - 1) / kWarps;
+    const int mb = min(b + warp * seg, e), me = min(mb + seg, e);
+    const u64 wtot = warp_sum_u64(count_members(c, g, mb, me));
+    u64 pre, pre_unused, tot, tot_unused;
+    block_warp_prefix2(*c.x, wtot, 0, pre, pre_unused, tot, tot_unused);
+    if (before + tot < n) { before += tot; in_tail = true; break; }
+    if (before + pre < n && n <= before + pre + wtot && lane == 0) {
+      c.x->bcast[4] = (u64)mb;
+      c.x->bcast[5] = (u64)me;
+      c.x->bcast[6] = before + pre;
+    }
+    __syncthreads();
+    b = (int)c.x->bcast[4];
+    e = (int)c.x->bcast[5];
+    before = c.x->bcast[6];
+    __syncthreads();
+  }
+  if (tid == 0) c.x->bcast[6] = 0;
+  __syncthreads();
+  if (!in_tail && warp == 0) {
+    // at most 128 chunks: rank members with warp scans
+    const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
+    const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
+    u64 running = before;
+    for (int i0 = b; i0 < e && running < n; i0 += 32) {
+      const int i = i0 + lane;
+      uint32_t memb = 0;
+      if (i < e) memb = chunk_members(c, g, i, src4[i], cls16p ? cls16p[i] : 0u);
+      const u64 incl = warp_scan_u64((u64)__popc(memb));
+      u64 rank = running + incl - __popc(memb);
+      for (int k = 0; k < 8; ++k) {
+        if (!((memb >> k) & 1u)) continue;
+        if (++rank == n) c.x->bcast[6] = (u64)(8 * i + k) + 1;
+      }
+      running += shfl_u64(incl, 31);
+    }
+    if (running < n) before = running;  // not reached inside the vector part: look in the tail
+    if (lane == 0 && running < n) c.x->bcast[5] = running;
+  }
+  __syncthreads();
+  if (c.x->bcast[6] == 0) {
+    // scalar tail of the row (all of it when the row is not 16-byte aligned)
+    if (!in_tail) before = c.x->bcast[5];
+    if (warp == 0) {
+      u64 running = in_tail ? before : c.x->bcast[5];
+      for (int id0 = n8 * 8; id0 < c.vocab && running < n; id0 += 32) {
+        const int id = id0 + lane;
+        const bool mbr = id < c.vocab && in_group(c, g, id, c.logits[id], c.class_of(id));
+        const uint32_t ballot = __ballot_sync(0xffffffffu, mbr);
+        const u64 rank = running + __popc(ballot & ((1u << lane) - 1u)) + 1;
+        if (mbr && rank == n) c.x->bcast[6] = (u64)id + 1;
+        running += __popc(ballot);
+      }
+    }
+    __syncthreads();
+  }
+  const u64 found = c.x->bcast[6];
+  __syncthreads();
+  if (found) result = (int)(found - 1);
+  return result;
+}
+
+// Appends to the gather buffer the ids of all group members with id <= id_limit.
+__device__ void emit_group_upto(Ctx3& c, const Group& g, int id_limit) {
+  const int n8 = c.vec ? c.vocab / 8 : 0;
+  const int last = min(n8, id_limit / 8 + 1);
+  const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
+  const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
+  auto emit = [&](int id) {
+    const int slot = atomicAdd(c.gbuf_n, 1);
+    if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{g.key, id, 1u, 0u, 0ull};
+  };
+  for (int i = threadIdx.x; i < last; i += kThreads) {
+    uint32_t memb = chunk_members(c, g, i, src4[i], cls16p ? cls16p[i] : 0u);
+    while (memb) {
+      const int k = __ffs(memb) - 1;
+      memb &= memb - 1;
+      if (8 * i + k <= id_limit) emit(8 * i + k);
+    }
+  }
+  for (int id = n8 * 8 + threadIdx.x; id < c.vocab && id <= id_limit; id += kThreads)
+    if (in_group(c, g, id, c.logits[id], c.class_of(id))) emit(id);
+  __syncthreads();
+}
+
+// A uniformly chosen member of the group by rejection: Philox-drawn positions are probed,
+// trial t = round * kThreads + thread, and the lowest hitting trial wins.  id_limit
+// restricts the choice to members with id <= id_limit.  Returns -1 if max_rounds pass
+// without a hit.
+__device__ int random_in_group(Ctx3& c, const Group& g, uint64_t seed, int id_limit, int max_rounds) {
+  const int tid = threadIdx.x;
+  for (int round = 0; round < max_rounds; ++round) {
+    const Philox4 r = philox4x32_10((uint32_t)round, (uint32_t)tid, 1u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32));
+    const u64 r64 = ((u64)r.v[0] << 32) | r.v[1];
+    const int id = (int)__umul64hi(r64, (u64)c.vocab);
+    const bool ok = id <= id_limit && in_group(c, g, id, c.logits[id], c.class_of(id));
+    // lowest trial index that hit
+    const uint32_t key = ok ? (uint32_t)(kThreads - tid) : 0u;
+    const uint32_t best = block_max_u32(*c.x, key);
+    if (best) {
+      if (key == best) c.x->bcast[6] = (u64)id;
+      __syncthreads();
+      const int token = (int)c.x->bcast[6];
+      __syncthreads();
+      return token;
+    }
+  }
+  return -1;
+}
+
+__global__ void __launch_bounds__(kThreads, 2) row_kernel_v3(const RowV3Args args) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const RowKernelArgs& a = args.base;
+  const LayoutV3 lay = layout_v3();
+  Ctx3 c;
+  c.x = reinterpret_cast<Exchange*>(smem_raw + lay.x);
+  c.tab = reinterpret_cast<uint32_t*>(smem_raw + lay.tab);
+  c.hist = reinterpret_cast<LocalHist*>(smem_raw + lay.hist);
+  c.gbuf = reinterpret_cast<V3Entry*>(smem_raw + lay.gbuf);
+  c.list = reinterpret_cast<V3Entry*>(smem_raw + lay.list);
+  int* rare_id = reinterpret_cast<int*>(smem_raw + lay.rare);
+  int* small = reinterpret_cast<int*>(smem_raw + lay.small);
+  c.gbuf_n = small;
+  int* rare_n = small + 1;
+  int* side_n = small + 2;
+  const int tid = threadIdx.x;
+  c.row = blockIdx.x;
+  c.vocab = a.vocab;
+  c.logits = reinterpret_cast<const unsigned short*>(a.logits) + (long long)c.row * a.row_stride;
+  c.vec = (reinterpret_cast<uintptr_t>(c.logits) & 15u) == 0;
+  const hs_row_params P = a.params[c.row];
+  hs_row_out* out = a.out + c.row;
+  c.greedy = P.temperature == 0.0f;
+  c.T = P.temperature;
+  c.rp = P.repetition_penalty;
+  c.pp = P.presence_penalty;
+  c.fp = P.frequency_penalty;
+  c.pool = a.pool;
+  c.slot = P.slot;
+  const bool penalised = P.slot >= 0 && (P.repetition_penalty != 1.0f || P.presence_penalty != 0.0f ||
+                                          P.frequency_penalty != 0.0f);
+  c.cls = penalised ? a.pool.cls + (size_t)P.slot * a.pool.cls_stride : nullptr;
+  c.s_pair = args.s_pair + (size_t)c.row * args.s_cap;
+  c.s_cap = args.s_cap;
+  c.n_s = 0;
+  c.m = 0.f;
+  unsigned long long* clocks = args.phase_clocks ? args.phase_clocks + (size_t)c.row * kV3PhaseSlots : nullptr;
+  auto mark = [&](int slot) {
+    if (clocks && tid == 0) clocks[slot] = clock64();
+  };
+  mark(0);
+  int status = 0;
+
+  // ---- plain greedy rows of a mixed batch: arg max only -----------------------------------
+  if (c.greedy && !penalised && P.n_logprobs < 0) {
+    u64 best = 0;
+    auto consider = [&](uint32_t raw, int id) {
+      const u64 packed = ((u64)key_of(canonical(__uint_as_float(raw << 16))) << 32) | (uint32_t)(~(uint32_t)id);
+      best = packed > best ? packed : best;
+    };
+    const int n8 = c.vec ? c.vocab / 8 : 0;
+    for (int i = tid; i < n8; i += kThreads) {
+      uint32_t raw[8], cls16;
+      load_chunk(c, i, raw, cls16);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) consider(raw[k], 8 * i + k);
+    }
+    for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) consider(c.logits[id], id);
+    best = block_max_u64(*c.x, best);
+    if (a.scores_out) {
+      float* dst = a.scores_out + (size_t)c.row * a.vocab;
+      for (int id = tid; id < c.vocab; id += kThreads) dst[id] = canonical(__uint_as_float((uint32_t)c.logits[id] << 16));
+    }
+    if (tid == 0) {
+      out->token = (int)(~(uint32_t)(best & 0xffffffffu));
+      out->logprob = 0.f; out->n_top = 0; out->status = 0;
+      out->n_kept = a.vocab; out->n_after_topk = a.vocab; out->n_after_minp = a.vocab; out->n_after_topp = a.vocab;
+      out->cut_bits = 0xff800000u; out->n_cut_ties = -1;
+      out->row_max = score_of((uint32_t)(best >> 32)); out->log_z = 0.f;
+    }
+    return;
+  }
+
+  for (int i = tid; i < kCells; i += kThreads) c.tab[i] = 0;
+  if (tid < 16) small[tid] = 0;
+  __syncthreads();
+
+  // ---- A. the one read of the row from HBM: count tokens per (count class, value) --------
+  {
+    auto count_one = [&](uint32_t raw, int cc, int id) {
+      if (cc == 3) return;  // listed per request; handled below with its exact count
+      const int b = v3_bin_of_raw(raw);
+      if (b >= 0) {
+        atomicAdd(&c.tab[cc * kV3Bins + b], 1u);
+      } else {
+        const int slot = atomicAdd(rare_n, 1);
+        if (slot < kV3RareCap) rare_id[slot] = id;
+      }
+    };
+    const int n8 = c.vec ? c.vocab / 8 : 0;
+    const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
+    const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
+    constexpr int kInFlight = 8;
+    for (int i0 = tid; i0 < n8; i0 += kInFlight * kThreads) {
+      uint4 w[kInFlight];
+      uint32_t cl[kInFlight];
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const int i = i0 + u * kThreads;
+        if (i < n8) {
+          w[u] = src4[i];
+          cl[u] = cls16p ? cls16p[i] : 0u;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        const int i = i0 + u * kThreads;
+        if (i >= n8) break;
+        const uint32_t words[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          count_one(words[k] & 0xffffu, (cl[u] >> (4 * k)) & 3, 8 * i + 2 * k);
+          count_one(words[k] >> 16, (cl[u] >> (4 * k + 2)) & 3, 8 * i + 2 * k + 1);
+        }
+      }
+    }
+    for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) count_one(c.logits[id], c.class_of(id), id);
+  }
+  __syncthreads();
+  mark(1);
+
+  // ---- B. the side list: tokens with history count >= 3, and values outside the bin window
+  u64 side_best = 0;
+  {
+    auto put = [&](int slot, int id, float s) {
+      if (slot >= args.s_cap) { status |= 4; return; }
+      c.s_pair[slot] = make_int2(id, __float_as_int(s));
+      const u64 packed = ((u64)key_of(s) << 32) | (uint32_t)(~(uint32_t)id);
+      side_best = packed > side_best ? packed : side_best;
+    };
+    int n_heavy = 0;
+    if (penalised) {
+      n_heavy = min(a.pool.n_heavy[P.slot], min(a.pool.unique_cap, args.s_cap));
+      const int32_t* heavy = a.pool.heavy + (size_t)P.slot * a.pool.unique_cap;
+      for (int j = tid; j < n_heavy; j += kThreads) {
+        const int id = heavy[j];
+        if (id < 0 || id >= c.vocab) { c.s_pair[j] = make_int2(-1, 0); continue; }
+        put(j, id, c.score_of(c.logits[id], c.heavy_count(id)));
+      }
+    }
+    const int n_rare = *rare_n;
+    if (n_rare <= kV3RareCap) {
+      for (int t = tid; t < n_rare; t += kThreads) {
+        const int id = rare_id[t];
+        put(n_heavy + t, id, c.score_of(c.logits[id], c.class_of(id)));
+      }
+      c.n_s = min(n_heavy + n_rare, args.s_cap);
+    } else {
+      // too many to remember: sweep the row again for out-of-window values
+      for (int id = tid; id < c.vocab; id += kThreads) {
+        const uint32_t raw = c.logits[id];
+        const int cc = c.class_of(id);
+        if (cc == 3 || v3_bin_of_raw(raw) >= 0) continue;
+        put(n_heavy + atomicAdd(side_n, 1), id, c.score_of(raw, cc));
+      }
+      __syncthreads();
+      c.n_s = min(n_heavy + *side_n, args.s_cap);
+    }
+  }
+  side_best = block_max_u64(*c.x, side_best);  // (its barriers also publish the side list)
+  mark(2);
+
+  // ---- C. row maximum ------------------------------------------------------------------------
+  // scores grow with the bin inside a count class: the top non-empty bin of each class decides
+  uint32_t cells_key = 0;
+  {
+    uint32_t top[3];
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      uint32_t mine = 0;
+      for (int cell = k * kV3Bins + tid; cell < (k + 1) * kV3Bins; cell += kThreads)
+        if (c.tab[cell]) mine = (uint32_t)cell + 1;
+      top[k] = block_max_u32(*c.x, mine);
+    }
+#pragma unroll
+    for (int k = 0; k < 3; ++k)
+      if (top[k]) cells_key = max(cells_key, key_of(c.cell_score((int)top[k] - 1)));
+  }
+  const uint32_t side_key = (uint32_t)(side_best >> 32);
+  const int side_arg = (int)(~(uint32_t)(side_best & 0xffffffffu));
+  const bool any_side = side_best != 0;
+  const uint32_t max_key = max(cells_key, side_key);
+  c.m = score_of(max_key);
+  const float m = c.m;
+  mark(3);
+
+  KeptSet kept{0u, 0x7fffffff};
+  int token = -1;
+  u64 n_topk = (u64)a.vocab, n_minp = (u64)a.vocab, n_kept = (u64)a.vocab;
+  u64 q_kept = 0;
+  bool have_totals = false;
+  long long cut_ties = -1;
+  u64 cut_group_cnt = 0;   // members at the cut key (kept or not)
+  bool tie_split = false;
+  Group cut_group{0u, {-1, -1, -1}};
+  bool have_cut_group = false;
+  auto need_cut_group = [&]() {
+    if (!have_cut_group) { cut_group = find_group(c, kept.cut_key); have_cut_group = true; }
+  };
+  auto need_tie_limit = [&]() {
+    if (tie_split && kept.tie_limit == 0x7fffffff) {
+      need_cut_group();
+      kept.tie_limit = nth_in_group(c, cut_group, (u64)cut_ties);
+    }
+  };
+
+  if (c.greedy) {
+    const Group g = find_group(c, max_key);
+    token = nth_in_group(c, g, 1);
+    if (token == 0x7fffffff) { token = any_side ? side_arg : 0; status |= 1; }
+    if (P.n_logprobs >= 0) {
+      u64 cn;
+      totals3(c, 0u, cn, q_kept);
+    }
+  } else {
+    u64 cnt = 0, mass = 0;
+    if (P.top_k > 0 && P.top_k < a.vocab) {
+      Selection sk = select_union3<false, true>(c, 0u, (u64)P.top_k, 1.0f);
+      if (!sk.ok) status |= 1;
+      kept.cut_key = sk.key;
+      cnt = sk.above_cnt + sk.bin_cnt;
+      mass = sk.above_mass + sk.bin_mass;
+      have_totals = sk.ok;
+      n_topk = cnt;
+      cut_group_cnt = sk.bin_cnt;
+    }
+    mark(4);
+    if (P.min_p > 0.0f) {
+      if (!have_totals) { totals3(c, kept.cut_key, cnt, mass); have_totals = true; }
+      const float z1 = mass_to_float(mass);
+      const float thr = __fmul_rn(__fdiv_rn(1.0f, z1), P.min_p);
+      uint32_t lowest = 0xffffffffu;
+      auto consider = [&](float s) {
+        const uint32_t k = key_of(s);
+        if (k >= kept.cut_key && !(__fdiv_rn(expf(s - m), z1) < thr)) lowest = min(lowest, k);
+      };
+      for_each_cell(c, [&](int, uint32_t, float s) { consider(s); });
+      for_each_side3(c, [&](int, float s) { consider(s); });
+      lowest = ~block_max_u32(*c.x, ~lowest);
+      if (lowest != 0xffffffffu && lowest > kept.cut_key) {
+        kept.cut_key = lowest;
+        have_totals = false;
+      }
+    }
+    mark(5);
+    if (P.top_p < 1.0f) {
+      Selection sp = select_union3<true, true>(c, kept.cut_key, 0, P.top_p);
+      n_minp = sp.total_cnt;
+      if (sp.ok && sp.bin_cnt > 0) {
+        const u64 qv = sp.bin_mass / sp.bin_cnt;  // every token at the cut key has the same mass
+        u64 t = sp.bin_cnt;
+        if (qv > 0) {
+          const u64 want = sp.target - sp.above_mass;
+          t = (want + qv - 1) / qv;
+          if (t < 1) t = 1;
+          if (t > sp.bin_cnt) t = sp.bin_cnt;
+        }
+        kept.cut_key = sp.key;
+        cnt = sp.above_cnt + t;
+        mass = sp.above_mass + t * qv;
+        cut_ties = (long long)t;
+        cut_group_cnt = sp.bin_cnt;
+        tie_split = t < sp.bin_cnt;
+        have_totals = true;
+      } else {
+        status |= 1;
+        cnt = sp.total_cnt;
+        mass = sp.total_mass;
+        have_totals = true;
+      }
+    } else {
+      if (!have_totals) { totals3(c, kept.cut_key, cnt, mass); have_totals = true; }
+      n_minp = cnt;
+    }
+    n_kept = cnt;
+    q_kept = mass;
+    mark(6);
+
+    // ---- draw --------------------------------------------------------------------------
+    if (q_kept == 0) {
+      status |= 1;
+      token = any_side ? side_arg : 0;
+    } else if (a.noise) {
+      // reference draws: arg max of fl(fl(e / z) / noise) over the kept set, lowest id on ties
+      need_tie_limit();
+      const float zf = mass_to_float(q_kept);
+      const float* noise_row = a.noise + (size_t)c.row * a.vocab;
+      u64 best = 0;
+      for (int id = tid; id < c.vocab; id += kThreads) {
+        const float s = c.element_score(id, c.logits[id], c.class_of(id));
+        if (!kept.has(key_of(s), id)) continue;
+        const float p = __fdiv_rn(expf(s - m), zf);
+        const float ratio = __fdiv_rn(p, noise_row[id]);
+        const u64 packed = ((u64)__float_as_uint(ratio) << 32) | (uint32_t)(~(uint32_t)id);
+        best = packed > best ? packed : best;
+      }
+      best = block_max_u64(*c.x, best);
+      token = (int)(~(uint32_t)(best & 0xffffffffu));
+    } else {
+      // Inverse CDF over exact integer masses in the order: classes above the cut (by class
+      // index), the tie group at the cut (its lowest ids), side elements above the cut (by id).
+      const Philox4 r = philox4x32_10(0u, 0u, 0u, 0u, (uint32_t)P.seed, (uint32_t)(P.seed >> 32));
+      const u64 r64 = ((u64)r.v[0] << 32) | r.v[1];
+      const u64 target = __umul64hi(r64, q_kept);
+      constexpr int kPerCells = kCells / kThreads;  // 36 consecutive classes per thread
+      const int cell0 = kPerCells * tid;
+      u64 chunk = 0;
+#pragma unroll 1
+      for (int u = 0; u < kPerCells; ++u) {
+        const uint32_t n = c.tab[cell0 + u];
+        if (!n) continue;
+        const float s = c.cell_score(cell0 + u);
+        if (key_of(s) > kept.cut_key) chunk += (u64)n * mass_of(s, m);
+      }
+      const u64 incl = warp_scan_u64(chunk);
+      u64 pre, pre_unused, q_cells, tot_unused;
+      block_warp_prefix2(*c.x, shfl_u64(incl, 31), 0, pre, pre_unused, q_cells, tot_unused);
+      // the group at the cut key: cut_ties members when top-p split it, else all of them
+      u64 group_kept = cut_ties >= 0 ? (u64)cut_ties : 0;
+      u64 q_cut = 0;
+      if (cut_ties < 0) {
+        // cut by top-k / min-p / nothing: everything at the cut key is kept; count it
+        u64 gc = 0, gm = 0;
+        for_each_cell(c, [&](int, uint32_t n, float s) { if (key_of(s) == kept.cut_key) gc += n; });
+        for_each_side3(c, [&](int, float s) { if (key_of(s) == kept.cut_key) gc += 1; });
+        block_sum2(*c.x, gc, gm);
+        group_kept = gc;
+      }
+      q_cut = mass_of(score_of(kept.cut_key), m);
+      const u64 q_group = group_kept * q_cut;
+      if (target < q_cells) {
+        if (tid == 0) c.x->bcast[5] = 0;
+        __syncthreads();
+        u64 run = pre + incl - chunk;
+        if (run <= target && target < run + chunk) {
+#pragma unroll 1
+          for (int u = 0; u < kPerCells; ++u) {
+            const uint32_t n = c.tab[cell0 + u];
+            if (!n) continue;
+            const float s = c.cell_score(cell0 + u);
+            if (key_of(s) <= kept.cut_key) continue;
+            const u64 q = mass_of(s, m);
+            const u64 w = (u64)n * q;
+            if (w && target < run + w) {
+              c.x->bcast[3] = n;
+              c.x->bcast[4] = (target - run) / q + 1;
+              c.x->bcast[5] = (u64)(cell0 + u) + 1;
+              break;
+            }
+            run += w;
+          }
+        }
+        __syncthreads();
+        const int cell = (int)c.x->bcast[5] - 1;
+        const u64 members = c.x->bcast[3], nth = c.x->bcast[4];
+        __syncthreads();
+        if (cell >= 0) {
+          Group g{key_of(c.cell_score(cell)), {-1, -1, -1}};
+          g.cell[cell / kV3Bins] = cell;
+          // only this class, not other members that share its key
+          if (members * (u64)(kThreads * 8) >= (u64)c.vocab) {
+            Group only = g;
+            only.key = 0xffffffffu;  // no out-of-class member can match
+            token = random_in_group(c, only, P.seed, 0x7fffffff, 64);
+            if (token < 0) token = nth_in_group(c, only, nth);
+          } else {
+            Group only = g;
+            only.key = 0xffffffffu;
+            token = nth_in_group(c, only, nth);
+          }
+        }
+        if (token < 0 || token == 0x7fffffff) { token = any_side ? side_arg : 0; status |= 1; }
+      } else if (target < q_cells + q_group) {
+        need_cut_group();
+        const u64 nth = q_cut ? (target - q_cells) / q_cut + 1 : 1;
+        token = nth_in_group(c, cut_group, nth);  // the kept members are the lowest ids
+        if (token == 0x7fffffff) { token = any_side ? side_arg : 0; status |= 1; }
+      } else {
+        SideDrawFill3 fill{&c, kept.cut_key};
+        Selection sd = descend_local<true>(c, fill, 0u, target - q_cells - q_group + 1, -1.0f, 0, 1, 0x7FFu);
+        if (sd.ok) token = (int)(~sd.key);
+        else { token = any_side ? side_arg : 0; status |= 1; }
+      }
+    }
+  }
+  mark(7);
+
+  // ---- D. log-probabilities -------------------------------------------------------------
+  float log_z = 0.f;
+  if (P.n_logprobs >= 0) {
+    log_z = (float)(log((double)q_kept) - (double)kMassShift * 0.6931471805599453);
+    if (tid == 0 && token >= 0 && token < a.vocab)
+      out->logprob = (c.element_score(token, c.logits[token], c.class_of(token)) - m) - log_z;
+    int n_want = min(P.n_logprobs, a.vocab);
+    if ((u64)n_want > n_kept) n_want = (int)n_kept;
+    if (n_want > 0) {
+      Selection sn = select_union3<false, false>(c, kept.cut_key, (u64)n_want, 1.0f);
+      if (sn.ok) {
+        const int need = n_want - (int)sn.above_cnt;  // lowest ids of the group at the N-th key
+        // members above the N-th key: fewer than N tokens in a few classes and side elements
+        if (tid == 0) *c.gbuf_n = 0;
+        __syncthreads();
+        for_each_side3(c, [&](int id, float s) {
+          const uint32_t k = key_of(s);
+          if (k > sn.key) {
+            const int slot = atomicAdd(c.gbuf_n, 1);
+            if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{k, id, 1u, 0u, 0ull};
+          }
+        });
+        // mark the classes above the N-th key in the (free) histogram area, then walk the row
+        uint32_t* marked = reinterpret_cast<uint32_t*>(c.hist);  // kCells bits
+        for (int i = tid; i < (kCells + 31) / 32; i += kThreads) marked[i] = 0;
+        __syncthreads();
+        int any_marked = 0;
+        for_each_cell(c, [&](int cell, uint32_t, float s) {
+          if (key_of(s) > sn.key) { atomicOr(&marked[cell >> 5], 1u << (cell & 31)); any_marked = 1; }
+        });
+        any_marked = __syncthreads_or(any_marked);
+        if (any_marked) {
+          auto probe = [&](int id, uint32_t raw, int cc) {
+            if (cc == 3) return;
+            const int b = v3_bin_of_raw(raw);
+            if (b < 0) return;
+            const int cell = cc * kV3Bins + b;
+            if ((marked[cell >> 5] >> (cell & 31)) & 1u) {
+              const int slot = atomicAdd(c.gbuf_n, 1);
+              if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{key_of(c.cell_score(cell)), id, 1u, 0u, 0ull};
+            }
+          };
+          const int n8 = c.vec ? c.vocab / 8 : 0;
+          for (int i = tid; i < n8; i += kThreads) {
+            uint32_t raw[8], cls16;
+            load_chunk(c, i, raw, cls16);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) probe(8 * i + k, raw[k], (cls16 >> (2 * k)) & 3);
+          }
+          for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) probe(id, c.logits[id], c.class_of(id));
+        }
+        __syncthreads();
+        if (need > 0) {
+          const Group g = sn.key == kept.cut_key && have_cut_group ? cut_group : find_group(c, sn.key);
+          const int last_id = nth_in_group(c, g, (u64)need);
+          emit_group_upto(c, g, last_id == 0x7fffffff ? -1 : last_id);
+        }
+        __syncthreads();
+        if (tid < 32) {
+          const int n = min(*c.gbuf_n, HS_MAX_LOGPROBS);
+          uint32_t kv = 0;
+          int id = 0x7fffffff;
+          if (tid < n) { kv = c.gbuf[tid].key; id = c.gbuf[tid].id; }
+          int pos = 0;
+          for (int j = 0; j < n; ++j) {
+            const uint32_t kj = __shfl_sync(0xffffffffu, kv, j);
+            const int idj = __shfl_sync(0xffffffffu, id, j);
+            if (kj > kv || (kj == kv && idj < id)) ++pos;
+          }
+          if (tid < n) {
+            out->top_ids[pos] = id;
+            out->top_logprobs[pos] = (score_of(kv) - m) - log_z;
+          }
+          if (tid == 0 && n != n_want) status |= 8;
+        }
+      } else {
+        n_want = 0;
+        status |= 1;
+      }
+    }
+    if (tid == 0) out->n_top = n_want;
+  } else if (tid == 0) {
+    out->n_top = 0;
+    out->logprob = 0.f;
+  }
+  mark(8);
+
+  // ---- E. optional dump of the final scores (parity tests) -------------------------------
+  if (a.scores_out) {
+    need_tie_limit();
+    float* dst = a.scores_out + (size_t)c.row * a.vocab;
+    const float ninf = __int_as_float(0xff800000);
+    for (int id = tid; id < c.vocab; id += kThreads) {
+      const float s = c.element_score(id, c.logits[id], c.class_of(id));
+      dst[id] = (c.greedy || kept.has(key_of(s), id)) ? s : ninf;
+    }
+  }
+
+  if (tid == 0) {
+    out->token = token;
+    out->status = status;
+    out->n_kept = (int32_t)n_kept;
+    out->n_after_topk = (int32_t)n_topk;
+    out->n_after_minp = (int32_t)n_minp;
+    out->n_after_topp = (int32_t)n_kept;
+    out->cut_bits = __float_as_uint(score_of(kept.cut_key));
+    out->n_cut_ties = (int32_t)cut_ties;
+    out->row_max = m;
+    out->log_z = log_z;
+    if ((a.flags & HS_SAMPLE_APPEND_TOKEN) && P.slot >= 0 && token >= 0 && token < a.vocab) {
+      if (!slot_append_one(a.pool, P.slot, token)) out->status = status | 2;
+    }
+  }
+  (void)cut_group_cnt;
+  mark(9);
+}
+
+}  // namespace hs

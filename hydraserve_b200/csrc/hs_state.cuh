@@ -1,11 +1,15 @@
 // Device-resident token-count histograms (one per request slot) and the plain-greedy
 // arg-max kernels.
 //
-// A slot holds the sparse form of the `counts` dict the reference builds per row per step
-// (sampling.py:106-110): parallel lists ids[] / cnts[] of the distinct token ids seen so
-// far, stored as (id, count) pairs, plus a dense index pos[token] = 1 + position in the
-// list (0 = unseen) that is touched only when tokens are appended.  The sampling kernel
-// reads just the list (8 bytes per distinct id, coalesced).
+// A slot is the device form of the `counts` dict the reference rebuilds per row per step
+// (sampling.py:106-110).  It holds
+//   pairs[]   the distinct token ids seen so far with their counts, (id, count), 8 bytes each
+//   pos[]     dense index: pos[token] = 1 + position in pairs (0 = unseen); touched only
+//             when tokens are appended
+//   cls[]     dense 2-bit class per token, min(count, 3), sixteen tokens per 32-bit word: what
+//             the bf16 sampling kernel streams next to the logits (V/4 bytes per row)
+//   heavy[]   the ids whose count reached 3: the only tokens whose exact count the bf16
+//             kernel has to look up (through pos and pairs)
 #pragma once
 
 #include "hs_common.cuh"
@@ -17,11 +21,31 @@ struct Pool {
   int2* pairs;     // [slots_total, unique_cap] (token id, count)
   int32_t* n;      // [slots_total]
   int32_t* pos;    // [slots_total, pos_stride]
+  uint32_t* cls;   // [slots_total, cls_stride] 2-bit classes
+  int32_t* heavy;  // [slots_total, unique_cap]
+  int32_t* n_heavy;  // [slots_total]
   int32_t* error;  // [1] sticky: 1 = a slot overflowed unique_cap
   int slots_total;
   int unique_cap;
   long long pos_stride;
+  long long cls_stride;  // words per slot
 };
+
+// Sets the 2-bit class of `token` to min(count, 3); returns the previous class.
+__device__ __forceinline__ uint32_t set_class(uint32_t* cls, int token, int count) {
+  const uint32_t want = (uint32_t)min(count, 3);
+  uint32_t* word = cls + (token >> 4);
+  const int shift = (token & 15) * 2;
+  uint32_t old = *word;
+  while (true) {
+    const uint32_t cur = (old >> shift) & 3u;
+    if (cur >= want) return cur;  // classes only grow between resets
+    const uint32_t next = (old & ~(3u << shift)) | (want << shift);
+    const uint32_t seen = atomicCAS(word, old, next);
+    if (seen == old) return cur;
+    old = seen;
+  }
+}
 
 // Empties each listed slot by walking its id list (no dense clear).
 __global__ void slots_reset_kernel(Pool p, const int32_t* slots, int n_slots) {
@@ -30,12 +54,16 @@ __global__ void slots_reset_kernel(Pool p, const int32_t* slots, int n_slots) {
   const int n = min(p.n[s], p.unique_cap);
   const int2* pairs = p.pairs + (size_t)s * p.unique_cap;
   int32_t* pos = p.pos + (size_t)s * p.pos_stride;
+  uint32_t* cls = p.cls + (size_t)s * p.cls_stride;
   for (int j = threadIdx.x; j < n; j += blockDim.x) {
     const int id = pairs[j].x;
-    if (id >= 0 && id < p.pos_stride) pos[id] = 0;
+    if (id >= 0 && id < p.pos_stride) {
+      pos[id] = 0;
+      cls[id >> 4] = 0;  // every non-zero field of the word belongs to a listed id
+    }
   }
   __syncthreads();
-  if (threadIdx.x == 0) p.n[s] = 0;
+  if (threadIdx.x == 0) { p.n[s] = 0; p.n_heavy[s] = 0; }
 }
 
 // Pass 1 of an append: give every token id not yet in the slot a list position.
@@ -79,6 +107,61 @@ __global__ void slots_count_kernel(Pool p, const int32_t* tokens, const int32_t*
     const int q = pos[t];
     if (q > 0) atomicAdd(&pairs[q - 1].y, 1);
   }
+}
+
+// Pass 3 of an append: with the counts final, refresh the 2-bit classes and list the ids
+// whose count reached 3 (the thread that moves a class to 3 does the listing).
+__global__ void slots_classify_kernel(Pool p, const int32_t* tokens, const int32_t* offsets,
+                                      const int32_t* slots, int n_slots, int vocab) {
+  const int row = blockIdx.y;
+  const int s = row < n_slots ? slots[row] : -1;
+  if (s < 0 || s >= p.slots_total) return;
+  const int t0 = offsets[row], t1 = offsets[row + 1];
+  const int2* pairs = p.pairs + (size_t)s * p.unique_cap;
+  const int32_t* pos = p.pos + (size_t)s * p.pos_stride;
+  uint32_t* cls = p.cls + (size_t)s * p.cls_stride;
+  int32_t* heavy = p.heavy + (size_t)s * p.unique_cap;
+  for (int j = t0 + blockIdx.x * blockDim.x + threadIdx.x; j < t1; j += gridDim.x * blockDim.x) {
+    const int t = tokens[j];
+    if (t < 0 || t >= vocab || t >= p.pos_stride) continue;
+    const int q = pos[t];
+    if (q <= 0) continue;
+    const int count = pairs[q - 1].y;
+    const uint32_t before = set_class(cls, t, count);
+    if (count >= 3 && before < 3u) {
+      const int idx = atomicAdd(&p.n_heavy[s], 1);
+      if (idx < p.unique_cap) heavy[idx] = t;
+    }
+  }
+}
+
+// One token appended by a single thread (the sampling kernel's epilogue).
+__device__ __forceinline__ bool slot_append_one(const Pool& p, int s, int token) {
+  int2* pairs = p.pairs + (size_t)s * p.unique_cap;
+  int32_t* pos = p.pos + (size_t)s * p.pos_stride;
+  uint32_t* cls = p.cls + (size_t)s * p.cls_stride;
+  int count;
+  const int q = pos[token];
+  if (q > 0) {
+    count = (pairs[q - 1].y += 1);
+  } else {
+    const int n = p.n[s];
+    if (n >= p.unique_cap) return false;
+    pairs[n] = make_int2(token, 1);
+    pos[token] = n + 1;
+    p.n[s] = n + 1;
+    count = 1;
+  }
+  if (count <= 3) {
+    uint32_t* word = cls + (token >> 4);
+    const int shift = (token & 15) * 2;
+    *word = (*word & ~(3u << shift)) | ((uint32_t)count << shift);
+    if (count == 3) {
+      const int h = p.n_heavy[s];
+      if (h < p.unique_cap) { (p.heavy + (size_t)s * p.unique_cap)[h] = token; p.n_heavy[s] = h + 1; }
+    }
+  }
+  return true;
 }
 
 // ---- plain greedy: arg max per row, lowest id on ties (reference sampling.py:69-73) ---

@@ -121,7 +121,7 @@ def test_bf16_rows_match_checker_on_the_general_kernel(general_sampler, name):
 
 
 def test_bf16_kernel_is_the_one_used_for_bf16(sampler):
-    assert sampler.query(4, 151_936, 1) == 1 and sampler.query(4, 248_320, 1) == 1
+    assert sampler.query(4, 151_936, 1) >= 1 and sampler.query(4, 248_320, 1) >= 1
     assert sampler.query(4, 151_936, 0) == 0
 
 
