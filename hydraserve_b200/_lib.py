@@ -30,7 +30,12 @@ ROW_OUT = np.dtype([
     ("cut_bits", "<u4"), ("n_cut_ties", "<i4"), ("row_max", "<f4"), ("log_z", "<f4"),
     ("top_ids", "<i4", (HS_MAX_LOGPROBS,)), ("top_logprobs", "<f4", (HS_MAX_LOGPROBS,)),
 ], align=True)
-assert ROW_PARAMS.itemsize == 48 and ROW_OUT.itemsize == 208
+HS_SHARD_CAND = 64
+SHARD_REC = np.dtype([
+    ("row_max", "<f4"), ("pad", "<f4"), ("z_mass", "<u8"), ("n", "<i4"), ("status", "<i4"),
+    ("ids", "<i4", (HS_SHARD_CAND,)), ("scores", "<f4", (HS_SHARD_CAND,)),
+], align=True)
+assert ROW_PARAMS.itemsize == 48 and ROW_OUT.itemsize == 208 and SHARD_REC.itemsize == 536
 
 EXPORTS = {
     # name: (restype, argtypes)
@@ -51,6 +56,10 @@ EXPORTS = {
     "hs_greedy_noalloc_error": (C.c_char_p, []),
     "hs_sample_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int,
                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "hs_sharded_partial": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int,
+                                     C.c_void_p, C.c_void_p, C.c_void_p]),
+    "hs_sharded_merge": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                   C.c_void_p, C.c_void_p, C.c_void_p]),
     "hs_query": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "hs_debug_phase_clocks": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
 }

@@ -17,12 +17,16 @@
 #include "hs_row_kernel.cuh"
 #include "hs_row_bf16.cuh"
 #include "hs_row_v3.cuh"
+#include "hs_row_topk.cuh"
+#include "hs_sharded.cuh"
+#include "hs_row_bf16_kernel.cuh"
 
 namespace {
 
 using hs::u64;
 
 constexpr int kGreedyMaxChunks = 64;
+constexpr int kMaxSplit = 4;  // CTAs per row of the candidate kernel
 
 struct DeviceGuard {
   int prev = -1;
@@ -64,6 +68,11 @@ struct hs_sampler {
   int force_general = 0;  // route bf16 rows through the general (fp32-stage) kernel too
   int force_cluster16 = 0;  // route bf16 rows through the cluster-resident bf16 kernel
   int2* side_pair = nullptr;  // [batch_max, side_cap] side lists of the bf16 kernel
+  hs::ClassEntry* clist = nullptr;
+  unsigned char* needs_count = nullptr;  // [batch_max]
+  unsigned long long* split_lists = nullptr;  // [batch_max, kMaxSplit, kSplitCap]
+  int* split_n = nullptr;
+  int* split_ticket = nullptr;  // [batch_max, kCells] class lists of the bf16 kernel
   int side_cap = 0;
   unsigned long long* phase_clocks = nullptr;  // HS_PHASE_CLOCKS=1: per-row phase timestamps
   hs::Pool pool{};
@@ -163,10 +172,17 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
     a.logits = logits; a.dtype = dtype; a.row_stride = row_stride; a.vocab = vocab; a.slice = 0;
     a.params = params; a.out = out; a.noise = noise; a.scores_out = scores_out; a.gstage = nullptr;
     a.pool = h->pool; a.flags = flags;
-    hs::RowV3Args a3{a, h->side_pair, h->side_cap, h->phase_clocks};
+    // small batches: several CTAs stream each row so that every SM has work
+    int split = (2 * h->sm_count + batch - 1) / batch;
+    split = std::max(1, std::min(split, kMaxSplit));
+    if (vocab < split * 2 * hs::kPrefix) split = 1;
+    hs::RowV3Args a3{a, h->clist, h->side_pair, h->side_cap, h->phase_clocks, h->needs_count,
+                     split, h->split_lists, h->split_n, h->split_ticket};
+    hs::row_kernel_topk<<<dim3((unsigned)split, (unsigned)batch), hs::kThreads, hs::layout_cand().total, stream>>>(a3);
+    HS_CUDA(h, cudaGetLastError());
     hs::row_kernel_v3<<<(unsigned)batch, hs::kThreads, hs::layout_v3().total, stream>>>(a3);
     HS_CUDA(h, cudaGetLastError());
-    h->launches += 1;
+    h->launches += 2;
     return HS_OK;
   }
   const bool bf16_path = dtype == HS_DTYPE_BF16 && make_plan16(h, vocab, plan);
@@ -244,7 +260,8 @@ int launch_append(hs_sampler* h, const int32_t* tokens, const int32_t* offsets, 
 
 void release(hs_sampler* h) {
   cudaFree(h->pool.pairs); cudaFree(h->pool.cls); cudaFree(h->pool.heavy); cudaFree(h->pool.n_heavy); cudaFree(h->pool.n); cudaFree(h->pool.pos);
-  cudaFree(h->side_pair); cudaFree(h->phase_clocks);
+  cudaFree(h->side_pair); cudaFree(h->clist); cudaFree(h->needs_count);
+  cudaFree(h->split_lists); cudaFree(h->split_n); cudaFree(h->split_ticket); cudaFree(h->phase_clocks);
   cudaFree(h->pool.error); cudaFree(h->greedy_partials); cudaFree(h->gstage); cudaFree(h->d_logits);
   cudaFree(h->d_params); cudaFree(h->d_out); cudaFree(h->d_hist); cudaFree(h->d_offsets); cudaFree(h->d_slots);
   if (h->h_params) cudaFreeHost(h->h_params);
@@ -374,6 +391,9 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   if (cudaFuncSetAttribute(hs::row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_optin) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::row_kernel_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_optin) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::row_kernel_v3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_v3().total) != cudaSuccess) return bail(HS_ERR_CUDA);
+  if (cudaFuncSetAttribute(hs::row_kernel_topk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_cand().total) != cudaSuccess) return bail(HS_ERR_CUDA);
+  if (cudaFuncSetAttribute(hs::shard_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_cand().total) != cudaSuccess) return bail(HS_ERR_CUDA);
+  if (cudaFuncSetAttribute(hs::shard_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_cand().total) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (const char* fg = std::getenv("HS_FORCE_GENERAL")) h->force_general = std::atoi(fg) != 0;
   if (const char* fc16 = std::getenv("HS_FORCE_CLUSTER16")) h->force_cluster16 = std::atoi(fc16) != 0;
 
@@ -397,6 +417,13 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   ok = ok && cudaMalloc(&h->d_slots, (size_t)batch_max * sizeof(int32_t)) == cudaSuccess;
   h->side_cap = (vocab_max + 7) & ~7;
   ok = ok && cudaMalloc(&h->side_pair, (size_t)batch_max * h->side_cap * sizeof(int2)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->needs_count, (size_t)batch_max) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->split_lists, (size_t)batch_max * kMaxSplit * hs::kSplitCap * sizeof(unsigned long long)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->split_n, (size_t)batch_max * kMaxSplit * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->split_ticket, (size_t)batch_max * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMemset(h->split_ticket, 0, (size_t)batch_max * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMemset(h->needs_count, 0, (size_t)batch_max) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->clist, (size_t)batch_max * hs::kCells * sizeof(hs::ClassEntry)) == cudaSuccess;
   ok = ok && cudaMallocHost(&h->h_params, (size_t)batch_max * sizeof(hs_row_params)) == cudaSuccess;
   ok = ok && cudaMallocHost(&h->h_small, (2 * (size_t)batch_max + 1) * sizeof(int32_t)) == cudaSuccess;
   if (const char* pc = std::getenv("HS_PHASE_CLOCKS")) {
@@ -573,6 +600,43 @@ int hs_sample_host(hs_sampler* h, const void* logits, int dtype, int64_t row_str
   if (rc != HS_OK) return rc;
   HS_CUDA(h, cudaMemcpyAsync(out, h->d_out, (size_t)batch * sizeof(hs_row_out), cudaMemcpyDeviceToHost, stream));
   HS_CUDA(h, cudaStreamSynchronize(stream));
+  return HS_OK;
+}
+
+int hs_sharded_partial(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch,
+                       int vocab_local, int vocab_offset, const hs_row_params* params,
+                       hs_shard_rec* recs_out, void* stream) {
+  int rc = check_common(h, logits, dtype, batch, vocab_local);
+  if (rc != HS_OK) return rc;
+  if (dtype != HS_DTYPE_BF16) return fail(h, HS_ERR_UNSUPPORTED, "sharded sampling takes bf16 slices");
+  if (batch == 0) return HS_OK;
+  if (!params || !recs_out) return fail(h, HS_ERR_INVALID, "params / recs_out is null");
+  if (row_stride < vocab_local || vocab_offset < 0) return fail(h, HS_ERR_INVALID, "bad row_stride / vocab_offset");
+  DeviceGuard guard(h->device);
+  hs::ShardArgs a{};
+  a.base.logits = logits; a.base.dtype = dtype; a.base.row_stride = row_stride; a.base.vocab = vocab_local;
+  a.base.params = params; a.base.pool = h->pool;
+  a.vocab_offset = vocab_offset;
+  a.recs = recs_out;
+  hs::shard_partial_kernel<<<(unsigned)batch, hs::kThreads, hs::layout_cand().total, (cudaStream_t)stream>>>(a);
+  HS_CUDA(h, cudaGetLastError());
+  h->launches += 1;
+  return HS_OK;
+}
+
+int hs_sharded_merge(hs_sampler* h, const hs_shard_rec* recs, int ranks, int batch, int vocab_total,
+                     const hs_row_params* params, hs_row_out* out, const float* noise, float* full_lse,
+                     void* stream) {
+  if (!h) return HS_ERR_INVALID;
+  if (batch < 0 || ranks < 1 || ranks > 64 || vocab_total < 1) return fail(h, HS_ERR_INVALID, "bad ranks / batch / vocab_total");
+  if (ranks * HS_SHARD_CAND > hs::kCandCap) return fail(h, HS_ERR_CAPACITY, "too many ranks for one merge");
+  if (batch == 0) return HS_OK;
+  if (!recs || !params || !out) return fail(h, HS_ERR_INVALID, "recs / params / out is null");
+  DeviceGuard guard(h->device);
+  hs::MergeArgs a{recs, ranks, batch, vocab_total, params, out, noise, full_lse};
+  hs::shard_merge_kernel<<<(unsigned)batch, hs::kThreads, hs::layout_cand().total, (cudaStream_t)stream>>>(a);
+  HS_CUDA(h, cudaGetLastError());
+  h->launches += 1;
   return HS_OK;
 }
 

@@ -1,0 +1,408 @@
+// Rows with a small top_k: the candidate path, and the list finisher shared with the
+// vocabulary-sharded merge.
+//
+// With top_k = k, only the k highest scores (and ties at the k-th) can ever be sampled or
+// reported, so nothing needs counting: the row is streamed once from HBM and compared, two
+// tokens per instruction, against a lower bound of the k-th highest score.  The bound comes
+// from the row itself: the first 2,048 tokens are all scored, their k-th highest score is a
+// valid bound for the whole row, and whenever the candidate list grows past 2,048 entries
+// the bound is raised to the list's k-th highest score and the list is compacted.  Scores
+// grow with the raw value inside a history-count class, so the bound turns into one raw
+// threshold per class (binary search over the 65,536 bf16 values); a token whose history
+// count is 3 or more is always scored exactly.
+//
+// What is left, at most a few thousand (score key, token id) pairs in shared memory, is
+// sorted by (score descending, id ascending).  In that order every filter of the reference
+// is a prefix: top-k with ties, min-p, top-p (a cut inside a tie group keeps the lowest ids),
+// the top-N log-probabilities; the draw is an inverse CDF over exact integer masses.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "hs_common.cuh"
+#include "hs_select.cuh"
+#include "hs_row_v3.cuh"
+
+namespace hs {
+
+constexpr int kTopKMax = 256;      // largest top_k served by the candidate path
+constexpr int kCandCap = 4096;     // candidate list capacity (shared memory, 8 bytes each)
+constexpr int kCandSoft = 2048;    // raise the bound once the list is this long
+constexpr int kPrefix = 2048;      // tokens scored unconditionally to get the first bound
+
+// (score key << 32) | ~id : sorting these descending orders by score, then by ascending id
+__device__ __forceinline__ u64 cand_pack(uint32_t key, int id) {
+  return ((u64)key << 32) | (uint32_t)(~(uint32_t)id);
+}
+__device__ __forceinline__ uint32_t cand_key(u64 p) { return (uint32_t)(p >> 32); }
+__device__ __forceinline__ int cand_id(u64 p) { return (int)(~(uint32_t)(p & 0xffffffffu)); }
+
+// Signed 16-bit image of bf16 bits whose integer order is the float order.
+__device__ __forceinline__ int t16_of_raw(uint32_t raw) {
+  const uint32_t t = raw ^ ((raw & 0x8000u) ? 0x7fffu : 0u);
+  return (int)(short)t;
+}
+__device__ __forceinline__ uint32_t raw_of_t16(int t) {
+  const uint32_t u = (uint32_t)t & 0xffffu;
+  return u ^ ((u & 0x8000u) ? 0x7fffu : 0u);
+}
+
+struct CandCtx {
+  u64* cand;        // [kCandCap]
+  int* n;           // entries in the list
+  int* lost;        // set when an append did not fit
+  uint32_t* count;  // [kBins] radix counters
+  int* thr;         // [4] per-class signed 16-bit thresholds
+  unsigned long long* dbg;  // optional phase clocks of this row (tuning aid), or null
+};
+
+// The k-th highest key among the n list entries (n >= k >= 1): three count-only radix levels.
+__device__ uint32_t cand_kth_key(Exchange& x, CandCtx& L, int n, int k) {
+  const int tid = threadIdx.x;
+  uint32_t prefix = 0;
+  int want = k;
+  for (int level = 0; level < 3; ++level) {
+    const int shift = level_shift(level), bits = level_bits(level);
+    const uint32_t mask = (1u << bits) - 1u;
+    for (int b = tid; b < kBins; b += kThreads) L.count[b] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += kThreads) {
+      const uint32_t key = cand_key(L.cand[i]);
+      if (level > 0 && (key >> (shift + bits)) != prefix) continue;
+      atomicAdd(&L.count[(key >> shift) & mask], 1u);
+    }
+    __syncthreads();
+    constexpr int kPer = kBins / kThreads;
+    const int hi = kBins - 1 - kPer * tid;
+    u64 sum = 0;
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) sum += L.count[hi - u];
+    const u64 incl = warp_scan_u64(sum);
+    u64 pre, pu, tot, tu;
+    block_warp_prefix2(x, shfl_u64(incl, 31), 0, pre, pu, tot, tu);
+    u64 ex = pre + incl - sum;
+    if (ex < (u64)want && (u64)want <= ex + sum) {
+#pragma unroll
+      for (int u = 0; u < kPer; ++u) {
+        const u64 bc = L.count[hi - u];
+        if ((u64)want <= ex + bc) {
+          x.bcast[0] = (u64)(hi - u);
+          x.bcast[1] = ex;
+          break;
+        }
+        ex += bc;
+      }
+    }
+    __syncthreads();
+    prefix = (prefix << bits) | (uint32_t)x.bcast[0];
+    want -= (int)x.bcast[1];
+    __syncthreads();
+  }
+  return prefix;
+}
+
+// Drops list entries with key < bound (in place).  Returns the new length.
+__device__ int cand_compact(CandCtx& L, int n, uint32_t bound) {
+  const int tid = threadIdx.x;
+  constexpr int kPer = kCandCap / kThreads;
+  u64 mine[kPer];
+#pragma unroll
+  for (int u = 0; u < kPer; ++u) {
+    const int i = tid + u * kThreads;
+    mine[u] = i < n ? L.cand[i] : 0ull;
+  }
+  __syncthreads();
+  if (tid == 0) *L.n = 0;
+  __syncthreads();
+#pragma unroll
+  for (int u = 0; u < kPer; ++u) {
+    const int i = tid + u * kThreads;
+    if (i < n && mine[u] != 0ull && cand_key(mine[u]) >= bound) L.cand[atomicAdd(L.n, 1)] = mine[u];
+  }
+  __syncthreads();
+  return *L.n;
+}
+
+// Per count class, the lowest raw value (as signed 16-bit image) whose score reaches `bound`.
+__device__ void cand_thresholds(const Ctx3& c, CandCtx& L, uint32_t bound) {
+  if (threadIdx.x < 3) {
+    const int cc = threadIdx.x;
+    int lo = -32768, hi = 32767;  // find the lowest t with key(score(t, cc)) >= bound; 32768 if none
+    if (key_of(c.score_of(raw_of_t16(hi), cc)) < bound) {
+      lo = 32768;
+    } else {
+      while (lo < hi) {
+        const int mid = lo + ((hi - lo) >> 1);
+        if (key_of(c.score_of(raw_of_t16(mid), cc)) >= bound) hi = mid; else lo = mid + 1;
+      }
+    }
+    // -0.0 scores like +0.0 but sits one step below it in the integer order
+    if (lo == 0) lo = -1;
+    L.thr[cc] = lo;
+  }
+  __syncthreads();
+}
+
+// Streams the row and leaves in L every token whose score can be among the top k (ties at
+// the k-th included).  Returns the list length, or -1 when the list overflowed (the caller
+// then uses the counting path).
+__device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
+  const int tid = threadIdx.x;
+  if (tid == 0) { *L.n = 0; *L.lost = 0; }
+  __syncthreads();
+  // A hit is stored unscored, (raw bits, count class, id), by the one lane that found it;
+  // scores are computed later for the whole list at once with every lane busy.
+  auto push = [&](int id, uint32_t raw, int cc) {
+    const int slot = atomicAdd(L.n, 1);
+    if (slot < kCandCap) L.cand[slot] = ((u64)raw << 48) | ((u64)cc << 32) | (uint32_t)id;
+    else *L.lost = 1;
+  };
+  auto score_pending = [&](int from, int to) {
+    for (int i = from + tid; i < to; i += kThreads) {
+      const u64 e = L.cand[i];
+      const int id = (int)(uint32_t)e;
+      int cc = (int)(e >> 32) & 7;
+      bool valid = true;
+      if (cc == 4) {  // found by the stream, which does not look at count classes
+        cc = c.class_of(id);
+        valid = cc != 3;  // tokens held three times or more come from the request's list
+      }
+      L.cand[i] = valid ? cand_pack(key_of(c.element_score(id, (uint32_t)(e >> 48), cc)), id) : 0ull;
+    }
+    __syncthreads();
+  };
+  // 1. the first tokens are all candidates; their k-th highest score bounds the row's.
+  // Tokens the history holds three times or more are candidates by definition (their score
+  // does not follow from a class threshold); they come from the request's list, not the stream.
+  const int n_prefix = min(c.hi - c.lo, kPrefix);
+  for (int id = c.lo + tid; id < c.lo + n_prefix; id += kThreads) {
+    const int cc = c.class_of(id);
+    if (cc != 3) push(id, c.logits[id], cc);
+  }
+  if (c.cls) {
+    const int n_heavy = min(c.pool.n_heavy[c.slot], c.pool.unique_cap);
+    const int32_t* heavy = c.pool.heavy + (size_t)c.slot * c.pool.unique_cap;
+    for (int j = tid; j < n_heavy; j += kThreads) {
+      const int id = heavy[j];
+      if (id >= c.lo && id < c.hi) push(id, c.logits[id], 3);
+    }
+  }
+  __syncthreads();
+  if (*L.lost) return -1;
+  int n = min(*L.n, kCandCap);
+  score_pending(0, n);
+  if (L.dbg && tid == 0) L.dbg[3] = clock64();
+  uint32_t bound = 0;
+  if (n >= k) {
+    bound = cand_kth_key(*c.x, L, n, k);
+    n = cand_compact(L, n, bound);
+  }
+  if (n_prefix == c.hi - c.lo) return n;
+  cand_thresholds(c, L, bound);
+  if (L.dbg && tid == 0) L.dbg[4] = clock64();
+  int refreshes = 0;
+  // 2. the rest of the row: eight tokens per 128-bit load, one native bf16x2 comparison per
+  // two tokens against the most permissive class threshold; the rare hit is looked at closely
+  const int first8 = (c.lo + n_prefix) / 8;  // lo and kPrefix are multiples of 8
+  const int n8 = c.vec ? c.hi / 8 : first8;
+  const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
+  constexpr int kInFlight = 8;
+  int n_scored = n;
+  for (int base = first8; base < n8; base += kInFlight * kThreads) {
+    // threshold as a bf16 value (NaN = nothing passes, -inf = everything passes)
+    int t_min = L.thr[0];
+    if (c.cls) t_min = min(t_min, min(L.thr[1], L.thr[2]));
+    uint32_t tb = t_min > 32640 ? 0x7fc0u : raw_of_t16(t_min);
+    if (t_min <= -32641) tb = 0xff80u;
+    const uint32_t pair = tb * 0x10001u;
+    const __nv_bfloat162 thr2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
+    uint4 w[kInFlight];
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      const int i = base + tid + u * kThreads;
+      if (i < n8) w[u] = __ldcs(src4 + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      const int i = base + tid + u * kThreads;
+      if (i >= n8) break;
+      const uint32_t m0 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].x), thr2);
+      const uint32_t m1 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].y), thr2);
+      const uint32_t m2 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].z), thr2);
+      const uint32_t m3 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].w), thr2);
+      if (!(m0 | m1 | m2 | m3)) continue;  // the common case
+      uint32_t hits = ((m0 & 1u) | ((m0 >> 15) & 2u)) | (((m1 & 1u) | ((m1 >> 15) & 2u)) << 2) |
+                      (((m2 & 1u) | ((m2 >> 15) & 2u)) << 4) | (((m3 & 1u) | ((m3 >> 15) & 2u)) << 6);
+#pragma unroll 1
+      while (hits) {
+        const int q = __ffs(hits) - 1;
+        hits &= hits - 1;
+        const uint32_t word = q < 2 ? w[u].x : (q < 4 ? w[u].y : (q < 6 ? w[u].z : w[u].w));
+        const uint32_t raw = (word >> (16 * (q & 1))) & 0xffffu;
+        push(8 * i + q, raw, 4);
+      }
+    }
+    // raise the bound when the list is getting long (block-uniform decision)
+    if (__syncthreads_or(*L.n >= kCandSoft)) {
+      if (*L.lost) return -1;
+      n = min(*L.n, kCandCap);
+      score_pending(n_scored, n);
+      bound = cand_kth_key(*c.x, L, n, k);
+      n = cand_compact(L, n, bound);
+      n_scored = n;
+      cand_thresholds(c, L, bound);
+      ++refreshes;
+    }
+  }
+  __syncthreads();
+  if (L.dbg && tid == 0) { L.dbg[5] = clock64(); L.dbg[6] = (unsigned long long)refreshes; L.dbg[7] = (unsigned long long)*L.n; }
+  // scalar tail (or the whole remainder of a row that is not 16-byte aligned)
+  for (int id = max(n8 * 8, c.lo + n_prefix) + tid; id < c.hi; id += kThreads) {
+    const uint32_t raw = c.logits[id];
+    const int cc = c.class_of(id);
+    if (cc != 3 && t16_of_raw(raw) >= L.thr[cc]) push(id, raw, cc);
+  }
+  __syncthreads();
+  if (*L.lost) return -1;
+  n = min(*L.n, kCandCap);
+  score_pending(n_scored, n);
+  return n;
+}
+
+// Sorts the first n list entries descending (bitonic, n padded to a power of two with zeros).
+__device__ void cand_sort(CandCtx& L, int n) {
+  int p = 1;
+  while (p < n) p <<= 1;
+  for (int i = n + threadIdx.x; i < p; i += kThreads) L.cand[i] = 0ull;
+  __syncthreads();
+  for (int size = 2; size <= p; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < p / 2; t += kThreads) {
+        const int lo = 2 * t - (t & (stride - 1));
+        const int hi = lo + stride;
+        const bool desc = (lo & size) == 0;
+        const u64 a = L.cand[lo], b = L.cand[hi];
+        if ((a < b) == desc) { L.cand[lo] = b; L.cand[hi] = a; }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+struct FinishOut {
+  int token;
+  int status;
+  u64 n_topk, n_minp, n_kept;
+  long long cut_ties;
+  uint32_t cut_key;
+  float m, log_z;
+};
+
+// Everything after top-k on a list sorted by (score descending, id ascending): min-p, top-p,
+// draw, log-probabilities.  n = tokens that survived top-k (ties included), n >= 1.
+// `mass` is scratch for n 64-bit values.
+__device__ FinishOut finish_sorted(Exchange& x, const u64* cand, u64* mass, int n, const hs_row_params& P,
+                                   const float* noise_row, hs_row_out* out) {
+  const int tid = threadIdx.x;
+  FinishOut r;
+  r.status = 0;
+  r.n_topk = (u64)n;
+  const float m = score_of(cand_key(cand[0]));
+  r.m = m;
+  // masses and their inclusive prefix, each thread owning a contiguous run of entries
+  const int per = (n + kThreads - 1) / kThreads;
+  const int i0 = min(tid * per, n), i1 = min(i0 + per, n);
+  u64 run = 0;
+  for (int i = i0; i < i1; ++i) { run += mass_of(score_of(cand_key(cand[i])), m); mass[i] = run; }
+  u64 incl = warp_scan_u64(run);
+  u64 pre, pu, z1, tu;
+  block_warp_prefix2(x, shfl_u64(incl, 31), 0, pre, pu, z1, tu);
+  const u64 my_off = pre + incl - run;
+  for (int i = i0; i < i1; ++i) mass[i] += my_off;  // mass[i] = inclusive cumulative mass
+  __syncthreads();
+  // min-p: the passing tokens are a prefix
+  int n1 = n;
+  if (P.min_p > 0.0f) {
+    const float z1f = mass_to_float(z1);
+    const float thr = __fmul_rn(__fdiv_rn(1.0f, z1f), P.min_p);
+    u64 pass = 0, unused = 0;
+    for (int i = tid; i < n; i += kThreads) {
+      const float s = score_of(cand_key(cand[i]));
+      pass += !(__fdiv_rn(expf(s - m), z1f) < thr) ? 1 : 0;
+    }
+    block_sum2(x, pass, unused);
+    n1 = max(1, (int)pass);
+  }
+  r.n_minp = (u64)n1;
+  // top-p: shortest prefix whose mass reaches the target
+  int n2 = n1;
+  r.cut_ties = -1;
+  if (P.top_p < 1.0f) {
+    const u64 z2 = mass[n1 - 1];
+    const u64 target = top_p_target(z2, P.top_p);
+    u64 below = 0, unused = 0;
+    for (int i = tid; i < n1; i += kThreads) below += mass[i] < target ? 1 : 0;
+    block_sum2(x, below, unused);
+    n2 = min(n1, (int)below + 1);
+    const uint32_t ck = cand_key(cand[n2 - 1]);
+    u64 ties = 0;
+    for (int i = tid; i < n2; i += kThreads) ties += cand_key(cand[i]) == ck ? 1 : 0;
+    block_sum2(x, ties, unused);
+    r.cut_ties = (long long)ties;
+  }
+  r.n_kept = (u64)n2;
+  r.cut_key = cand_key(cand[n2 - 1]);
+  const u64 z3 = mass[n2 - 1];
+  // draw
+  if (noise_row) {
+    const float zf = mass_to_float(z3);
+    u64 best = 0;
+    for (int i = tid; i < n2; i += kThreads) {
+      const int id = cand_id(cand[i]);
+      const float p = __fdiv_rn(expf(score_of(cand_key(cand[i])) - m), zf);
+      const float ratio = __fdiv_rn(p, noise_row[id]);
+      const u64 packed = ((u64)__float_as_uint(ratio) << 32) | (uint32_t)(~(uint32_t)id);
+      best = packed > best ? packed : best;
+    }
+    best = block_max_u64(x, best);
+    r.token = (int)(~(uint32_t)(best & 0xffffffffu));
+  } else {
+    const Philox4 ph = philox4x32_10(0u, 0u, 0u, 0u, (uint32_t)P.seed, (uint32_t)(P.seed >> 32));
+    const u64 target = __umul64hi(((u64)ph.v[0] << 32) | ph.v[1], z3);
+    u64 le = 0, unused = 0;
+    for (int i = tid; i < n2; i += kThreads) le += mass[i] <= target ? 1 : 0;
+    block_sum2(x, le, unused);
+    r.token = cand_id(cand[min((int)le, n2 - 1)]);
+  }
+  // log-probabilities over the kept set
+  r.log_z = 0.f;
+  if (P.n_logprobs >= 0) {
+    r.log_z = (float)(log((double)z3) - (double)kMassShift * 0.6931471805599453);
+    const int n_want = min(P.n_logprobs, n2);
+    for (int i = tid; i < n2; i += kThreads) {
+      const float lp = (score_of(cand_key(cand[i])) - m) - r.log_z;
+      if (i < n_want) { out->top_ids[i] = cand_id(cand[i]); out->top_logprobs[i] = lp; }
+      if (cand_id(cand[i]) == r.token) out->logprob = lp;
+    }
+    if (tid == 0) out->n_top = n_want;
+  } else if (tid == 0) {
+    out->n_top = 0;
+    out->logprob = 0.f;
+  }
+  return r;
+}
+
+__device__ __forceinline__ void write_finish(const FinishOut& r, hs_row_out* out) {
+  out->token = r.token;
+  out->status = r.status;
+  out->n_kept = (int32_t)r.n_kept;
+  out->n_after_topk = (int32_t)r.n_topk;
+  out->n_after_minp = (int32_t)r.n_minp;
+  out->n_after_topp = (int32_t)r.n_kept;
+  out->cut_bits = __float_as_uint(score_of(r.cut_key));
+  out->n_cut_ties = (int32_t)r.cut_ties;
+  out->row_max = r.m;
+  out->log_z = r.log_z;
+}
+
+}  // namespace hs

@@ -39,6 +39,7 @@ constexpr uint32_t kV3Base = 113u << 7;       // smallest binned magnitude: 2^-1
 constexpr int kV3ListCap = 128;               // members resolved by sorting
 constexpr int kV3RareCap = 512;               // out-of-window tokens remembered before a sweep
 constexpr int kV3PhaseSlots = 12;
+constexpr int kSplitCap = 4096;               // candidate entries one CTA of a split row can hand over
 
 struct V3Entry {
   uint32_t key;  // 32-bit key of the score
@@ -56,11 +57,27 @@ struct LocalHist {
   }
 };
 
+// A non-empty class with its score key and mass, computed once per row.
+struct __align__(16) ClassEntry {
+  uint32_t key;   // 32-bit key of the class score
+  uint32_t cnt;   // tokens in the class
+  uint32_t cell;  // count class * kV3Bins + bin
+  uint32_t pad;
+  u64 q;          // mass of one token
+  u64 w;          // cnt * q
+};
+
 struct RowV3Args {
   RowKernelArgs base;
+  ClassEntry* clist;  // [batch, kCells] scratch: the row's non-empty classes
   int2* s_pair;   // [batch, s_cap] side lists: (token id or -1, fp32 bits of the score)
   int s_cap;
   unsigned long long* phase_clocks;  // [batch, kV3PhaseSlots] or null
+  unsigned char* needs_count;        // [batch] set by row_kernel_topk when a row must be counted after all
+  int split;                         // CTAs per row in row_kernel_topk
+  unsigned long long* split_lists;   // [batch, split, kSplitCap] candidate lists of the row's CTAs
+  int* split_n;                      // [batch, split] their lengths
+  int* split_ticket;                 // [batch] arrival counter (returns to 0)
 };
 
 struct LayoutV3 {
@@ -103,6 +120,7 @@ struct Ctx3 {
   V3Entry* list;     // sorted members
   int* gbuf_n;
   int row, vocab;
+  int lo, hi;                    // token range this CTA streams in the candidate path (lo a multiple of 8)
   const unsigned short* logits;  // this row
   const uint32_t* cls;           // this row's 2-bit classes, or null (no penalties)
   bool vec;                      // row start is 16-byte aligned
@@ -110,6 +128,8 @@ struct Ctx3 {
   int slot;
   int2* s_pair;
   int n_s, s_cap;
+  ClassEntry* cl;    // this row's non-empty classes, ascending class index
+  int n_cl;
   float T, rp, pp, fp;
   bool greedy;
   float m;
@@ -159,11 +179,18 @@ __device__ __forceinline__ void for_each_side3(const Ctx3& c, F&& f) {
       if (e[u].x >= 0) f(e[u].x, __int_as_float(e[u].y));
   }
 }
+// Calls f(entry) for the row's non-empty classes, thread t taking entries t, t + kThreads, ...
+// (four 32-byte entries in flight per thread).
 template <class F>
-__device__ __forceinline__ void for_each_cell(const Ctx3& c, F&& f) {
-  for (int cell = threadIdx.x; cell < kCells; cell += kThreads) {
-    const uint32_t n = c.tab[cell];
-    if (n) f(cell, n, c.cell_score(cell));
+__device__ __forceinline__ void for_each_class(const Ctx3& c, F&& f) {
+  for (int i = threadIdx.x; i < c.n_cl; i += kThreads) {
+    const uint4* p = reinterpret_cast<const uint4*>(c.cl + i);
+    const uint4 lo = p[0], hi = p[1];
+    ClassEntry e;
+    e.key = lo.x; e.cnt = lo.y; e.cell = lo.z; e.pad = 0;
+    e.q = ((u64)hi.y << 32) | hi.x;
+    e.w = ((u64)hi.w << 32) | hi.z;
+    f(e);
   }
 }
 
@@ -281,28 +308,9 @@ struct UnionFill3 {
       const bool valid = ok(k);
       add(valid, (k >> shift) & mask, 1u, (WITH_MASS && valid) ? mass_of(s, c->m) : 0ull);
     });
-    // classes: each thread owns consecutive classes, whose scores are neighbours, so runs
-    // that fall into one bucket are merged in registers before touching shared memory
-    constexpr int kPerCells = kCells / kThreads;
-    const int cell0 = kPerCells * threadIdx.x;
-    uint32_t run_bin = 0xffffffffu, run_cnt = 0;
-    u64 run_mass = 0;
-#pragma unroll 1
-    for (int u = 0; u < kPerCells; ++u) {
-      const uint32_t n = c->tab[cell0 + u];
-      if (!n) continue;
-      const float s = c->cell_score(cell0 + u);
-      const uint32_t k = key_of(s);
-      if (!ok(k)) continue;
-      const uint32_t bin = (k >> shift) & mask;
-      if (bin != run_bin) {
-        add(run_cnt != 0, run_bin, run_cnt, run_mass);
-        run_bin = bin; run_cnt = 0; run_mass = 0;
-      }
-      run_cnt += n;
-      if (WITH_MASS) run_mass += (u64)n * mass_of(s, c->m);
-    }
-    add(run_cnt != 0, run_bin, run_cnt, run_mass);
+    for_each_class(*c, [&](const ClassEntry& e) {
+      add(ok(e.key), (e.key >> shift) & mask, e.cnt, WITH_MASS ? e.w : 0ull);
+    });
   }
 };
 
@@ -339,11 +347,10 @@ __device__ int gather_members3(Ctx3& c, uint32_t lo_key, int levels, uint32_t pr
     const int slot = atomicAdd(c.gbuf_n, 1);
     if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{k, id, 1u, 0u, mass_of(s, c.m)};
   });
-  for_each_cell(c, [&](int cell, uint32_t n, float s) {
-    const uint32_t k = key_of(s);
-    if (!matches(k)) return;
+  for_each_class(c, [&](const ClassEntry& e) {
+    if (!matches(e.key)) return;
     const int slot = atomicAdd(c.gbuf_n, 1);
-    if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{k, -1, n, (uint32_t)cell, mass_of(s, c.m)};
+    if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{e.key, -1, e.cnt, e.cell, e.q};
   });
   __syncthreads();
   const int n = min(*c.gbuf_n, kV3ListCap);
@@ -421,8 +428,8 @@ __device__ void totals3(Ctx3& c, uint32_t lo_key, u64& cnt, u64& mass) {
   for_each_side3(c, [&](int, float s) {
     if (key_of(s) >= lo_key) { ++a; b += mass_of(s, c.m); }
   });
-  for_each_cell(c, [&](int, uint32_t n, float s) {
-    if (key_of(s) >= lo_key) { a += n; b += (u64)n * mass_of(s, c.m); }
+  for_each_class(c, [&](const ClassEntry& e) {
+    if (e.key >= lo_key) { a += e.cnt; b += e.w; }
   });
   block_sum2(*c.x, a, b);
   cnt = a;
@@ -433,18 +440,21 @@ __device__ void totals3(Ctx3& c, uint32_t lo_key, u64& cnt, u64& mass) {
 // the bin) and the side elements whose score key equals it ---------------------------------
 struct Group {
   uint32_t key;
-  int cell[3];  // class index per count class, or -1
+  int cell0, cell1, cell2;  // class index per count class, or -1
+  __device__ __forceinline__ int cell_of(int cc) const { return cc == 0 ? cell0 : (cc == 1 ? cell1 : cell2); }
 };
 __device__ Group find_group(Ctx3& c, uint32_t key) {
   if (threadIdx.x < 3) c.x->bcast[threadIdx.x] = 0;
   __syncthreads();
-  for_each_cell(c, [&](int cell, uint32_t, float s) {
-    if (key_of(s) == key) c.x->bcast[cell / kV3Bins] = (u64)cell + 1;
+  for_each_class(c, [&](const ClassEntry& e) {
+    if (e.key == key) c.x->bcast[e.cell / kV3Bins] = (u64)e.cell + 1;
   });
   __syncthreads();
   Group g;
   g.key = key;
-  for (int i = 0; i < 3; ++i) g.cell[i] = (int)c.x->bcast[i] - 1;
+  g.cell0 = (int)c.x->bcast[0] - 1;
+  g.cell1 = (int)c.x->bcast[1] - 1;
+  g.cell2 = (int)c.x->bcast[2] - 1;
   __syncthreads();
   return g;
 }
@@ -452,7 +462,7 @@ __device__ Group find_group(Ctx3& c, uint32_t key) {
 __device__ __forceinline__ bool in_group(const Ctx3& c, const Group& g, int id, uint32_t raw, int cc) {
   if (cc < 3) {
     const int b = v3_bin_of_raw(raw);
-    if (b >= 0) return g.cell[cc] == cc * kV3Bins + b;
+    if (b >= 0) return g.cell_of(cc) == cc * kV3Bins + b;
     return key_of(c.score_of(raw, cc)) == g.key;  // outside the bin window: a side element
   }
   return key_of(c.score_of(raw, c.heavy_count(id))) == g.key;
@@ -622,510 +632,6 @@ __device__ int random_in_group(Ctx3& c, const Group& g, uint64_t seed, int id_li
     }
   }
   return -1;
-}
-
-__global__ void __launch_bounds__(kThreads, 2) row_kernel_v3(const RowV3Args args) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const RowKernelArgs& a = args.base;
-  const LayoutV3 lay = layout_v3();
-  Ctx3 c;
-  c.x = reinterpret_cast<Exchange*>(smem_raw + lay.x);
-  c.tab = reinterpret_cast<uint32_t*>(smem_raw + lay.tab);
-  c.hist = reinterpret_cast<LocalHist*>(smem_raw + lay.hist);
-  c.gbuf = reinterpret_cast<V3Entry*>(smem_raw + lay.gbuf);
-  c.list = reinterpret_cast<V3Entry*>(smem_raw + lay.list);
-  int* rare_id = reinterpret_cast<int*>(smem_raw + lay.rare);
-  int* small = reinterpret_cast<int*>(smem_raw + lay.small);
-  c.gbuf_n = small;
-  int* rare_n = small + 1;
-  int* side_n = small + 2;
-  const int tid = threadIdx.x;
-  c.row = blockIdx.x;
-  c.vocab = a.vocab;
-  c.logits = reinterpret_cast<const unsigned short*>(a.logits) + (long long)c.row * a.row_stride;
-  c.vec = (reinterpret_cast<uintptr_t>(c.logits) & 15u) == 0;
-  const hs_row_params P = a.params[c.row];
-  hs_row_out* out = a.out + c.row;
-  c.greedy = P.temperature == 0.0f;
-  c.T = P.temperature;
-  c.rp = P.repetition_penalty;
-  c.pp = P.presence_penalty;
-  c.fp = P.frequency_penalty;
-  c.pool = a.pool;
-  c.slot = P.slot;
-  const bool penalised = P.slot >= 0 && (P.repetition_penalty != 1.0f || P.presence_penalty != 0.0f ||
-                                          P.frequency_penalty != 0.0f);
-  c.cls = penalised ? a.pool.cls + (size_t)P.slot * a.pool.cls_stride : nullptr;
-  c.s_pair = args.s_pair + (size_t)c.row * args.s_cap;
-  c.s_cap = args.s_cap;
-  c.n_s = 0;
-  c.m = 0.f;
-  unsigned long long* clocks = args.phase_clocks ? args.phase_clocks + (size_t)c.row * kV3PhaseSlots : nullptr;
-  auto mark = [&](int slot) {
-    if (clocks && tid == 0) clocks[slot] = clock64();
-  };
-  mark(0);
-  int status = 0;
-
-  // ---- plain greedy rows of a mixed batch: arg max only -----------------------------------
-  if (c.greedy && !penalised && P.n_logprobs < 0) {
-    u64 best = 0;
-    auto consider = [&](uint32_t raw, int id) {
-      const u64 packed = ((u64)key_of(canonical(__uint_as_float(raw << 16))) << 32) | (uint32_t)(~(uint32_t)id);
-      best = packed > best ? packed : best;
-    };
-    const int n8 = c.vec ? c.vocab / 8 : 0;
-    for (int i = tid; i < n8; i += kThreads) {
-      uint32_t raw[8], cls16;
-      load_chunk(c, i, raw, cls16);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) consider(raw[k], 8 * i + k);
-    }
-    for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) consider(c.logits[id], id);
-    best = block_max_u64(*c.x, best);
-    if (a.scores_out) {
-      float* dst = a.scores_out + (size_t)c.row * a.vocab;
-      for (int id = tid; id < c.vocab; id += kThreads) dst[id] = canonical(__uint_as_float((uint32_t)c.logits[id] << 16));
-    }
-    if (tid == 0) {
-      out->token = (int)(~(uint32_t)(best & 0xffffffffu));
-      out->logprob = 0.f; out->n_top = 0; out->status = 0;
-      out->n_kept = a.vocab; out->n_after_topk = a.vocab; out->n_after_minp = a.vocab; out->n_after_topp = a.vocab;
-      out->cut_bits = 0xff800000u; out->n_cut_ties = -1;
-      out->row_max = score_of((uint32_t)(best >> 32)); out->log_z = 0.f;
-    }
-    return;
-  }
-
-  for (int i = tid; i < kCells; i += kThreads) c.tab[i] = 0;
-  if (tid < 16) small[tid] = 0;
-  __syncthreads();
-
-  // ---- A. the one read of the row from HBM: count tokens per (count class, value) --------
-  {
-    auto count_one = [&](uint32_t raw, int cc, int id) {
-      if (cc == 3) return;  // listed per request; handled below with its exact count
-      const int b = v3_bin_of_raw(raw);
-      if (b >= 0) {
-        atomicAdd(&c.tab[cc * kV3Bins + b], 1u);
-      } else {
-        const int slot = atomicAdd(rare_n, 1);
-        if (slot < kV3RareCap) rare_id[slot] = id;
-      }
-    };
-    const int n8 = c.vec ? c.vocab / 8 : 0;
-    const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
-    const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
-    constexpr int kInFlight = 8;
-    for (int i0 = tid; i0 < n8; i0 += kInFlight * kThreads) {
-      uint4 w[kInFlight];
-      uint32_t cl[kInFlight];
-#pragma unroll
-      for (int u = 0; u < kInFlight; ++u) {
-        const int i = i0 + u * kThreads;
-        if (i < n8) {
-          w[u] = src4[i];
-          cl[u] = cls16p ? cls16p[i] : 0u;
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kInFlight; ++u) {
-        const int i = i0 + u * kThreads;
-        if (i >= n8) break;
-        const uint32_t words[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          count_one(words[k] & 0xffffu, (cl[u] >> (4 * k)) & 3, 8 * i + 2 * k);
-          count_one(words[k] >> 16, (cl[u] >> (4 * k + 2)) & 3, 8 * i + 2 * k + 1);
-        }
-      }
-    }
-    for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) count_one(c.logits[id], c.class_of(id), id);
-  }
-  __syncthreads();
-  mark(1);
-
-  // ---- B. the side list: tokens with history count >= 3, and values outside the bin window
-  u64 side_best = 0;
-  {
-    auto put = [&](int slot, int id, float s) {
-      if (slot >= args.s_cap) { status |= 4; return; }
-      c.s_pair[slot] = make_int2(id, __float_as_int(s));
-      const u64 packed = ((u64)key_of(s) << 32) | (uint32_t)(~(uint32_t)id);
-      side_best = packed > side_best ? packed : side_best;
-    };
-    int n_heavy = 0;
-    if (penalised) {
-      n_heavy = min(a.pool.n_heavy[P.slot], min(a.pool.unique_cap, args.s_cap));
-      const int32_t* heavy = a.pool.heavy + (size_t)P.slot * a.pool.unique_cap;
-      for (int j = tid; j < n_heavy; j += kThreads) {
-        const int id = heavy[j];
-        if (id < 0 || id >= c.vocab) { c.s_pair[j] = make_int2(-1, 0); continue; }
-        put(j, id, c.score_of(c.logits[id], c.heavy_count(id)));
-      }
-    }
-    const int n_rare = *rare_n;
-    if (n_rare <= kV3RareCap) {
-      for (int t = tid; t < n_rare; t += kThreads) {
-        const int id = rare_id[t];
-        put(n_heavy + t, id, c.score_of(c.logits[id], c.class_of(id)));
-      }
-      c.n_s = min(n_heavy + n_rare, args.s_cap);
-    } else {
-      // too many to remember: sweep the row again for out-of-window values
-      for (int id = tid; id < c.vocab; id += kThreads) {
-        const uint32_t raw = c.logits[id];
-        const int cc = c.class_of(id);
-        if (cc == 3 || v3_bin_of_raw(raw) >= 0) continue;
-        put(n_heavy + atomicAdd(side_n, 1), id, c.score_of(raw, cc));
-      }
-      __syncthreads();
-      c.n_s = min(n_heavy + *side_n, args.s_cap);
-    }
-  }
-  side_best = block_max_u64(*c.x, side_best);  // (its barriers also publish the side list)
-  mark(2);
-
-  // ---- C. row maximum ------------------------------------------------------------------------
-  // scores grow with the bin inside a count class: the top non-empty bin of each class decides
-  uint32_t cells_key = 0;
-  {
-    uint32_t top[3];
-#pragma unroll
-    for (int k = 0; k < 3; ++k) {
-      uint32_t mine = 0;
-      for (int cell = k * kV3Bins + tid; cell < (k + 1) * kV3Bins; cell += kThreads)
-        if (c.tab[cell]) mine = (uint32_t)cell + 1;
-      top[k] = block_max_u32(*c.x, mine);
-    }
-#pragma unroll
-    for (int k = 0; k < 3; ++k)
-      if (top[k]) cells_key = max(cells_key, key_of(c.cell_score((int)top[k] - 1)));
-  }
-  const uint32_t side_key = (uint32_t)(side_best >> 32);
-  const int side_arg = (int)(~(uint32_t)(side_best & 0xffffffffu));
-  const bool any_side = side_best != 0;
-  const uint32_t max_key = max(cells_key, side_key);
-  c.m = score_of(max_key);
-  const float m = c.m;
-  mark(3);
-
-  KeptSet kept{0u, 0x7fffffff};
-  int token = -1;
-  u64 n_topk = (u64)a.vocab, n_minp = (u64)a.vocab, n_kept = (u64)a.vocab;
-  u64 q_kept = 0;
-  bool have_totals = false;
-  long long cut_ties = -1;
-  u64 cut_group_cnt = 0;   // members at the cut key (kept or not)
-  bool tie_split = false;
-  Group cut_group{0u, {-1, -1, -1}};
-  bool have_cut_group = false;
-  auto need_cut_group = [&]() {
-    if (!have_cut_group) { cut_group = find_group(c, kept.cut_key); have_cut_group = true; }
-  };
-  auto need_tie_limit = [&]() {
-    if (tie_split && kept.tie_limit == 0x7fffffff) {
-      need_cut_group();
-      kept.tie_limit = nth_in_group(c, cut_group, (u64)cut_ties);
-    }
-  };
-
-  if (c.greedy) {
-    const Group g = find_group(c, max_key);
-    token = nth_in_group(c, g, 1);
-    if (token == 0x7fffffff) { token = any_side ? side_arg : 0; status |= 1; }
-    if (P.n_logprobs >= 0) {
-      u64 cn;
-      totals3(c, 0u, cn, q_kept);
-    }
-  } else {
-    u64 cnt = 0, mass = 0;
-    if (P.top_k > 0 && P.top_k < a.vocab) {
-      Selection sk = select_union3<false, true>(c, 0u, (u64)P.top_k, 1.0f);
-      if (!sk.ok) status |= 1;
-      kept.cut_key = sk.key;
-      cnt = sk.above_cnt + sk.bin_cnt;
-      mass = sk.above_mass + sk.bin_mass;
-      have_totals = sk.ok;
-      n_topk = cnt;
-      cut_group_cnt = sk.bin_cnt;
-    }
-    mark(4);
-    if (P.min_p > 0.0f) {
-      if (!have_totals) { totals3(c, kept.cut_key, cnt, mass); have_totals = true; }
-      const float z1 = mass_to_float(mass);
-      const float thr = __fmul_rn(__fdiv_rn(1.0f, z1), P.min_p);
-      uint32_t lowest = 0xffffffffu;
-      auto consider = [&](float s) {
-        const uint32_t k = key_of(s);
-        if (k >= kept.cut_key && !(__fdiv_rn(expf(s - m), z1) < thr)) lowest = min(lowest, k);
-      };
-      for_each_cell(c, [&](int, uint32_t, float s) { consider(s); });
-      for_each_side3(c, [&](int, float s) { consider(s); });
-      lowest = ~block_max_u32(*c.x, ~lowest);
-      if (lowest != 0xffffffffu && lowest > kept.cut_key) {
-        kept.cut_key = lowest;
-        have_totals = false;
-      }
-    }
-    mark(5);
-    if (P.top_p < 1.0f) {
-      Selection sp = select_union3<true, true>(c, kept.cut_key, 0, P.top_p);
-      n_minp = sp.total_cnt;
-      if (sp.ok && sp.bin_cnt > 0) {
-        const u64 qv = sp.bin_mass / sp.bin_cnt;  // every token at the cut key has the same mass
-        u64 t = sp.bin_cnt;
-        if (qv > 0) {
-          const u64 want = sp.target - sp.above_mass;
-          t = (want + qv - 1) / qv;
-          if (t < 1) t = 1;
-          if (t > sp.bin_cnt) t = sp.bin_cnt;
-        }
-        kept.cut_key = sp.key;
-        cnt = sp.above_cnt + t;
-        mass = sp.above_mass + t * qv;
-        cut_ties = (long long)t;
-        cut_group_cnt = sp.bin_cnt;
-        tie_split = t < sp.bin_cnt;
-        have_totals = true;
-      } else {
-        status |= 1;
-        cnt = sp.total_cnt;
-        mass = sp.total_mass;
-        have_totals = true;
-      }
-    } else {
-      if (!have_totals) { totals3(c, kept.cut_key, cnt, mass); have_totals = true; }
-      n_minp = cnt;
-    }
-    n_kept = cnt;
-    q_kept = mass;
-    mark(6);
-
-    // ---- draw --------------------------------------------------------------------------
-    if (q_kept == 0) {
-      status |= 1;
-      token = any_side ? side_arg : 0;
-    } else if (a.noise) {
-      // reference draws: arg max of fl(fl(e / z) / noise) over the kept set, lowest id on ties
-      need_tie_limit();
-      const float zf = mass_to_float(q_kept);
-      const float* noise_row = a.noise + (size_t)c.row * a.vocab;
-      u64 best = 0;
-      for (int id = tid; id < c.vocab; id += kThreads) {
-        const float s = c.element_score(id, c.logits[id], c.class_of(id));
-        if (!kept.has(key_of(s), id)) continue;
-        const float p = __fdiv_rn(expf(s - m), zf);
-        const float ratio = __fdiv_rn(p, noise_row[id]);
-        const u64 packed = ((u64)__float_as_uint(ratio) << 32) | (uint32_t)(~(uint32_t)id);
-        best = packed > best ? packed : best;
-      }
-      best = block_max_u64(*c.x, best);
-      token = (int)(~(uint32_t)(best & 0xffffffffu));
-    } else {
-      // Inverse CDF over exact integer masses in the order: classes above the cut (by class
-      // index), the tie group at the cut (its lowest ids), side elements above the cut (by id).
-      const Philox4 r = philox4x32_10(0u, 0u, 0u, 0u, (uint32_t)P.seed, (uint32_t)(P.seed >> 32));
-      const u64 r64 = ((u64)r.v[0] << 32) | r.v[1];
-      const u64 target = __umul64hi(r64, q_kept);
-      constexpr int kPerCells = kCells / kThreads;  // 36 consecutive classes per thread
-      const int cell0 = kPerCells * tid;
-      u64 chunk = 0;
-#pragma unroll 1
-      for (int u = 0; u < kPerCells; ++u) {
-        const uint32_t n = c.tab[cell0 + u];
-        if (!n) continue;
-        const float s = c.cell_score(cell0 + u);
-        if (key_of(s) > kept.cut_key) chunk += (u64)n * mass_of(s, m);
-      }
-      const u64 incl = warp_scan_u64(chunk);
-      u64 pre, pre_unused, q_cells, tot_unused;
-      block_warp_prefix2(*c.x, shfl_u64(incl, 31), 0, pre, pre_unused, q_cells, tot_unused);
-      // the group at the cut key: cut_ties members when top-p split it, else all of them
-      u64 group_kept = cut_ties >= 0 ? (u64)cut_ties : 0;
-      u64 q_cut = 0;
-      if (cut_ties < 0) {
-        // cut by top-k / min-p / nothing: everything at the cut key is kept; count it
-        u64 gc = 0, gm = 0;
-        for_each_cell(c, [&](int, uint32_t n, float s) { if (key_of(s) == kept.cut_key) gc += n; });
-        for_each_side3(c, [&](int, float s) { if (key_of(s) == kept.cut_key) gc += 1; });
-        block_sum2(*c.x, gc, gm);
-        group_kept = gc;
-      }
-      q_cut = mass_of(score_of(kept.cut_key), m);
-      const u64 q_group = group_kept * q_cut;
-      if (target < q_cells) {
-        if (tid == 0) c.x->bcast[5] = 0;
-        __syncthreads();
-        u64 run = pre + incl - chunk;
-        if (run <= target && target < run + chunk) {
-#pragma unroll 1
-          for (int u = 0; u < kPerCells; ++u) {
-            const uint32_t n = c.tab[cell0 + u];
-            if (!n) continue;
-            const float s = c.cell_score(cell0 + u);
-            if (key_of(s) <= kept.cut_key) continue;
-            const u64 q = mass_of(s, m);
-            const u64 w = (u64)n * q;
-            if (w && target < run + w) {
-              c.x->bcast[3] = n;
-              c.x->bcast[4] = (target - run) / q + 1;
-              c.x->bcast[5] = (u64)(cell0 + u) + 1;
-              break;
-            }
-            run += w;
-          }
-        }
-        __syncthreads();
-        const int cell = (int)c.x->bcast[5] - 1;
-        const u64 members = c.x->bcast[3], nth = c.x->bcast[4];
-        __syncthreads();
-        if (cell >= 0) {
-          Group g{key_of(c.cell_score(cell)), {-1, -1, -1}};
-          g.cell[cell / kV3Bins] = cell;
-          // only this class, not other members that share its key
-          if (members * (u64)(kThreads * 8) >= (u64)c.vocab) {
-            Group only = g;
-            only.key = 0xffffffffu;  // no out-of-class member can match
-            token = random_in_group(c, only, P.seed, 0x7fffffff, 64);
-            if (token < 0) token = nth_in_group(c, only, nth);
-          } else {
-            Group only = g;
-            only.key = 0xffffffffu;
-            token = nth_in_group(c, only, nth);
-          }
-        }
-        if (token < 0 || token == 0x7fffffff) { token = any_side ? side_arg : 0; status |= 1; }
-      } else if (target < q_cells + q_group) {
-        need_cut_group();
-        const u64 nth = q_cut ? (target - q_cells) / q_cut + 1 : 1;
-        token = nth_in_group(c, cut_group, nth);  // the kept members are the lowest ids
-        if (token == 0x7fffffff) { token = any_side ? side_arg : 0; status |= 1; }
-      } else {
-        SideDrawFill3 fill{&c, kept.cut_key};
-        Selection sd = descend_local<true>(c, fill, 0u, target - q_cells - q_group + 1, -1.0f, 0, 1, 0x7FFu);
-        if (sd.ok) token = (int)(~sd.key);
-        else { token = any_side ? side_arg : 0; status |= 1; }
-      }
-    }
-  }
-  mark(7);
-
-  // ---- D. log-probabilities -------------------------------------------------------------
-  float log_z = 0.f;
-  if (P.n_logprobs >= 0) {
-    log_z = (float)(log((double)q_kept) - (double)kMassShift * 0.6931471805599453);
-    if (tid == 0 && token >= 0 && token < a.vocab)
-      out->logprob = (c.element_score(token, c.logits[token], c.class_of(token)) - m) - log_z;
-    int n_want = min(P.n_logprobs, a.vocab);
-    if ((u64)n_want > n_kept) n_want = (int)n_kept;
-    if (n_want > 0) {
-      Selection sn = select_union3<false, false>(c, kept.cut_key, (u64)n_want, 1.0f);
-      if (sn.ok) {
-        const int need = n_want - (int)sn.above_cnt;  // lowest ids of the group at the N-th key
-        // members above the N-th key: fewer than N tokens in a few classes and side elements
-        if (tid == 0) *c.gbuf_n = 0;
-        __syncthreads();
-        for_each_side3(c, [&](int id, float s) {
-          const uint32_t k = key_of(s);
-          if (k > sn.key) {
-            const int slot = atomicAdd(c.gbuf_n, 1);
-            if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{k, id, 1u, 0u, 0ull};
-          }
-        });
-        // mark the classes above the N-th key in the (free) histogram area, then walk the row
-        uint32_t* marked = reinterpret_cast<uint32_t*>(c.hist);  // kCells bits
-        for (int i = tid; i < (kCells + 31) / 32; i += kThreads) marked[i] = 0;
-        __syncthreads();
-        int any_marked = 0;
-        for_each_cell(c, [&](int cell, uint32_t, float s) {
-          if (key_of(s) > sn.key) { atomicOr(&marked[cell >> 5], 1u << (cell & 31)); any_marked = 1; }
-        });
-        any_marked = __syncthreads_or(any_marked);
-        if (any_marked) {
-          auto probe = [&](int id, uint32_t raw, int cc) {
-            if (cc == 3) return;
-            const int b = v3_bin_of_raw(raw);
-            if (b < 0) return;
-            const int cell = cc * kV3Bins + b;
-            if ((marked[cell >> 5] >> (cell & 31)) & 1u) {
-              const int slot = atomicAdd(c.gbuf_n, 1);
-              if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{key_of(c.cell_score(cell)), id, 1u, 0u, 0ull};
-            }
-          };
-          const int n8 = c.vec ? c.vocab / 8 : 0;
-          for (int i = tid; i < n8; i += kThreads) {
-            uint32_t raw[8], cls16;
-            load_chunk(c, i, raw, cls16);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) probe(8 * i + k, raw[k], (cls16 >> (2 * k)) & 3);
-          }
-          for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) probe(id, c.logits[id], c.class_of(id));
-        }
-        __syncthreads();
-        if (need > 0) {
-          const Group g = sn.key == kept.cut_key && have_cut_group ? cut_group : find_group(c, sn.key);
-          const int last_id = nth_in_group(c, g, (u64)need);
-          emit_group_upto(c, g, last_id == 0x7fffffff ? -1 : last_id);
-        }
-        __syncthreads();
-        if (tid < 32) {
-          const int n = min(*c.gbuf_n, HS_MAX_LOGPROBS);
-          uint32_t kv = 0;
-          int id = 0x7fffffff;
-          if (tid < n) { kv = c.gbuf[tid].key; id = c.gbuf[tid].id; }
-          int pos = 0;
-          for (int j = 0; j < n; ++j) {
-            const uint32_t kj = __shfl_sync(0xffffffffu, kv, j);
-            const int idj = __shfl_sync(0xffffffffu, id, j);
-            if (kj > kv || (kj == kv && idj < id)) ++pos;
-          }
-          if (tid < n) {
-            out->top_ids[pos] = id;
-            out->top_logprobs[pos] = (score_of(kv) - m) - log_z;
-          }
-          if (tid == 0 && n != n_want) status |= 8;
-        }
-      } else {
-        n_want = 0;
-        status |= 1;
-      }
-    }
-    if (tid == 0) out->n_top = n_want;
-  } else if (tid == 0) {
-    out->n_top = 0;
-    out->logprob = 0.f;
-  }
-  mark(8);
-
-  // ---- E. optional dump of the final scores (parity tests) -------------------------------
-  if (a.scores_out) {
-    need_tie_limit();
-    float* dst = a.scores_out + (size_t)c.row * a.vocab;
-    const float ninf = __int_as_float(0xff800000);
-    for (int id = tid; id < c.vocab; id += kThreads) {
-      const float s = c.element_score(id, c.logits[id], c.class_of(id));
-      dst[id] = (c.greedy || kept.has(key_of(s), id)) ? s : ninf;
-    }
-  }
-
-  if (tid == 0) {
-    out->token = token;
-    out->status = status;
-    out->n_kept = (int32_t)n_kept;
-    out->n_after_topk = (int32_t)n_topk;
-    out->n_after_minp = (int32_t)n_minp;
-    out->n_after_topp = (int32_t)n_kept;
-    out->cut_bits = __float_as_uint(score_of(kept.cut_key));
-    out->n_cut_ties = (int32_t)cut_ties;
-    out->row_max = m;
-    out->log_z = log_z;
-    if ((a.flags & HS_SAMPLE_APPEND_TOKEN) && P.slot >= 0 && token >= 0 && token < a.vocab) {
-      if (!slot_append_one(a.pool, P.slot, token)) out->status = status | 2;
-    }
-  }
-  (void)cut_group_cnt;
-  mark(9);
 }
 
 }  // namespace hs

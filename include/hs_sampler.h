@@ -141,6 +141,33 @@ int hs_sample_host(hs_sampler* h, const void* logits, int dtype, int64_t row_str
                    const int32_t* hist_tokens, const int32_t* hist_offsets, uint32_t flags,
                    void* stream);
 
+/* Vocabulary-sharded sampling (no counterpart in the reference, which has no tensor-parallel
+ * LM head; the result equals sample_logits on the concatenated row, sampling.py:54-163).
+ * Each rank reduces its contiguous slice of every row to an hs_shard_rec with
+ * hs_sharded_partial; the records of all ranks are exchanged by the caller (an all-gather,
+ * e.g. NCCL over NVLink) into recs[ranks][batch]; hs_sharded_merge finishes the rows from the
+ * union of the candidates.  Needs 0 < top_k <= HS_SHARD_CAND - 8 on every row; token ids in
+ * the records and results are global (slice-local id + vocab_offset).  Histories, when
+ * penalties are on, are slots of THIS rank's sampler filled with slice-local ids. */
+#define HS_SHARD_CAND 64
+typedef struct hs_shard_rec {
+  float row_max;       /* highest score of the slice (after penalties and temperature) */
+  float pad;
+  uint64_t z_mass;     /* sum over the slice of round(exp(score - row_max) * 2^40) */
+  int32_t n;           /* candidates that follow: the slice's top_k, ties at the k-th included */
+  int32_t status;      /* 0 ok; 16: candidate list overflowed; 32: more ties than the record holds */
+  int32_t ids[HS_SHARD_CAND];    /* global token ids, descending score then ascending id */
+  float scores[HS_SHARD_CAND];
+} hs_shard_rec;
+int hs_sharded_partial(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch,
+                       int vocab_local, int vocab_offset, const hs_row_params* params,
+                       hs_shard_rec* recs_out, void* stream);
+/* noise: NULL or [batch, vocab_total] Exp(1) variates (parity tests).  full_lse: NULL or
+ * [batch] floats receiving log-sum-exp of the scores over the whole vocabulary. */
+int hs_sharded_merge(hs_sampler* h, const hs_shard_rec* recs, int ranks, int batch, int vocab_total,
+                     const hs_row_params* params, hs_row_out* out, const float* noise,
+                     float* full_lse, void* stream);
+
 /* Introspection. */
 const char* hs_last_error(hs_sampler* h);
 const char* hs_status_string(int status);

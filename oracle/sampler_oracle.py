@@ -109,6 +109,15 @@ def _softmax64(scores: np.ndarray):
     return e / z, m, z
 
 
+def scaled_scores(row, history, p):
+    """Penalised logits and the scores the filters see: penalties, then the true fp32
+    division by the temperature (reference sampling.py:105-123).  Greedy rows are not scaled."""
+    y = penalise(np.asarray(row, dtype=F32), history, p)
+    if p.temperature == 0.0:
+        return y, y.copy()
+    return y, (y / F32(p.temperature)).astype(F32)
+
+
 def sample_row(row, history, p, step: int, *, draws: np.ndarray | None = None,
                want_probabilities: bool = True) -> OracleRow:
     """One row through penalties -> temperature -> top-k -> min-p -> top-p -> draw ->
@@ -116,14 +125,20 @@ def sample_row(row, history, p, step: int, *, draws: np.ndarray | None = None,
 
     ``draws``: the Exp(1) variates to use for the draw; default = the reference's own
     (``exponential_draws(mixed_seed(seed, step), V)``)."""
-    y = penalise(np.asarray(row, dtype=F32), history, p)
-    vocab = y.size
+    y, scores = scaled_scores(row, history, p)
+    return sample_from_scores(y, scores, p, step, draws=draws, want_probabilities=want_probabilities)
+
+
+def sample_from_scores(y, scores, p, step: int, *, draws: np.ndarray | None = None,
+                       want_probabilities: bool = True) -> OracleRow:
+    """The filters, the draw and the log-probabilities on already scaled scores
+    (reference sampling.py:124-163); -inf entries are tokens that are not candidates."""
+    scores = np.array(scores, dtype=F32, copy=True)
+    vocab = scores.size
     margins: dict = {}
     greedy = p.temperature == 0.0
-    scores = y.copy()
     n_k = n_m = n_p = vocab
     if not greedy:
-        scores = (scores / F32(p.temperature)).astype(F32)  # true fp32 division, :123
         if p.top_k:  # :124-127, ties at the k-th value stay
             keep = min(int(p.top_k), vocab)
             kth = np.partition(scores, vocab - keep)[vocab - keep]

@@ -1,0 +1,95 @@
+"""Vocabulary-sharded sampling on the GPU: the slices of every row go through
+hs_sharded_partial one after the other (one process stands in for the ranks; the exchange
+is a concatenation), hs_sharded_merge finishes the rows, and the result must equal the CPU
+checker on the concatenated row."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+from hydraserve_b200 import workloads  # noqa: E402
+from hydraserve_b200.engine import _device, sharded  # noqa: E402
+from hydraserve_b200.engine.sampling import SamplingParams  # noqa: E402
+from oracle import sampler_oracle as O  # noqa: E402
+from tests import parity  # noqa: E402
+
+
+def run_sharded(w, ranks):
+    bits = torch.from_numpy(w.logits.view(np.int16)).view(torch.bfloat16).cuda()
+    bounds = sharded.shard_bounds(w.vocab, ranks)
+    width = bounds[0][1] - bounds[0][0]
+    sampler = _device.DeviceSampler("cuda:0", vocab_max=width, batch_max=w.batch, resident_slots=4)
+    noise = np.ones((w.batch, w.vocab), np.float32)
+    rows = []
+    for r in range(w.batch):
+        q = O.exponential_draws(O.mixed_seed(w.params[r].seed, w.steps[r]), w.vocab)
+        noise[r] = q
+        rows.append(O.sample_row(w.logits_f32()[r], w.histories[r], w.params[r], w.steps[r], draws=q,
+                                 want_probabilities=False))
+    recs, d_params = [], None
+    for lo, hi in bounds:
+        rec, d_params = sharded.partial_records(sampler, bits[:, lo:hi].contiguous(), w.histories, w.params,
+                                                w.steps, lo)
+        recs.append(rec)
+    gathered = torch.stack(recs)
+    records, lse = sharded.merge_records(sampler, gathered, ranks, d_params, w.batch, w.vocab,
+                                         noise=torch.from_numpy(noise))
+    host_recs = gathered.cpu().numpy().view(np.uint8).reshape(ranks, w.batch, -1)
+    sampler.close()
+    return rows, records, lse.cpu().numpy(), host_recs
+
+
+@pytest.mark.parametrize("ranks", [2, 8])
+def test_sharded_rows_match_full_row_checker(built_library, ranks):
+    w = workloads.config5(batch=16)
+    rows, records, lse, _ = run_sharded(w, ranks)
+    report = parity.Report()
+    x = w.logits_f32()
+    for r, o in enumerate(rows):
+        rec = records[r]
+        assert rec["status"] == 0, (r, rec["status"])
+        n_top = int(rec["n_top"])
+        top = list(zip(rec["top_ids"][:n_top].tolist(), rec["top_logprobs"][:n_top].tolist()))
+        parity.compare_with_oracle(report, r, o, token=int(rec["token"]), logprob=float(rec["logprob"]), top=top,
+                                   kept_n=int(rec["n_kept"]), eps=2e-7, exact_ties=True)
+        assert int(rec["n_after_topk"]) == o.n_after_topk
+        _, sc = O.scaled_scores(x[r], w.histories[r], w.params[r])
+        want = float(np.log(np.exp(sc.astype(np.float64) - sc.max()).sum()) + sc.max())
+        assert abs(lse[r] - want) <= 1e-5 * max(1.0, abs(want))
+    report.assert_ok(max_sensitive_fraction=0.3)
+
+
+def test_sharded_with_penalties_ties_and_min_p(built_library):
+    rng = np.random.default_rng(77)
+    vocab, batch = 31_040 * 2, 6
+    x = np.round(rng.standard_normal((batch, vocab)) * 3 * 4) / 4  # quarter steps: ties at the k-th
+    bits = workloads.f32_to_bf16_bits(x.astype(np.float32))
+    params = [SamplingParams(temperature=0.9, top_k=k, top_p=p, min_p=mp, seed=100 + i, logprobs=lp,
+                             repetition_penalty=1.2, presence_penalty=0.3, frequency_penalty=0.1)
+              for i, (k, p, mp, lp) in enumerate([(5, 0.9, 0.0, 20), (40, 1.0, 0.05, 5), (56, 0.5, 0.0, None),
+                                                  (1, 0.9, 0.0, 3), (20, 0.8, 0.1, 0), (50, 0.95, 0.01, 20)])]
+    hist = [rng.integers(0, vocab, 2000).astype(np.int32) for _ in range(batch)]
+    w = workloads.Workload("sharded-ties", bits, "bf16", hist, params, list(range(batch)))
+    rows, records, _, host_recs = run_sharded(w, 2)
+    report = parity.Report()
+    for r, o in enumerate(rows):
+        rec = records[r]
+        if rec["status"] & 32:
+            continue  # more ties than a record holds: reported, not compared
+        assert rec["status"] == 0
+        n_top = int(rec["n_top"])
+        top = list(zip(rec["top_ids"][:n_top].tolist(), rec["top_logprobs"][:n_top].tolist()))
+        if w.params[r].logprobs is not None:
+            want = min(w.params[r].logprobs, w.vocab)
+            taken, i = {t for t, _ in top}, 0
+            while len(top) < want:
+                if i not in taken:
+                    top.append((i, float("-inf")))
+                i += 1
+        parity.compare_with_oracle(report, r, o, token=int(rec["token"]),
+                                   logprob=float(rec["logprob"]) if w.params[r].logprobs is not None else None,
+                                   top=top, kept_n=int(rec["n_kept"]), eps=2e-7, exact_ties=True)
+    report.assert_ok()
+    assert report.rows >= 3
