@@ -15,7 +15,6 @@
 #include "hs_common.cuh"
 #include "hs_state.cuh"
 #include "hs_row_kernel.cuh"
-#include "hs_row_bf16.cuh"
 #include "hs_row_v3.cuh"
 #include "hs_row_topk.cuh"
 #include "hs_sharded.cuh"
@@ -66,13 +65,14 @@ struct hs_sampler {
   int smem_optin = 0;
   int force_cluster = 0;
   int force_general = 0;  // route bf16 rows through the general (fp32-stage) kernel too
-  int force_cluster16 = 0;  // route bf16 rows through the cluster-resident bf16 kernel
   int2* side_pair = nullptr;  // [batch_max, side_cap] side lists of the bf16 kernel
   hs::ClassEntry* clist = nullptr;
   unsigned char* needs_count = nullptr;  // [batch_max]
   unsigned long long* split_lists = nullptr;  // [batch_max, kMaxSplit, kSplitCap]
   int* split_n = nullptr;
-  int* split_ticket = nullptr;  // [batch_max, kCells] class lists of the bf16 kernel
+  int* split_ticket = nullptr;
+  cudaStream_t aux_stream = nullptr;  // the candidate kernel runs here, next to the counting kernel
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;  // [batch_max, kCells] class lists of the bf16 kernel
   int side_cap = 0;
   unsigned long long* phase_clocks = nullptr;  // HS_PHASE_CLOCKS=1: per-row phase timestamps
   hs::Pool pool{};
@@ -134,24 +134,6 @@ bool make_plan(const hs_sampler* h, int vocab, Plan& p) {
   return true;
 }
 
-// Launch shape of the bf16 kernel: the smallest cluster whose CTAs can hold their slice of
-// raw bf16 bits next to the fixed work areas.
-bool make_plan16(const hs_sampler* h, int vocab, Plan& p) {
-  if (h->force_general) return false;
-  static const int sizes[4] = {1, 2, 4, 8};
-  for (int k = 0; k < 4; ++k) {
-    const int c = sizes[k];
-    if (h->force_cluster && c != h->force_cluster) continue;
-    const int slice = ((vocab + c - 1) / c + 7) & ~7;
-    const size_t smem = hs::layout16(c).stage + (size_t)slice * sizeof(uint16_t);
-    if (smem <= (size_t)h->smem_optin && slice <= hs::kMaxSliceElems) {
-      p = Plan{c, slice, smem, false};
-      return true;
-    }
-  }
-  return false;
-}
-
 int check_common(hs_sampler* h, const void* logits, int dtype, int batch, int vocab) {
   if (!h) return HS_ERR_INVALID;
   if (!logits && batch > 0) return fail(h, HS_ERR_INVALID, "logits is null");
@@ -166,7 +148,7 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
                 const hs_row_params* params, hs_row_out* out, const float* noise, float* scores_out,
                 uint32_t flags, cudaStream_t stream) {
   Plan plan;
-  if (dtype == HS_DTYPE_BF16 && !h->force_general && !h->force_cluster16) {
+  if (dtype == HS_DTYPE_BF16 && !h->force_general) {
     // one CTA per row, two CTAs per SM
     hs::RowKernelArgs a{};
     a.logits = logits; a.dtype = dtype; a.row_stride = row_stride; a.vocab = vocab; a.slice = 0;
@@ -175,19 +157,29 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
     // small batches: several CTAs stream each row so that every SM has work
     int split = (2 * h->sm_count + batch - 1) / batch;
     split = std::max(1, std::min(split, kMaxSplit));
-    if (vocab < split * 2 * hs::kPrefix) split = 1;
+    if (vocab < split * 2 * hs::kSample) split = 1;
     hs::RowV3Args a3{a, h->clist, h->side_pair, h->side_cap, h->phase_clocks, h->needs_count,
-                     split, h->split_lists, h->split_n, h->split_ticket};
-    hs::row_kernel_topk<<<dim3((unsigned)split, (unsigned)batch), hs::kThreads, hs::layout_cand().total, stream>>>(a3);
+                     split, h->split_lists, h->split_n, h->split_ticket, 0};
+    // The two kernels serve disjoint rows and fit on an SM together, so they run side by
+    // side: the candidate kernel on an auxiliary stream forked from the caller's.  A row
+    // whose candidate list overflowed (rare) is counted by a second pass afterwards.
+    HS_CUDA(h, cudaEventRecord(h->ev_fork, stream));
+    HS_CUDA(h, cudaStreamWaitEvent(h->aux_stream, h->ev_fork, 0));
+    hs::row_kernel_topk<<<dim3((unsigned)split, (unsigned)batch), hs::kThreads, hs::layout_cand().total, h->aux_stream>>>(a3);
     HS_CUDA(h, cudaGetLastError());
+    HS_CUDA(h, cudaEventRecord(h->ev_join, h->aux_stream));
+    a3.pass = 0;
     hs::row_kernel_v3<<<(unsigned)batch, hs::kThreads, hs::layout_v3().total, stream>>>(a3);
     HS_CUDA(h, cudaGetLastError());
-    h->launches += 2;
+    HS_CUDA(h, cudaStreamWaitEvent(stream, h->ev_join, 0));
+    a3.pass = 1;
+    hs::row_kernel_v3<<<(unsigned)batch, hs::kThreads, hs::layout_v3().total, stream>>>(a3);
+    HS_CUDA(h, cudaGetLastError());
+    h->launches += 3;
     return HS_OK;
   }
-  const bool bf16_path = dtype == HS_DTYPE_BF16 && make_plan16(h, vocab, plan);
-  if (!bf16_path && !make_plan(h, vocab, plan)) return fail(h, HS_ERR_CAPACITY, "vocabulary too wide for the row kernel");
-  if (!bf16_path && plan.global_stage) {
+  if (!make_plan(h, vocab, plan)) return fail(h, HS_ERR_CAPACITY, "vocabulary too wide for the row kernel");
+  if (plan.global_stage) {
     const size_t need = (size_t)batch * plan.slice * plan.cluster;
     if (need > h->gstage_elems) return fail(h, HS_ERR_CAPACITY, "global stage too small for this batch x vocab");
   }
@@ -201,7 +193,7 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
   a.out = out;
   a.noise = noise;
   a.scores_out = scores_out;
-  a.gstage = (!bf16_path && plan.global_stage) ? h->gstage : nullptr;
+  a.gstage = plan.global_stage ? h->gstage : nullptr;
   a.pool = h->pool;
   a.flags = flags;
 
@@ -217,12 +209,7 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (bf16_path) {
-    hs::Row16Args a16{a, h->side_pair, h->side_cap, h->phase_clocks};
-    HS_CUDA(h, cudaLaunchKernelEx(&cfg, hs::row_kernel_bf16, a16));
-  } else {
-    HS_CUDA(h, cudaLaunchKernelEx(&cfg, hs::row_kernel, a));
-  }
+  HS_CUDA(h, cudaLaunchKernelEx(&cfg, hs::row_kernel, a));
   h->launches += 1;
   return HS_OK;
 }
@@ -261,7 +248,10 @@ int launch_append(hs_sampler* h, const int32_t* tokens, const int32_t* offsets, 
 void release(hs_sampler* h) {
   cudaFree(h->pool.pairs); cudaFree(h->pool.cls); cudaFree(h->pool.heavy); cudaFree(h->pool.n_heavy); cudaFree(h->pool.n); cudaFree(h->pool.pos);
   cudaFree(h->side_pair); cudaFree(h->clist); cudaFree(h->needs_count);
-  cudaFree(h->split_lists); cudaFree(h->split_n); cudaFree(h->split_ticket); cudaFree(h->phase_clocks);
+  cudaFree(h->split_lists); cudaFree(h->split_n); cudaFree(h->split_ticket);
+  if (h->aux_stream) cudaStreamDestroy(h->aux_stream);
+  if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+  if (h->ev_join) cudaEventDestroy(h->ev_join); cudaFree(h->phase_clocks);
   cudaFree(h->pool.error); cudaFree(h->greedy_partials); cudaFree(h->gstage); cudaFree(h->d_logits);
   cudaFree(h->d_params); cudaFree(h->d_out); cudaFree(h->d_hist); cudaFree(h->d_offsets); cudaFree(h->d_slots);
   if (h->h_params) cudaFreeHost(h->h_params);
@@ -389,13 +379,11 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   if (cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaDeviceGetAttribute(&h->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_optin) != cudaSuccess) return bail(HS_ERR_CUDA);
-  if (cudaFuncSetAttribute(hs::row_kernel_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_optin) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::row_kernel_v3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_v3().total) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::row_kernel_topk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_cand().total) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::shard_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_cand().total) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::shard_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_cand().total) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (const char* fg = std::getenv("HS_FORCE_GENERAL")) h->force_general = std::atoi(fg) != 0;
-  if (const char* fc16 = std::getenv("HS_FORCE_CLUSTER16")) h->force_cluster16 = std::atoi(fc16) != 0;
 
   const size_t st = (size_t)h->slots_total;
   h->pool.slots_total = h->slots_total;
@@ -417,6 +405,9 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   ok = ok && cudaMalloc(&h->d_slots, (size_t)batch_max * sizeof(int32_t)) == cudaSuccess;
   h->side_cap = (vocab_max + 7) & ~7;
   ok = ok && cudaMalloc(&h->side_pair, (size_t)batch_max * h->side_cap * sizeof(int2)) == cudaSuccess;
+  ok = ok && cudaStreamCreateWithFlags(&h->aux_stream, cudaStreamNonBlocking) == cudaSuccess;
+  ok = ok && cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming) == cudaSuccess;
+  ok = ok && cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming) == cudaSuccess;
   ok = ok && cudaMalloc(&h->needs_count, (size_t)batch_max) == cudaSuccess;
   ok = ok && cudaMalloc(&h->split_lists, (size_t)batch_max * kMaxSplit * hs::kSplitCap * sizeof(unsigned long long)) == cudaSuccess;
   ok = ok && cudaMalloc(&h->split_n, (size_t)batch_max * kMaxSplit * sizeof(int)) == cudaSuccess;
@@ -428,7 +419,7 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   ok = ok && cudaMallocHost(&h->h_small, (2 * (size_t)batch_max + 1) * sizeof(int32_t)) == cudaSuccess;
   if (const char* pc = std::getenv("HS_PHASE_CLOCKS")) {
     if (std::atoi(pc) != 0) {
-      const size_t bytes = (size_t)batch_max * hs::kPhaseSlots * sizeof(unsigned long long);
+      const size_t bytes = (size_t)batch_max * hs::kV3PhaseSlots * sizeof(unsigned long long);
       ok = ok && cudaMalloc(&h->phase_clocks, bytes) == cudaSuccess;
       ok = ok && cudaMemset(h->phase_clocks, 0, bytes) == cudaSuccess;
     }
@@ -644,7 +635,7 @@ int hs_debug_phase_clocks(hs_sampler* h, int batch, unsigned long long* out_host
   if (!h || !out_host || batch < 0 || batch > h->batch_max) return HS_ERR_INVALID;
   if (!h->phase_clocks) return fail(h, HS_ERR_UNSUPPORTED, "create the sampler with HS_PHASE_CLOCKS=1");
   DeviceGuard guard(h->device);
-  HS_CUDA(h, cudaMemcpy(out_host, h->phase_clocks, (size_t)batch * hs::kPhaseSlots * sizeof(unsigned long long),
+  HS_CUDA(h, cudaMemcpy(out_host, h->phase_clocks, (size_t)batch * hs::kV3PhaseSlots * sizeof(unsigned long long),
                         cudaMemcpyDeviceToHost));
   return HS_OK;
 }
@@ -652,12 +643,11 @@ int hs_debug_phase_clocks(hs_sampler* h, int batch, unsigned long long* out_host
 int hs_query(hs_sampler* h, int what, int vocab, int dtype) {
   if (!h) return HS_ERR_INVALID;
   Plan plan;
-  const bool v3 = dtype == HS_DTYPE_BF16 && !h->force_general && !h->force_cluster16;
-  const bool bf16_path = !v3 && dtype == HS_DTYPE_BF16 && make_plan16(h, vocab, plan);
+  const bool v3 = dtype == HS_DTYPE_BF16 && !h->force_general;
   switch (what) {
-    case 0: return v3 ? 1 : ((bf16_path || make_plan(h, vocab, plan)) ? plan.cluster : HS_ERR_CAPACITY);
-    case 1: return v3 ? 0 : ((bf16_path || make_plan(h, vocab, plan)) ? (plan.global_stage ? 0 : 1) : HS_ERR_CAPACITY);
-    case 4: return v3 ? 2 : (bf16_path ? 1 : 0);
+    case 0: return v3 ? 1 : (make_plan(h, vocab, plan) ? plan.cluster : HS_ERR_CAPACITY);
+    case 1: return v3 ? 0 : (make_plan(h, vocab, plan) ? (plan.global_stage ? 0 : 1) : HS_ERR_CAPACITY);
+    case 4: return v3 ? 1 : 0;
     case 2: return h->sm_count;
     case 3: return (int)(h->launches & 0x7fffffffull);
     default: return HS_ERR_INVALID;

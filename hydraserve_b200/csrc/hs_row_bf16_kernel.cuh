@@ -50,8 +50,12 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
   auto mark = [&](int slot) {
     if (clocks && tid == 0) clocks[slot] = clock64();
   };
-  // rows with a small top_k were served by row_kernel_topk unless their list overflowed
-  if (!c.greedy && P.top_k > 0 && P.top_k <= kTopKMax && P.top_k < a.vocab && !args.needs_count[c.row]) return;
+  // rows with a small top_k belong to row_kernel_topk; it hands back (pass 1) the rare row
+  // whose candidate list overflowed
+  {
+    const bool small_k = !c.greedy && P.top_k > 0 && P.top_k <= kTopKMax && P.top_k < a.vocab;
+    if (args.pass == 0 ? small_k : !(small_k && args.needs_count[c.row])) return;
+  }
   mark(0);
   int status = 0;
 
@@ -199,34 +203,30 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
   c.m = score_of(max_key);
   const float m = c.m;
   // ---- the row's non-empty classes, each with its key and mass computed once ---------------
+  // Thread t owns classes t, t + kThreads, ... (the populated value range spreads evenly over
+  // the threads) and writes its entries back to back; the order is fixed by the counts alone.
   {
     constexpr int kPerCells = kCells / kThreads;
-    const int cell0 = kPerCells * tid;
     int mine = 0;
 #pragma unroll 4
-    for (int u = 0; u < kPerCells; ++u) mine += c.tab[cell0 + u] != 0;
+    for (int u = 0; u < kPerCells; ++u) mine += c.tab[tid + u * kThreads] != 0;
     const u64 incl = warp_scan_u64((u64)mine);
     u64 pre, pre_unused, tot, tot_unused;
     block_warp_prefix2(*c.x, shfl_u64(incl, 31), 0, pre, pre_unused, tot, tot_unused);
     int at = (int)(pre + incl) - mine;
     for (int u = 0; u < kPerCells; ++u) {
-      const uint32_t n = c.tab[cell0 + u];
+      const int cell = tid + u * kThreads;
+      const uint32_t n = c.tab[cell];
       if (!n) continue;
-      c.cl[at].cnt = n;
-      c.cl[at].cell = (uint32_t)(cell0 + u);
+      const float s = c.cell_score(cell);
+      const u64 q = mass_of(s, m);
+      const u64 wgt = (u64)n * q;
+      uint4* dst = reinterpret_cast<uint4*>(c.cl + at);
+      dst[0] = make_uint4(key_of(s), n, (uint32_t)cell, 0u);
+      dst[1] = make_uint4((uint32_t)q, (uint32_t)(q >> 32), (uint32_t)wgt, (uint32_t)(wgt >> 32));
       ++at;
     }
     c.n_cl = (int)tot;
-    __syncthreads();
-    for (int i = tid; i < c.n_cl; i += kThreads) {  // balanced: one class per thread per step
-      const uint32_t n = c.cl[i].cnt;
-      const float s = c.cell_score((int)c.cl[i].cell);
-      const u64 q = mass_of(s, m);
-      c.cl[i].key = key_of(s);
-      c.cl[i].pad = 0;
-      c.cl[i].q = q;
-      c.cl[i].w = (u64)n * q;
-    }
     __syncthreads();
   }
   mark(3);

@@ -4,8 +4,9 @@
 // With top_k = k, only the k highest scores (and ties at the k-th) can ever be sampled or
 // reported, so nothing needs counting: the row is streamed once from HBM and compared, two
 // tokens per instruction, against a lower bound of the k-th highest score.  The bound comes
-// from the row itself: the first 2,048 tokens are all scored, their k-th highest score is a
-// valid bound for the whole row, and whenever the candidate list grows past 2,048 entries
+// from the row itself: among the first 16,384 tokens, those the history does not hold are
+// ranked by raw value (no scoring needed: their score grows with it), and the k-th highest is
+// a valid bound for the whole row; whenever the candidate list grows past 2,048 entries
 // the bound is raised to the list's k-th highest score and the list is compacted.  Scores
 // grow with the raw value inside a history-count class, so the bound turns into one raw
 // threshold per class (binary search over the 65,536 bf16 values); a token whose history
@@ -28,7 +29,7 @@ namespace hs {
 constexpr int kTopKMax = 256;      // largest top_k served by the candidate path
 constexpr int kCandCap = 4096;     // candidate list capacity (shared memory, 8 bytes each)
 constexpr int kCandSoft = 2048;    // raise the bound once the list is this long
-constexpr int kPrefix = 2048;      // tokens scored unconditionally to get the first bound
+constexpr int kSample = 16384;     // tokens sampled (their raw values only) to get the first bound
 
 // (score key << 32) | ~id : sorting these descending orders by score, then by ascending id
 __device__ __forceinline__ u64 cand_pack(uint32_t key, int id) {
@@ -143,6 +144,78 @@ __device__ void cand_thresholds(const Ctx3& c, CandCtx& L, uint32_t bound) {
   __syncthreads();
 }
 
+// The k-th highest raw value (as signed 16-bit image) among the tokens of [begin, end) that
+// the history does not hold, or -32768 when there are fewer than k of them.  Two radix
+// levels over the 16 bits (2,048 buckets of 32 values, then the 32 values of one bucket).
+__device__ int sample_kth_t16(const Ctx3& c, CandCtx& L, int begin, int end, int k) {
+  const int tid = threadIdx.x;
+  const bool vec = c.vec && (begin & 7) == 0;
+  const int n8 = vec ? (end - begin) / 8 : 0;  // whole 8-token chunks read as 128-bit words
+  const uint4* src4 = reinterpret_cast<const uint4*>(c.logits) + (begin >> 3);
+  const unsigned short* cls16p = c.cls ? reinterpret_cast<const unsigned short*>(c.cls) + (begin >> 3) : nullptr;
+  int prefix = -1;
+  int want = k;
+  for (int level = 0; level < 2; ++level) {
+    for (int b = tid; b < kBins; b += kThreads) L.count[b] = 0;
+    __syncthreads();
+    auto see = [&](uint32_t raw) {
+      const int v = t16_of_raw(raw) + 32768;  // 0 .. 65535, float order
+      if (level == 0) atomicAdd(&L.count[v >> 5], 1u);
+      else if ((v >> 5) == prefix) atomicAdd(&L.count[v & 31], 1u);
+    };
+    for (int i0 = tid; i0 < n8; i0 += 4 * kThreads) {
+      uint4 w[4];
+      uint32_t cl[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kThreads;
+        if (i < n8) { w[u] = src4[i]; cl[u] = cls16p ? cls16p[i] : 0u; }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (i0 + u * kThreads >= n8) break;
+        const uint32_t words[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (((cl[u] >> (2 * q)) & 3u) == 0) see((words[q >> 1] >> (16 * (q & 1))) & 0xffffu);
+      }
+    }
+    for (int id = begin + n8 * 8 + tid; id < end; id += kThreads)
+      if (c.class_of(id) == 0) see(c.logits[id]);
+    if (tid == 0) L.thr[3] = -1;
+    __syncthreads();
+    constexpr int kPer = kBins / kThreads;
+    const int hi = kBins - 1 - kPer * tid;
+    u64 sum = 0;
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) sum += L.count[hi - u];
+    const u64 incl = warp_scan_u64(sum);
+    u64 pre, pu, tot, tu;
+    block_warp_prefix2(*c.x, shfl_u64(incl, 31), 0, pre, pu, tot, tu);
+    u64 ex = pre + incl - sum;
+    if (ex < (u64)want && (u64)want <= ex + sum) {
+#pragma unroll
+      for (int u = 0; u < kPer; ++u) {
+        const u64 bc = L.count[hi - u];
+        if ((u64)want <= ex + bc) {
+          L.thr[3] = hi - u;
+          c.x->bcast[1] = ex;
+          break;
+        }
+        ex += bc;
+      }
+    }
+    __syncthreads();
+    const int found = L.thr[3];
+    const int above = (int)c.x->bcast[1];
+    __syncthreads();
+    if (found < 0) return -32768;  // fewer than k such tokens
+    want -= above;
+    if (level == 0) prefix = found; else return ((prefix << 5) | found) - 32768;
+  }
+  return -32768;
+}
+
 // Streams the row and leaves in L every token whose score can be among the top k (ties at
 // the k-th included).  Returns the list length, or -1 when the list overflowed (the caller
 // then uses the counting path).
@@ -171,14 +244,8 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
     }
     __syncthreads();
   };
-  // 1. the first tokens are all candidates; their k-th highest score bounds the row's.
-  // Tokens the history holds three times or more are candidates by definition (their score
+  // 1. Tokens the history holds three times or more are candidates by definition (their score
   // does not follow from a class threshold); they come from the request's list, not the stream.
-  const int n_prefix = min(c.hi - c.lo, kPrefix);
-  for (int id = c.lo + tid; id < c.lo + n_prefix; id += kThreads) {
-    const int cc = c.class_of(id);
-    if (cc != 3) push(id, c.logits[id], cc);
-  }
   if (c.cls) {
     const int n_heavy = min(c.pool.n_heavy[c.slot], c.pool.unique_cap);
     const int32_t* heavy = c.pool.heavy + (size_t)c.slot * c.pool.unique_cap;
@@ -191,19 +258,16 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
   if (*L.lost) return -1;
   int n = min(*L.n, kCandCap);
   score_pending(0, n);
+  // the first bound: k-th highest raw value among the sampled tokens outside the history
+  const int t_k = sample_kth_t16(c, L, c.lo, min(c.hi, c.lo + kSample), k);
+  uint32_t bound = t_k > -32768 ? key_of(c.score_of(raw_of_t16(t_k), 0)) : 0u;
   if (L.dbg && tid == 0) L.dbg[3] = clock64();
-  uint32_t bound = 0;
-  if (n >= k) {
-    bound = cand_kth_key(*c.x, L, n, k);
-    n = cand_compact(L, n, bound);
-  }
-  if (n_prefix == c.hi - c.lo) return n;
   cand_thresholds(c, L, bound);
   if (L.dbg && tid == 0) L.dbg[4] = clock64();
   int refreshes = 0;
   // 2. the rest of the row: eight tokens per 128-bit load, one native bf16x2 comparison per
   // two tokens against the most permissive class threshold; the rare hit is looked at closely
-  const int first8 = (c.lo + n_prefix) / 8;  // lo and kPrefix are multiples of 8
+  const int first8 = c.lo / 8;  // lo is a multiple of 8
   const int n8 = c.vec ? c.hi / 8 : first8;
   const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
   constexpr int kInFlight = 8;
@@ -257,7 +321,7 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
   __syncthreads();
   if (L.dbg && tid == 0) { L.dbg[5] = clock64(); L.dbg[6] = (unsigned long long)refreshes; L.dbg[7] = (unsigned long long)*L.n; }
   // scalar tail (or the whole remainder of a row that is not 16-byte aligned)
-  for (int id = max(n8 * 8, c.lo + n_prefix) + tid; id < c.hi; id += kThreads) {
+  for (int id = max(n8 * 8, c.lo) + tid; id < c.hi; id += kThreads) {
     const uint32_t raw = c.logits[id];
     const int cc = c.class_of(id);
     if (cc != 3 && t16_of_raw(raw) >= L.thr[cc]) push(id, raw, cc);

@@ -50,6 +50,7 @@ struct V3Entry {
 };
 
 struct LocalHist {
+  uint32_t ent[kBins];  // entries (classes + side elements) per bucket
   uint32_t cnt[kBins];
   uint32_t l0[kBins], l1[kBins], l2[kBins];  // mass in 14-bit limbs: 32-bit shared atomics only
   __device__ __forceinline__ u64 mass(int b) const {
@@ -78,6 +79,7 @@ struct RowV3Args {
   unsigned long long* split_lists;   // [batch, split, kSplitCap] candidate lists of the row's CTAs
   int* split_n;                      // [batch, split] their lengths
   int* split_ticket;                 // [batch] arrival counter (returns to 0)
+  int pass;                          // row_kernel_v3: 0 = rows without a small top_k, 1 = rows the candidate kernel handed back
 };
 
 struct LayoutV3 {
@@ -183,14 +185,27 @@ __device__ __forceinline__ void for_each_side3(const Ctx3& c, F&& f) {
 // (four 32-byte entries in flight per thread).
 template <class F>
 __device__ __forceinline__ void for_each_class(const Ctx3& c, F&& f) {
-  for (int i = threadIdx.x; i < c.n_cl; i += kThreads) {
-    const uint4* p = reinterpret_cast<const uint4*>(c.cl + i);
-    const uint4 lo = p[0], hi = p[1];
-    ClassEntry e;
-    e.key = lo.x; e.cnt = lo.y; e.cell = lo.z; e.pad = 0;
-    e.q = ((u64)hi.y << 32) | hi.x;
-    e.w = ((u64)hi.w << 32) | hi.z;
-    f(e);
+  for (int i0 = threadIdx.x; i0 < c.n_cl; i0 += 4 * kThreads) {
+    uint4 lo[4], hi[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * kThreads;
+      if (i < c.n_cl) {
+        const uint4* p = reinterpret_cast<const uint4*>(c.cl + i);
+        lo[u] = p[0];
+        hi[u] = p[1];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * kThreads;
+      if (i >= c.n_cl) break;
+      ClassEntry e;
+      e.key = lo[u].x; e.cnt = lo[u].y; e.cell = lo[u].z; e.pad = 0;
+      e.q = ((u64)hi[u].y << 32) | hi[u].x;
+      e.w = ((u64)hi[u].w << 32) | hi[u].z;
+      f(e);
+    }
   }
 }
 
@@ -199,6 +214,7 @@ struct LocalAdder {
   LocalHist* h;
   __device__ __forceinline__ void operator()(bool valid, uint32_t bin, uint32_t count, u64 mass) const {
     if (!valid) return;
+    atomicAdd(&h->ent[bin], 1u);
     atomicAdd(&h->cnt[bin], count);
     const uint32_t a0 = (uint32_t)mass & kLimbMask;
     const uint32_t a1 = (uint32_t)(mass >> kLimbBits) & kLimbMask;
@@ -226,7 +242,7 @@ __device__ Selection descend_local(Ctx3& c, Fill& fill, uint32_t lo_key, u64 tar
   for (int level = first_level; level < 3; ++level) {
     const int shift = level_shift(level);
     const int bits = level_bits(level);
-    for (int b = tid; b < kBins; b += kThreads) { h.cnt[b] = 0; h.l0[b] = 0; h.l1[b] = 0; h.l2[b] = 0; }
+    for (int b = tid; b < kBins; b += kThreads) { h.ent[b] = 0; h.cnt[b] = 0; h.l0[b] = 0; h.l1[b] = 0; h.l2[b] = 0; }
     if (tid == 0) c.x->bcast[7] = 0;
     __syncthreads();
     fill(level, shift, bits, prefix, lo_key, add);
@@ -262,6 +278,7 @@ __device__ Selection descend_local(Ctx3& c, Fill& fill, uint32_t lo_key, u64 tar
             c.x->bcast[2] = ex_mass;
             c.x->bcast[3] = bc;
             c.x->bcast[4] = bm;
+            c.x->bcast[5] = h.ent[hi - u];
             c.x->bcast[7] = 1;
             break;
           }
@@ -284,10 +301,11 @@ __device__ Selection descend_local(Ctx3& c, Fill& fill, uint32_t lo_key, u64 tar
     sel.above_mass += c.x->bcast[2];
     sel.bin_cnt = c.x->bcast[3];
     sel.bin_mass = c.x->bcast[4];
+    const u64 entries = c.x->bcast[5];
     prefix = (prefix << bits) | bin;
     sel.levels = level + 1;
     __syncthreads();
-    if (stop_pop && level < 2 && sel.bin_cnt <= stop_pop) break;
+    if (stop_pop && level < 2 && entries <= stop_pop) break;  // few enough members to sort
   }
   sel.prefix = prefix;
   sel.key = sel.levels == 3 ? prefix : (prefix << (sel.levels == 1 ? 21 : 10));

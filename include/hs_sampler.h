@@ -173,12 +173,13 @@ const char* hs_last_error(hs_sampler* h);
 const char* hs_status_string(int status);
 int hs_abi_version(void);
 /* what: 0 = CTAs per row (cluster size) hs_sample would use for (vocab, dtype),
- *       1 = 1 if that row would be staged in shared memory, 0 if in global scratch,
+ *       1 = 1 if the general kernel would hold that row in shared memory, 0 if in global scratch
+ *           (the bf16 kernels do not hold the row at all),
  *       2 = number of SMs, 3 = kernels launched by this sampler so far (low 31 bits),
- *       4 = 1 if (vocab, dtype) takes the bf16 value-histogram kernel, 0 if the general one */
+ *       4 = 1 if (vocab, dtype) takes the bf16 kernels (candidate / counting), 0 if the general one */
 int hs_query(hs_sampler* h, int what, int vocab, int dtype);
 /* Tuning aid: when the sampler was created with the environment variable HS_PHASE_CLOCKS=1,
- * the bf16 kernel records the SM clock at 12 phase boundaries per row of the last launch;
+ * the bf16 kernels record the SM clock at 12 phase boundaries per row of the last launch;
  * this copies batch x 12 counters to out_host (synchronises the device). */
 int hs_debug_phase_clocks(hs_sampler* h, int batch, unsigned long long* out_host);
 
