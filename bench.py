@@ -40,6 +40,9 @@ if str(ROOT) not in sys.path:
 METRIC = "sampled rows/sec"
 UNIT = "rows/s"
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of the two kernels of one step, from the ncu
+# capture summarised in profiles/ (same workload, one step)
+NCU_DRAM_BYTES_PER_STEP = None
 ROTATING_SETS = 3
 
 
@@ -67,7 +70,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", uuid], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             pass
@@ -223,8 +226,10 @@ def run_ours(args, world, rank, local_rank):
     host_logits = torch.from_numpy(w.logits.view(np.int16)).view(torch.bfloat16).pin_memory()
     sets = [host_logits.to(device, non_blocking=True).clone() for _ in range(ROTATING_SETS)]
     total_steps = args.steps + args.warmup
+    # a few parameter sets (the step number advances the seeded stream) reused round robin
+    n_param_sets = min(total_steps, 16)
     param_sets = []
-    for i in range(total_steps):
+    for i in range(n_param_sets):
         rec = _device.pack_params(w.params, [s + i for s in w.steps], slots)
         param_sets.append(sampler._to_device(rec.view(np.uint8).reshape(batch, -1)))
     d_out = torch.empty((batch, _lib.ROW_OUT.itemsize), dtype=torch.uint8, device=device)
@@ -233,7 +238,7 @@ def run_ours(args, world, rank, local_rank):
 
     def step(i):
         st = lib.hs_sample(handle, sets[i % ROTATING_SETS].data_ptr(), _lib.HS_DTYPE_BF16, vocab, batch, vocab,
-                           param_sets[i].data_ptr(), d_out.data_ptr(), None, None,
+                           param_sets[i % n_param_sets].data_ptr(), d_out.data_ptr(), None, None,
                            _lib.HS_SAMPLE_APPEND_TOKEN, stream)
         if st != 0:
             raise RuntimeError(lib.hs_last_error(handle).decode())
@@ -310,7 +315,10 @@ def run_ours(args, world, rank, local_rank):
     achieved = algo_bytes / (ms_per_step * 1e-3) / 1e9
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-        "traffic": None, "kernel": "hs::row_kernel", "peak_source": peak_src,
+        "traffic": NCU_DRAM_BYTES_PER_STEP if (batch, vocab, args.history) == (256, 248_320, 32_768) else None,
+        "kernel": "hs::row_kernel_v3 (counting rows) and hs::row_kernel_topk (small top_k rows), side by side on "
+                  "two streams; one step = both",
+        "peak_source": peak_src,
         "algorithmic_bytes_per_launch": algo_bytes, "logits_bytes_per_launch": logits_bytes,
         "logits_only_gbs": logits_bytes / (ms_per_step * 1e-3) / 1e9,
     }
@@ -342,13 +350,13 @@ def run_ours(args, world, rank, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--vocab", type=int, default=248_320)
     ap.add_argument("--history", type=int, default=32_768)
-    ap.add_argument("--e2e-steps", type=int, default=8)
+    ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--cpu-rows", type=int, default=64)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--kernel-only", action="store_true",

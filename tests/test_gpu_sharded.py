@@ -93,3 +93,63 @@ def test_sharded_with_penalties_ties_and_min_p(built_library):
                                    top=top, kept_n=int(rec["n_kept"]), eps=2e-7, exact_ties=True)
     report.assert_ok()
     assert report.rows >= 3
+
+
+def _nccl_worker(rank, world, port, queue):
+    import os
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        w = workloads.config5(batch=32)
+        lo, hi = sharded.shard_bounds(w.vocab, world)[rank]
+        bits = torch.from_numpy(np.ascontiguousarray(w.logits[:, lo:hi]).view(np.int16)).view(torch.bfloat16).cuda()
+        samples = sharded.sample_logits_sharded(bits, w.histories, w.params, steps=w.steps, vocab_offset=lo,
+                                                vocab_total=w.vocab)
+        again = sharded.sample_logits_sharded(bits, w.histories, w.params, steps=w.steps, vocab_offset=lo,
+                                              vocab_total=w.vocab)
+        assert samples == again
+        x = w.logits_f32()
+        for r, s in enumerate(samples):
+            o = O.sample_row(x[r], w.histories[r], w.params[r], w.steps[r], draws=np.ones(w.vocab, np.float32),
+                             want_probabilities=False)
+            assert s.token_id in set(o.kept.tolist())
+            assert len(s.top_logprobs) == 20
+            want = [v for _, v in o.top_logprobs]
+            got = [v for _, v in s.top_logprobs]
+            assert np.allclose(got, want, rtol=1e-5, atol=2e-6), (r, got[:3], want[:3])
+        gathered = [None] * world
+        dist.all_gather_object(gathered, [s.token_id for s in samples])
+        assert all(g == gathered[0] for g in gathered)
+        queue.put((rank, "ok"))
+    except Exception as exc:  # pragma: no cover
+        import traceback
+
+        queue.put((rank, traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_sampling_over_nccl(built_library):
+    """One process per GPU, records exchanged with an NCCL all-gather."""
+    import socket
+
+    import torch.multiprocessing as mp
+
+    world = min(torch.cuda.device_count(), 8)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [queue.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(results) == [(r, "ok") for r in range(world)], results
