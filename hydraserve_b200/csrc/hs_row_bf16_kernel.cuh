@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
   c.n_cl = 0;
   c.m = 0.f;
   unsigned long long* clocks = args.phase_clocks ? args.phase_clocks + (size_t)c.row * kV3PhaseSlots : nullptr;
+  c.dbg = clocks;
   auto mark = [&](int slot) {
     if (clocks && tid == 0) clocks[slot] = clock64();
   };
@@ -97,44 +98,44 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
 
   // ---- A. the one read of the row from HBM: count tokens per (count class, value) --------
   {
-    auto count_one = [&](uint32_t raw, int cc, int id) {
-      if (cc == 3) return;  // listed per request; handled below with its exact count
-      const int b = v3_bin_of_raw(raw);
-      if (b >= 0) {
-        atomicAdd(&c.tab[cc * kV3Bins + b], 1u);
-      } else {
-        const int slot = atomicAdd(rare_n, 1);
-        if (slot < kV3RareCap) rare_id[slot] = id;
-      }
-    };
-    const int n8 = c.vec ? c.vocab / 8 : 0;
-    const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
-    const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
-    constexpr int kInFlight = 8;
-    for (int i0 = tid; i0 < n8; i0 += kInFlight * kThreads) {
-      uint4 w[kInFlight];
-      uint32_t cl[kInFlight];
-#pragma unroll
-      for (int u = 0; u < kInFlight; ++u) {
-        const int i = i0 + u * kThreads;
-        if (i < n8) {
-          w[u] = src4[i];
-          cl[u] = cls16p ? cls16p[i] : 0u;
+      auto count_one = [&](uint32_t raw, int cc, int id) {
+        if (cc == 3) return;  // listed per request; handled below with its exact count
+        const int b = v3_bin_of_raw(raw);
+        if (b >= 0) {
+          atomicAdd(&c.tab[cc * kV3Bins + b], 1u);
+        } else {
+          const int slot = atomicAdd(rare_n, 1);
+          if (slot < kV3RareCap) rare_id[slot] = id;
+        }
+      };
+      const int n8 = c.vec ? c.vocab / 8 : 0;
+      const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
+      const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
+      constexpr int kInFlight = 8;
+      for (int i0 = tid; i0 < n8; i0 += kInFlight * kThreads) {
+        uint4 w[kInFlight];
+        uint32_t cl[kInFlight];
+  #pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+          const int i = i0 + u * kThreads;
+          if (i < n8) {
+            w[u] = src4[i];
+            cl[u] = cls16p ? cls16p[i] : 0u;
+          }
+        }
+  #pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+          const int i = i0 + u * kThreads;
+          if (i >= n8) break;
+          const uint32_t words[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+  #pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            count_one(words[k] & 0xffffu, (cl[u] >> (4 * k)) & 3, 8 * i + 2 * k);
+            count_one(words[k] >> 16, (cl[u] >> (4 * k + 2)) & 3, 8 * i + 2 * k + 1);
+          }
         }
       }
-#pragma unroll
-      for (int u = 0; u < kInFlight; ++u) {
-        const int i = i0 + u * kThreads;
-        if (i >= n8) break;
-        const uint32_t words[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          count_one(words[k] & 0xffffu, (cl[u] >> (4 * k)) & 3, 8 * i + 2 * k);
-          count_one(words[k] >> 16, (cl[u] >> (4 * k + 2)) & 3, 8 * i + 2 * k + 1);
-        }
-      }
-    }
-    for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) count_one(c.logits[id], c.class_of(id), id);
+      for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) count_one(c.logits[id], c.class_of(id), id);
   }
   __syncthreads();
   mark(1);
@@ -230,6 +231,7 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
     __syncthreads();
   }
   mark(3);
+  if (clocks && tid == 0) { clocks[10] = (unsigned long long)c.n_cl; clocks[11] = (unsigned long long)c.n_s; }
 
   KeptSet kept{0u, 0x7fffffff};
   int token = -1;
@@ -355,6 +357,7 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
       const u64 incl = warp_scan_u64(chunk);
       u64 pre, pre_unused, q_cells, tot_unused;
       block_warp_prefix2(*c.x, shfl_u64(incl, 31), 0, pre, pre_unused, q_cells, tot_unused);
+      mark(12);
       // the group at the cut key: cut_ties members when top-p split it, else all of them
       u64 group_kept = cut_ties >= 0 ? (u64)cut_ties : 0;
       u64 q_cut = 0;
@@ -368,6 +371,7 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
       }
       q_cut = mass_of(score_of(kept.cut_key), m);
       const u64 q_group = group_kept * q_cut;
+      mark(13);
       if (target < q_cells) {
         if (tid == 0) c.x->bcast[5] = 0;
         __syncthreads();
@@ -390,18 +394,23 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
         const int cell = (int)c.x->bcast[5] - 1;
         const u64 members = c.x->bcast[3], nth = c.x->bcast[4];
         __syncthreads();
+        mark(14);
+        if (clocks && tid == 0) clocks[15] = members;
         if (cell >= 0) {
           Group g{key_of(c.cell_score(cell)), -1, -1, -1};
           if (cell < kV3Bins) g.cell0 = cell; else if (cell < 2 * kV3Bins) g.cell1 = cell; else g.cell2 = cell;
-          // only this class, not other members that share its key
-          if (members * (u64)(kThreads * 8) >= (u64)c.vocab) {
+          // only this class, not other members that share its key: large classes by rejection
+          // (about vocab / members scattered probes), small ones by one scan of the row
+          if (members * 8192ull >= (u64)c.vocab) {
+            const u64 per_round = ((u64)c.vocab + members - 1) / members;  // probes for ~63 % success
+            const int trials = (int)min((u64)kRandomTrials, max(1ull, (per_round + kThreads - 1) / kThreads));
+            token = random_in_class(c, cell, trials, P.seed, 32);
+          } else if (members <= (u64)kV3ListCap) {
+            token = nth_in_small_class(c, cell, nth);
+          }
+          if (token < 0) {
             Group only = g;
             only.key = 0xffffffffu;  // no out-of-class member can match
-            token = random_in_group(c, only, P.seed, 0x7fffffff, 64);
-            if (token < 0) token = nth_in_group(c, only, nth);
-          } else {
-            Group only = g;
-            only.key = 0xffffffffu;
             token = nth_in_group(c, only, nth);
           }
         }
@@ -539,6 +548,11 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
 }
 
 
+// The counting pass of row_kernel_v3 as a kernel of its own: light on registers, several
+// CTAs per SM and per row, so the shared-memory atomics of all SMs work on the counting rows
+// at once.  Each CTA counts its slice of the row per (count class, value) in shared memory and
+// adds its non-empty classes to the row's table in global memory; row_kernel_v3 picks the
+// table up (and clears it for the next step).
 // Rows with 0 < top_k <= kTopKMax: the candidate path.  A row whose candidate list overflows
 // is flagged in needs_count and left to row_kernel_v3, which is launched next.
 __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args args) {

@@ -38,7 +38,7 @@ constexpr int kCells = 3 * kV3Bins;           // count classes 0, 1, 2
 constexpr uint32_t kV3Base = 113u << 7;       // smallest binned magnitude: 2^-14
 constexpr int kV3ListCap = 128;               // members resolved by sorting
 constexpr int kV3RareCap = 512;               // out-of-window tokens remembered before a sweep
-constexpr int kV3PhaseSlots = 12;
+constexpr int kV3PhaseSlots = 16;
 constexpr int kSplitCap = 4096;               // candidate entries one CTA of a split row can hand over
 
 struct V3Entry {
@@ -122,6 +122,7 @@ struct Ctx3 {
   V3Entry* list;     // sorted members
   int* gbuf_n;
   int row, vocab;
+  unsigned long long* dbg = nullptr;
   int lo, hi;                    // token range this CTA streams in the candidate path (lo a multiple of 8)
   const unsigned short* logits;  // this row
   const uint32_t* cls;           // this row's 2-bit classes, or null (no penalties)
@@ -604,6 +605,68 @@ __device__ int nth_in_group(Ctx3& c, const Group& g, u64 n) {
   return result;
 }
 
+// Token id of the n-th (1-based, ascending id) token of ONE class (count class and
+// one-value bin `cell`), for classes of at most kV3ListCap tokens, or -1 when the row has
+// no 16-byte aligned view or the class turns out larger.  One pass over the row: a class
+// is one bf16 bit pattern, so eight tokens are screened with four XORs and a zero-half
+// test, and only words with a matching half look at the class map.  The few ids found are
+// ranked among themselves.
+__device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
+  if (!c.vec) return -1;
+  const int tid = threadIdx.x;
+  const int cc = cell / kV3Bins;
+  const uint32_t raw = v3_raw_of_bin(cell - cc * kV3Bins);
+  const uint32_t vv = raw | (raw << 16);
+  int* ids = reinterpret_cast<int*>(c.gbuf);
+  if (tid == 0) *c.gbuf_n = 0;
+  __syncthreads();
+  const int n8 = c.vocab / 8;
+  const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
+  auto zero_half = [](uint32_t x) { return (x - 0x00010001u) & ~x & 0x80008000u; };
+  auto probe = [&](int id, uint32_t r) {
+    if (r == raw && c.class_of(id) == cc) {
+      const int slot = atomicAdd(c.gbuf_n, 1);
+      if (slot < kV3ListCap) ids[slot] = id;
+    }
+  };
+  constexpr int kInFlight = 8;  // 64 KB per SM on the way: the row may have left L2
+  for (int i0 = tid; i0 < n8; i0 += kInFlight * kThreads) {
+    uint4 w[kInFlight];
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      const int i = i0 + u * kThreads;
+      w[u] = i < n8 ? src4[i] : make_uint4(~vv, ~vv, ~vv, ~vv);
+    }
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      const uint32_t z = zero_half(w[u].x ^ vv) | zero_half(w[u].y ^ vv) | zero_half(w[u].z ^ vv) |
+                         zero_half(w[u].w ^ vv);
+      if (z) {
+        const int id = 8 * (i0 + u * kThreads);
+        probe(id, w[u].x & 0xffffu); probe(id + 1, w[u].x >> 16);
+        probe(id + 2, w[u].y & 0xffffu); probe(id + 3, w[u].y >> 16);
+        probe(id + 4, w[u].z & 0xffffu); probe(id + 5, w[u].z >> 16);
+        probe(id + 6, w[u].w & 0xffffu); probe(id + 7, w[u].w >> 16);
+      }
+    }
+  }
+  for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) probe(id, c.logits[id]);
+  if (tid == 0) c.x->bcast[6] = 0;
+  __syncthreads();
+  const int found = *c.gbuf_n;
+  if (found <= kV3ListCap && tid < found) {
+    const int mine = ids[tid];
+    u64 rank = 1;
+    for (int j = 0; j < found; ++j) rank += ids[j] < mine ? 1 : 0;
+    if (rank == n) c.x->bcast[6] = (u64)mine + 1;
+  }
+  __syncthreads();
+  const u64 hit = c.x->bcast[6];
+  __syncthreads();
+  if (found > kV3ListCap) return -1;
+  return hit ? (int)(hit - 1) : 0x7fffffff;
+}
+
 // Appends to the gather buffer the ids of all group members with id <= id_limit.
 __device__ void emit_group_upto(Ctx3& c, const Group& g, int id_limit) {
   const int n8 = c.vec ? c.vocab / 8 : 0;
@@ -627,22 +690,43 @@ __device__ void emit_group_upto(Ctx3& c, const Group& g, int id_limit) {
   __syncthreads();
 }
 
-// A uniformly chosen member of the group by rejection: Philox-drawn positions are probed,
-// trial t = round * kThreads + thread, and the lowest hitting trial wins.  id_limit
-// restricts the choice to members with id <= id_limit.  Returns -1 if max_rounds pass
-// without a hit.
-__device__ int random_in_group(Ctx3& c, const Group& g, uint64_t seed, int id_limit, int max_rounds) {
+// A uniformly chosen token of ONE class (count class and one-value bin `cell`) by rejection:
+// Philox-drawn positions are probed, `trials` (<= kRandomTrials) per thread and round with
+// their loads in flight together; trial t = (round * trials + j) * kThreads + thread, and
+// the lowest hitting trial wins.  A lone CTA sustains well under one scattered load per
+// clock, so a probe reads the value first and the class map only when the value matches.
+// Returns -1 if max_rounds pass without a hit.
+constexpr int kRandomTrials = 8;
+__device__ int random_in_class(Ctx3& c, int cell, int trials, uint64_t seed, int max_rounds) {
   const int tid = threadIdx.x;
+  const int cc = cell / kV3Bins;
+  const uint32_t value = v3_raw_of_bin(cell - cc * kV3Bins);
   for (int round = 0; round < max_rounds; ++round) {
-    const Philox4 r = philox4x32_10((uint32_t)round, (uint32_t)tid, 1u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32));
-    const u64 r64 = ((u64)r.v[0] << 32) | r.v[1];
-    const int id = (int)__umul64hi(r64, (u64)c.vocab);
-    const bool ok = id <= id_limit && in_group(c, g, id, c.logits[id], c.class_of(id));
-    // lowest trial index that hit
-    const uint32_t key = ok ? (uint32_t)(kThreads - tid) : 0u;
+    int id[kRandomTrials];
+    uint32_t raw[kRandomTrials];
+#pragma unroll
+    for (int j = 0; j < kRandomTrials / 2; ++j) {
+      if (2 * j < trials) {
+        const Philox4 r = philox4x32_10((uint32_t)round, (uint32_t)tid, 1u + (uint32_t)j, 0u, (uint32_t)seed,
+                                        (uint32_t)(seed >> 32));
+        id[2 * j] = (int)__umul64hi(((u64)r.v[0] << 32) | r.v[1], (u64)c.vocab);
+        id[2 * j + 1] = (int)__umul64hi(((u64)r.v[2] << 32) | r.v[3], (u64)c.vocab);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kRandomTrials; ++j) raw[j] = j < trials ? (uint32_t)c.logits[id[j]] : ~value;
+    uint32_t key = 0;
+    int mine = -1;
+#pragma unroll
+    for (int j = kRandomTrials - 1; j >= 0; --j) {
+      if (j < trials && raw[j] == value && c.class_of(id[j]) == cc) {
+        key = (uint32_t)((kRandomTrials - j) * kThreads - tid);
+        mine = id[j];
+      }
+    }
     const uint32_t best = block_max_u32(*c.x, key);
     if (best) {
-      if (key == best) c.x->bcast[6] = (u64)id;
+      if (key == best) c.x->bcast[6] = (u64)mine;
       __syncthreads();
       const int token = (int)c.x->bcast[6];
       __syncthreads();

@@ -179,8 +179,8 @@ int hs_abi_version(void);
  *       4 = 1 if (vocab, dtype) takes the bf16 kernels (candidate / counting), 0 if the general one */
 int hs_query(hs_sampler* h, int what, int vocab, int dtype);
 /* Tuning aid: when the sampler was created with the environment variable HS_PHASE_CLOCKS=1,
- * the bf16 kernels record the SM clock at 12 phase boundaries per row of the last launch;
- * this copies batch x 12 counters to out_host (synchronises the device). */
+ * the bf16 kernels record the SM clock at 16 phase slots per row of the last launch;
+ * this copies batch x 16 counters to out_host (synchronises the device). */
 int hs_debug_phase_clocks(hs_sampler* h, int batch, unsigned long long* out_host);
 
 #ifdef __cplusplus
