@@ -37,6 +37,12 @@ __device__ __forceinline__ float canonical(float f) {
   return (__float_as_uint(f) == 0x80000000u) ? 0.0f : f;
 }
 
+// Hint: bring `bytes` (a multiple of 16) starting at the 16-byte aligned global address p
+// into L2.  No completion to wait for, nothing is written.
+__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 // ---- probability mass as an exact integer -------------------------------------------
 // e = exp(s - m) in (0, 1]; mass = round(e * 2^40).  Sums of masses are exact and do not
 // depend on the order of accumulation, which makes every cut reproducible.

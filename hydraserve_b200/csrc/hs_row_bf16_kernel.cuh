@@ -1,12 +1,36 @@
 // The bf16 row kernel: dispatches each row to the candidate path (small top_k), the
 // plain arg-max path, or the counting path (hs_row_v3.cuh).
 #pragma once
+#include <type_traits>
 
 #include "hs_row_v3.cuh"
 #include "hs_row_topk.cuh"
 #include "hs_sharded.cuh"
 
+#ifndef HS_STREAM_BATCH
+#define HS_STREAM_BATCH 4
+#endif
 namespace hs {
+
+// One chunk of eight tokens the counting loop could not take in its branch-free form (a
+// value outside the bin window, a token of count class 3): token by token, out of line so
+// that the unrolled loop stays small.
+__device__ __noinline__ void count_chunk_slow(uint32_t* tab, int* rare_n, int* rare_id, uint4 w, uint32_t cl, int i) {
+  const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll 1
+  for (int k = 0; k < 8; ++k) {
+    const uint32_t raw = (words[k >> 1] >> (16 * (k & 1))) & 0xffffu;
+    const int cc = (int)((cl >> (2 * k)) & 3u);
+    if (cc == 3) continue;  // listed per request; scored individually with its exact count
+    const int b = v3_bin_of_raw(raw);
+    if (b >= 0) {
+      atomicAdd(&tab[cc * kV3Bins + b], 1u);
+    } else {
+      const int slot = atomicAdd(rare_n, 1);
+      if (slot < kV3RareCap) rare_id[slot] = 8 * i + k;
+    }
+  }
+}
 
 __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args args) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -90,6 +114,21 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
     return;
   }
 
+  // ask L2 for the whole row (and its class map) now: the counting loop then waits for L2,
+  // not for HBM, and the later walks over the row find it there
+  if (c.vec) {
+    constexpr uint32_t kPiece = 16384;
+    const size_t row_bytes = ((size_t)c.vocab * 2) & ~(size_t)15;
+    for (size_t at = (size_t)tid * kPiece; at < row_bytes; at += (size_t)kThreads * kPiece)
+      prefetch_l2_bulk(reinterpret_cast<const unsigned char*>(c.logits) + at,
+                       (uint32_t)min((size_t)kPiece, row_bytes - at));
+    if (c.cls && (reinterpret_cast<uintptr_t>(c.cls) & 15u) == 0) {
+      const size_t cls_bytes = ((size_t)c.vocab / 4) & ~(size_t)15;
+      for (size_t at = (size_t)tid * kPiece; at < cls_bytes; at += (size_t)kThreads * kPiece)
+        prefetch_l2_bulk(reinterpret_cast<const unsigned char*>(c.cls) + at,
+                         (uint32_t)min((size_t)kPiece, cls_bytes - at));
+    }
+  }
   if (tid < 16) small[tid] = 0;
   __syncthreads();
 
@@ -111,29 +150,69 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
       const int n8 = c.vec ? c.vocab / 8 : 0;
       const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
       const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
-      constexpr int kInFlight = 8;
-      for (int i0 = tid; i0 < n8; i0 += kInFlight * kThreads) {
-        uint4 w[kInFlight];
-        uint32_t cl[kInFlight];
+      // Eight tokens at a time without a branch per token.  Per 32-bit word (two tokens):
+      // |x| + (0x8000 - base) sets bit 15 of a half iff |x| >= base and leaves |x| - base
+      // in its low bits; |x| + (0x8000 - top) sets it iff |x| >= top.  A chunk with a value
+      // outside the window or a token of count class 3 (rare) takes the per-token path.
+      constexpr uint32_t kLoAdd = (0x8000u - kV3Base) * 0x00010001u;
+      constexpr uint32_t kHiAdd = (0x8000u - (kV3Base + (uint32_t)kV3Half)) * 0x00010001u;
+      // 32-bit shared-memory addresses: one LOP3, one multiply-add, one shift-add and the
+      // reduction per token
+      const uint32_t tab_mid = (uint32_t)__cvta_generic_to_shared(c.tab + kV3Half);
+      // J-th token of the chunk: its 2-bit class sits at bit 2J of cl
+      auto bump = [&](uint32_t u16, uint32_t sign_mask, uint32_t cl, auto J) {
+        constexpr int kShift = 2 * decltype(J)::value;
+        constexpr uint32_t kClassBytes = (uint32_t)(kV3Bins * 4);  // 3 << 13
+        // bin = kV3Half + idx for x >= 0, kV3Half - 1 - idx = kV3Half + ~idx for x < 0
+        const uint32_t rel = (u16 & 0x7fffu) ^ sign_mask;
+        const uint32_t base = kShift < 14 ? (cl & (3u << kShift)) * (kClassBytes >> kShift) + tab_mid
+                                          : (cl >> 14) * kClassBytes + tab_mid;
+        const uint32_t addr = base + (rel << 2);
+        asm volatile("red.shared.add.u32 [%0], 1;" ::"r"(addr) : "memory");
+      };
+      auto take_chunk = [&](const uint4& w4, uint32_t cl4, int i) {
+        const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+        uint32_t lo[4], bad = cl4 & (cl4 >> 1) & 0x5555u;  // a token of class 3
+  #pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t mag = words[k] & 0x7fff7fffu;
+          lo[k] = mag + kLoAdd;
+          bad |= (~lo[k] | (mag + kHiAdd)) & 0x80008000u;
+        }
+        if (bad == 0) {
+#define HS_BUMP_WORD(K)                                                                                    \
+  bump(lo[K], (uint32_t)((int)(words[K] << 16) >> 31), cl4, std::integral_constant<int, 2 * K>{});         \
+  bump(lo[K] >> 16, (uint32_t)((int)words[K] >> 31), cl4, std::integral_constant<int, 2 * K + 1>{});
+          HS_BUMP_WORD(0) HS_BUMP_WORD(1) HS_BUMP_WORD(2) HS_BUMP_WORD(3)
+#undef HS_BUMP_WORD
+        } else {
+          count_chunk_slow(c.tab, rare_n, rare_id, w4, cl4, i);
+        }
+      };
+      // two batches of loads: the next one is on its way while this one is counted
+      constexpr int kInFlight = HS_STREAM_BATCH;
+      uint4 w[kInFlight], wn[kInFlight];
+      uint32_t cl[kInFlight], cn[kInFlight];
+      auto fetch = [&](uint4 (&dw)[kInFlight], uint32_t (&dc)[kInFlight], int i0) {
   #pragma unroll
         for (int u = 0; u < kInFlight; ++u) {
           const int i = i0 + u * kThreads;
           if (i < n8) {
-            w[u] = src4[i];
-            cl[u] = cls16p ? cls16p[i] : 0u;
+            dw[u] = src4[i];
+            dc[u] = cls16p ? cls16p[i] : 0u;
           }
         }
+      };
+      fetch(w, cl, tid);
+      for (int i0 = tid; i0 < n8; i0 += kInFlight * kThreads) {
+        fetch(wn, cn, i0 + kInFlight * kThreads);
   #pragma unroll
         for (int u = 0; u < kInFlight; ++u) {
           const int i = i0 + u * kThreads;
-          if (i >= n8) break;
-          const uint32_t words[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
-  #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            count_one(words[k] & 0xffffu, (cl[u] >> (4 * k)) & 3, 8 * i + 2 * k);
-            count_one(words[k] >> 16, (cl[u] >> (4 * k + 2)) & 3, 8 * i + 2 * k + 1);
-          }
+          if (i < n8) take_chunk(w[u], cl[u], i);
         }
+  #pragma unroll
+        for (int u = 0; u < kInFlight; ++u) { w[u] = wn[u]; cl[u] = cn[u]; }
       }
       for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) count_one(c.logits[id], c.class_of(id), id);
   }
