@@ -66,7 +66,7 @@ struct hs_sampler {
   int force_cluster = 0;
   int force_general = 0;  // route bf16 rows through the general (fp32-stage) kernel too
   int2* side_pair = nullptr;  // [batch_max, side_cap] side lists of the bf16 kernel
-  hs::ClassEntry* clist = nullptr;
+  hs::ClassPacked* clist = nullptr;
   unsigned char* needs_count = nullptr;  // [batch_max]
   unsigned long long* split_lists = nullptr;  // [batch_max, kMaxSplit, kSplitCap]
   int* split_n = nullptr;
@@ -159,7 +159,7 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
     split = std::max(1, std::min(split, kMaxSplit));
     if (vocab < split * 2 * hs::kSample) split = 1;
     hs::RowV3Args a3{a, h->clist, h->side_pair, h->side_cap, h->phase_clocks, h->needs_count,
-                     split, h->split_lists, h->split_n, h->split_ticket, 0};
+                     split, h->split_lists, h->split_n, h->split_ticket, 0, batch};
     // The kernels serve disjoint rows, so they run side by side: the candidate kernel on an
     // auxiliary stream forked from the caller's, followed there by the second pass that
     // counts a row whose candidate list overflowed (rare; otherwise an empty launch that
@@ -415,7 +415,7 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   ok = ok && cudaMalloc(&h->split_ticket, (size_t)batch_max * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMemset(h->split_ticket, 0, (size_t)batch_max * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMemset(h->needs_count, 0, (size_t)batch_max) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->clist, (size_t)batch_max * hs::kCells * sizeof(hs::ClassEntry)) == cudaSuccess;
+  ok = ok && cudaMalloc(&h->clist, (size_t)batch_max * (hs::kCells - hs::kV3SharedClasses) * sizeof(hs::ClassPacked)) == cudaSuccess;
   ok = ok && cudaMallocHost(&h->h_params, (size_t)batch_max * sizeof(hs_row_params)) == cudaSuccess;
   ok = ok && cudaMallocHost(&h->h_small, (2 * (size_t)batch_max + 1) * sizeof(int32_t)) == cudaSuccess;
   if (const char* pc = std::getenv("HS_PHASE_CLOCKS")) {

@@ -67,7 +67,8 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
   c.s_pair = args.s_pair + (size_t)c.row * args.s_cap;
   c.s_cap = args.s_cap;
   c.n_s = 0;
-  c.cl = args.clist + (size_t)c.row * kCells;
+  c.scl = reinterpret_cast<ClassPacked*>(smem_raw + lay.scl);
+  c.cl = args.clist + (size_t)c.row * (kCells - kV3SharedClasses);
   c.n_cl = 0;
   c.m = 0.f;
   unsigned long long* clocks = args.phase_clocks ? args.phase_clocks + (size_t)c.row * kV3PhaseSlots : nullptr;
@@ -300,10 +301,8 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
       if (!n) continue;
       const float s = c.cell_score(cell);
       const u64 q = mass_of(s, m);
-      const u64 wgt = (u64)n * q;
-      uint4* dst = reinterpret_cast<uint4*>(c.cl + at);
-      dst[0] = make_uint4(key_of(s), n, (uint32_t)cell, 0u);
-      dst[1] = make_uint4((uint32_t)q, (uint32_t)(q >> 32), (uint32_t)wgt, (uint32_t)(wgt >> 32));
+      ClassPacked* dst = at < kV3SharedClasses ? c.scl + at : c.cl + (at - kV3SharedClasses);
+      *reinterpret_cast<uint4*>(dst) = pack_class(key_of(s), n, (uint32_t)cell, q);
       ++at;
     }
     c.n_cl = (int)tot;
@@ -458,7 +457,7 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
         if (run <= target && target < run + chunk) {
           bool done = false;
           for (int i = tid; i < c.n_cl && !done; i += kThreads) {
-            const ClassEntry e = c.cl[i];
+            const ClassEntry e = c.class_at(i);
             if (e.key <= kept.cut_key) continue;
             if (e.w && target < run + e.w) {
               c.x->bcast[3] = e.cnt;
@@ -479,12 +478,13 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
           Group g{key_of(c.cell_score(cell)), -1, -1, -1};
           if (cell < kV3Bins) g.cell0 = cell; else if (cell < 2 * kV3Bins) g.cell1 = cell; else g.cell2 = cell;
           // only this class, not other members that share its key: large classes by rejection
-          // (about vocab / members scattered probes), small ones by one scan of the row
-          if (members * 8192ull >= (u64)c.vocab) {
+          // (about vocab / members scattered probes, which a lone CTA issues slowly), classes
+          // of up to kV3ListCap tokens by one scan of the row
+          if (members > (u64)kV3ListCap) {
             const u64 per_round = ((u64)c.vocab + members - 1) / members;  // probes for ~63 % success
             const int trials = (int)min((u64)kRandomTrials, max(1ull, (per_round + kThreads - 1) / kThreads));
             token = random_in_class(c, cell, trials, P.seed, 32);
-          } else if (members <= (u64)kV3ListCap) {
+          } else {
             token = nth_in_small_class(c, cell, nth);
           }
           if (token < 0) {
@@ -627,11 +627,6 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
 }
 
 
-// The counting pass of row_kernel_v3 as a kernel of its own: light on registers, several
-// CTAs per SM and per row, so the shared-memory atomics of all SMs work on the counting rows
-// at once.  Each CTA counts its slice of the row per (count class, value) in shared memory and
-// adds its non-empty classes to the row's table in global memory; row_kernel_v3 picks the
-// table up (and clears it for the next step).
 // Rows with 0 < top_k <= kTopKMax: the candidate path.  A row whose candidate list overflows
 // is flagged in needs_count and left to row_kernel_v3, which is launched next.
 __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args args) {
@@ -662,7 +657,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args a
   c.slot = P.slot;
   const bool penalised = P.slot >= 0 && (c.rp != 1.0f || c.pp != 0.0f || c.fp != 0.0f);
   c.cls = penalised ? a.pool.cls + (size_t)P.slot * a.pool.cls_stride : nullptr;
-  c.s_pair = nullptr; c.n_s = 0; c.s_cap = 0; c.cl = nullptr; c.n_cl = 0; c.m = 0.f;
+  c.s_pair = nullptr; c.n_s = 0; c.s_cap = 0; c.scl = nullptr; c.cl = nullptr; c.n_cl = 0; c.m = 0.f;
   c.tab = nullptr; c.hist = nullptr; c.gbuf = nullptr; c.list = nullptr; c.gbuf_n = nullptr;
   unsigned long long* clocks = args.phase_clocks ? args.phase_clocks + (size_t)c.row * kV3PhaseSlots : nullptr;
   auto mark = [&](int slot) {

@@ -58,19 +58,36 @@ struct LocalHist {
   }
 };
 
-// A non-empty class with its score key and mass, computed once per row.
-struct __align__(16) ClassEntry {
-  uint32_t key;   // 32-bit key of the class score
-  uint32_t cnt;   // tokens in the class
-  uint32_t cell;  // count class * kV3Bins + bin
-  uint32_t pad;
-  u64 q;          // mass of one token
-  u64 w;          // cnt * q
+// A non-empty class with its score key and mass, computed once per row.  Stored in 16 bytes
+// (the first kV3SharedClasses of a row in shared memory, the rest in global scratch) and
+// handed to the visitors of for_each_class unpacked.
+struct __align__(16) ClassPacked {
+  uint32_t key;  // 32-bit key of the class score
+  uint32_t cnt;  // tokens in the class
+  u64 qc;        // bits 0..47: mass of one token (<= 2^40); bits 48..63: count class * kV3Bins + bin
 };
+struct ClassEntry {
+  uint32_t key, cnt, cell;
+  u64 q;  // mass of one token
+  u64 w;  // cnt * q
+};
+__device__ __forceinline__ ClassEntry unpack_class(const uint4& v) {
+  ClassEntry e;
+  e.key = v.x;
+  e.cnt = v.y;
+  e.cell = v.w >> 16;
+  e.q = ((u64)(v.w & 0xffffu) << 32) | v.z;
+  e.w = (u64)e.cnt * e.q;
+  return e;
+}
+__device__ __forceinline__ uint4 pack_class(uint32_t key, uint32_t cnt, uint32_t cell, u64 q) {
+  return make_uint4(key, cnt, (uint32_t)q, (uint32_t)(q >> 32) | (cell << 16));
+}
+constexpr int kV3SharedClasses = 6144;  // 96 KB of class entries next to the count table
 
 struct RowV3Args {
   RowKernelArgs base;
-  ClassEntry* clist;  // [batch, kCells] scratch: the row's non-empty classes
+  ClassPacked* clist;  // [batch, kCells - kV3SharedClasses] scratch: classes beyond those held in shared memory
   int2* s_pair;   // [batch, s_cap] side lists: (token id or -1, fp32 bits of the score)
   int s_cap;
   unsigned long long* phase_clocks;  // [batch, kV3PhaseSlots] or null
@@ -80,10 +97,11 @@ struct RowV3Args {
   int* split_n;                      // [batch, split] their lengths
   int* split_ticket;                 // [batch] arrival counter (returns to 0)
   int pass;                          // row_kernel_v3: 0 = rows without a small top_k, 1 = rows the candidate kernel handed back
+  int batch;                         // rows in the launch
 };
 
 struct LayoutV3 {
-  size_t x, tab, hist, gbuf, list, rare, small, total;
+  size_t x, tab, hist, gbuf, list, rare, small, scl, total;
 };
 __host__ __device__ inline LayoutV3 layout_v3() {
   LayoutV3 l{};
@@ -100,6 +118,7 @@ __host__ __device__ inline LayoutV3 layout_v3() {
   l.list = take(sizeof(V3Entry) * kV3ListCap);
   l.rare = take(sizeof(int) * kV3RareCap);
   l.small = take(sizeof(int) * 16);
+  l.scl = take(sizeof(ClassPacked) * kV3SharedClasses);
   l.total = off;
   return l;
 }
@@ -131,7 +150,13 @@ struct Ctx3 {
   int slot;
   int2* s_pair;
   int n_s, s_cap;
-  ClassEntry* cl;    // this row's non-empty classes, ascending class index
+  ClassPacked* scl;  // this row's non-empty classes: entries [0, kV3SharedClasses) in shared memory,
+  ClassPacked* cl;   // the rest in global scratch
+  // entry i of the row's class list
+  __device__ __forceinline__ ClassEntry class_at(int i) const {
+    const ClassPacked* p = i < kV3SharedClasses ? scl + i : cl + (i - kV3SharedClasses);
+    return unpack_class(*reinterpret_cast<const uint4*>(p));
+  }
   int n_cl;
   float T, rp, pp, fp;
   bool greedy;
@@ -183,29 +208,25 @@ __device__ __forceinline__ void for_each_side3(const Ctx3& c, F&& f) {
   }
 }
 // Calls f(entry) for the row's non-empty classes, thread t taking entries t, t + kThreads, ...
-// (four 32-byte entries in flight per thread).
 template <class F>
 __device__ __forceinline__ void for_each_class(const Ctx3& c, F&& f) {
-  for (int i0 = threadIdx.x; i0 < c.n_cl; i0 += 4 * kThreads) {
-    uint4 lo[4], hi[4];
+  const int n_shared = min(c.n_cl, kV3SharedClasses);
+#pragma unroll 4
+  for (int i = threadIdx.x; i < n_shared; i += kThreads) f(unpack_class(reinterpret_cast<const uint4*>(c.scl)[i]));
+  // the overflow in global scratch, four entries in flight per thread
+  const int n_global = c.n_cl - n_shared;
+  for (int i0 = threadIdx.x; i0 < n_global; i0 += 4 * kThreads) {
+    uint4 v[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int i = i0 + u * kThreads;
-      if (i < c.n_cl) {
-        const uint4* p = reinterpret_cast<const uint4*>(c.cl + i);
-        lo[u] = p[0];
-        hi[u] = p[1];
-      }
+      if (i < n_global) v[u] = reinterpret_cast<const uint4*>(c.cl)[i];
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int i = i0 + u * kThreads;
-      if (i >= c.n_cl) break;
-      ClassEntry e;
-      e.key = lo[u].x; e.cnt = lo[u].y; e.cell = lo[u].z; e.pad = 0;
-      e.q = ((u64)hi[u].y << 32) | hi[u].x;
-      e.w = ((u64)hi[u].w << 32) | hi[u].z;
-      f(e);
+      if (i >= n_global) break;
+      f(unpack_class(v[u]));
     }
   }
 }
@@ -619,6 +640,14 @@ __device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
   const uint32_t vv = raw | (raw << 16);
   int* ids = reinterpret_cast<int*>(c.gbuf);
   if (tid == 0) *c.gbuf_n = 0;
+  {
+    // the row may have left L2 since it was counted
+    constexpr uint32_t kPiece = 16384;
+    const size_t row_bytes = ((size_t)c.vocab * 2) & ~(size_t)15;
+    for (size_t at = (size_t)tid * kPiece; at < row_bytes; at += (size_t)kThreads * kPiece)
+      prefetch_l2_bulk(reinterpret_cast<const unsigned char*>(c.logits) + at,
+                       (uint32_t)min((size_t)kPiece, row_bytes - at));
+  }
   __syncthreads();
   const int n8 = c.vocab / 8;
   const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);

@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(kThreads, 2) shard_partial_kernel(const ShardA
   c.slot = P.slot;
   const bool penalised = P.slot >= 0 && (c.rp != 1.0f || c.pp != 0.0f || c.fp != 0.0f);
   c.cls = penalised ? a.pool.cls + (size_t)P.slot * a.pool.cls_stride : nullptr;
-  c.s_pair = nullptr; c.n_s = 0; c.s_cap = 0; c.cl = nullptr; c.n_cl = 0; c.m = 0.f;
+  c.s_pair = nullptr; c.n_s = 0; c.s_cap = 0; c.scl = nullptr; c.cl = nullptr; c.n_cl = 0; c.m = 0.f;
   c.tab = nullptr; c.hist = nullptr; c.gbuf = nullptr; c.list = nullptr; c.gbuf_n = nullptr;
   hs_shard_rec* rec = args.recs + c.row;
   if (tid < 16) small[tid] = 0;
