@@ -160,16 +160,17 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
     if (vocab < split * 2 * hs::kSample) split = 1;
     hs::RowV3Args a3{a, h->clist, h->side_pair, h->side_cap, h->phase_clocks, h->needs_count,
                      split, h->split_lists, h->split_n, h->split_ticket, 0, batch};
-    // The kernels serve disjoint rows, so they run side by side: the candidate kernel on an
-    // auxiliary stream forked from the caller's, followed there by the second pass that
-    // counts a row whose candidate list overflowed (rare; otherwise an empty launch that
-    // hides behind the counting kernel).
+    // The kernels serve disjoint rows and run side by side.  The counting kernel goes first:
+    // its rows are the long ones and take an SM each, while the candidate kernel (on an
+    // auxiliary stream forked from the caller's) fills the SMs that are left and those that
+    // free up.  The second counting pass for a row whose candidate list overflowed (rare;
+    // otherwise an empty launch) follows the candidate kernel on its stream.
     HS_CUDA(h, cudaEventRecord(h->ev_fork, stream));
     HS_CUDA(h, cudaStreamWaitEvent(h->aux_stream, h->ev_fork, 0));
-    hs::row_kernel_topk<<<dim3((unsigned)split, (unsigned)batch), hs::kThreads, hs::layout_cand().total, h->aux_stream>>>(a3);
-    HS_CUDA(h, cudaGetLastError());
     a3.pass = 0;
     hs::row_kernel_v3<<<(unsigned)batch, hs::kThreads, hs::layout_v3().total, stream>>>(a3);
+    HS_CUDA(h, cudaGetLastError());
+    hs::row_kernel_topk<<<dim3((unsigned)split, (unsigned)batch), hs::kThreads, hs::layout_cand().total, h->aux_stream>>>(a3);
     HS_CUDA(h, cudaGetLastError());
     a3.pass = 1;
     hs::row_kernel_v3<<<(unsigned)batch, hs::kThreads, hs::layout_v3().total, h->aux_stream>>>(a3);

@@ -76,6 +76,11 @@ __device__ __forceinline__ Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint3
 }
 
 // ---- warp / block primitives ---------------------------------------------------------
+__device__ __forceinline__ u64 shfl_xor_u64(u64 v, int lane_mask) {
+  const uint32_t lo = __shfl_xor_sync(0xffffffffu, (uint32_t)v, lane_mask);
+  const uint32_t hi = __shfl_xor_sync(0xffffffffu, (uint32_t)(v >> 32), lane_mask);
+  return ((u64)hi << 32) | lo;
+}
 __device__ __forceinline__ u64 shfl_u64(u64 v, int src) {
   return __shfl_sync(0xffffffffu, v, src);
 }

@@ -233,10 +233,12 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
     if (penalised) {
       n_heavy = min(a.pool.n_heavy[P.slot], min(a.pool.unique_cap, args.s_cap));
       const int32_t* heavy = a.pool.heavy + (size_t)P.slot * a.pool.unique_cap;
+      const int2* pairs = a.pool.pairs + (size_t)P.slot * a.pool.unique_cap;
       for (int j = tid; j < n_heavy; j += kThreads) {
-        const int id = heavy[j];
-        if (id < 0 || id >= c.vocab) { c.s_pair[j] = make_int2(-1, 0); continue; }
-        put(j, id, c.score_of(c.logits[id], c.heavy_count(id)));
+        const int q = heavy[j];
+        const int2 pr = q >= 0 && q < a.pool.unique_cap ? pairs[q] : make_int2(-1, 0);  // (id, count)
+        if (pr.x < 0 || pr.x >= c.vocab) { c.s_pair[j] = make_int2(-1, 0); continue; }
+        put(j, pr.x, c.score_of(c.logits[pr.x], pr.y));
       }
     }
     const int n_rare = *rare_n;
@@ -669,7 +671,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args a
   __syncthreads();
   int n = c.hi > c.lo ? topk_candidates(c, L, min(P.top_k, c.hi - c.lo)) : 0;
   mark(1);
-  if (n > P.top_k) {
+  // a lone CTA cuts its list at the k-th highest score now; a part of a split row hands its
+  // candidates over as they are unless they would crowd the merged list
+  if (n > P.top_k && (split == 1 || n > kCandCap / split)) {
     const uint32_t cut = cand_kth_key(*c.x, L, n, P.top_k);
     n = cand_compact(L, n, cut);
   } else if (n > 0) {
@@ -685,6 +689,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args a
     if (tid == 0) small[6] = atomicAdd(&args.split_ticket[c.row], 1);
     __syncthreads();
     if (small[6] != split - 1) return;
+    mark(12);
     __threadfence();
     if (tid == 0) { args.split_ticket[c.row] = 0; *L.n = 0; small[7] = 0; }
     __syncthreads();
@@ -700,8 +705,9 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args a
       __syncthreads();
     }
     n = *L.n;
+    mark(13);
     if (small[7] || n > kCandCap) n = -1;
-    if (n > P.top_k) {
+    if (n > kSortAll) {
       const uint32_t cut = cand_kth_key(*c.x, L, n, P.top_k);
       n = cand_compact(L, n, cut);
     }
@@ -711,10 +717,20 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args a
     return;
   }
   if (tid == 0) args.needs_count[c.row] = 0;
+  mark(14);
   cand_sort(L, n);
+  mark(15);
+  if (n > P.top_k) {
+    // a list that was sorted whole: top-k keeps the first k entries and the ties of the k-th
+    const uint32_t cut = cand_key(L.cand[P.top_k - 1]);
+    u64 keep = 0, unused = 0;
+    for (int i = tid; i < n; i += kThreads) keep += cand_key(L.cand[i]) >= cut ? 1 : 0;
+    block_sum2(*c.x, keep, unused);
+    n = (int)keep;
+  }
   mark(2);
   const float* noise_row = a.noise ? a.noise + (size_t)c.row * a.vocab : nullptr;
-  const FinishOut r = finish_sorted(*c.x, L.cand, reinterpret_cast<u64*>(smem_raw + lay.mass), n, P, noise_row, out);
+  const FinishOut r = finish_sorted(*c.x, L.cand, reinterpret_cast<u64*>(smem_raw + lay.mass), n, P, noise_row, out, clocks);
   if (a.scores_out) {
     float* dst = a.scores_out + (size_t)c.row * a.vocab;
     for (int id = tid; id < c.vocab; id += kThreads) dst[id] = __int_as_float(0xff800000);

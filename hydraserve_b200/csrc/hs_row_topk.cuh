@@ -29,6 +29,7 @@ namespace hs {
 constexpr int kTopKMax = 256;      // largest top_k served by the candidate path
 constexpr int kCandCap = 4096;     // candidate list capacity (shared memory, 8 bytes each)
 constexpr int kCandSoft = 2048;    // raise the bound once the list is this long
+constexpr int kSortAll = 128;      // a merged list this short is sorted whole instead of cut first
 constexpr int kSample = 16384;     // tokens sampled (their raw values only) to get the first bound
 
 // (score key << 32) | ~id : sorting these descending orders by score, then by ascending id
@@ -57,14 +58,28 @@ struct CandCtx {
   unsigned long long* dbg;  // optional phase clocks of this row (tuning aid), or null
 };
 
-// The k-th highest key among the n list entries (n >= k >= 1): three count-only radix levels.
+// The k-th highest key among the n list entries (n >= k >= 1): count-only radix levels of
+// 11 + 11 + 10 bits.  Candidates lie close together, so a level whose bits are the same in
+// the lowest and the highest key is skipped.
 __device__ uint32_t cand_kth_key(Exchange& x, CandCtx& L, int n, int k) {
   const int tid = threadIdx.x;
+  uint32_t lo_key = 0xffffffffu, hi_key = 0u;
+  for (int i = tid; i < n; i += kThreads) {
+    const uint32_t key = cand_key(L.cand[i]);
+    lo_key = min(lo_key, key);
+    hi_key = max(hi_key, key);
+  }
+  hi_key = block_max_u32(x, hi_key);
+  lo_key = ~block_max_u32(x, ~lo_key);
   uint32_t prefix = 0;
   int want = k;
   for (int level = 0; level < 3; ++level) {
     const int shift = level_shift(level), bits = level_bits(level);
     const uint32_t mask = (1u << bits) - 1u;
+    if ((lo_key >> shift) == (hi_key >> shift)) {  // one bucket holds everything that is left
+      prefix = hi_key >> shift;
+      continue;
+    }
     for (int b = tid; b < kBins; b += kThreads) L.count[b] = 0;
     __syncthreads();
     for (int i = tid; i < n; i += kThreads) {
@@ -98,6 +113,9 @@ __device__ uint32_t cand_kth_key(Exchange& x, CandCtx& L, int n, int k) {
     prefix = (prefix << bits) | (uint32_t)x.bcast[0];
     want -= (int)x.bcast[1];
     __syncthreads();
+    // keys outside the chosen bucket no longer matter for the remaining levels
+    lo_key = max(lo_key, prefix << shift);
+    hi_key = min(hi_key, (prefix << shift) | ((1u << shift) - 1u));
   }
   return prefix;
 }
@@ -124,94 +142,121 @@ __device__ int cand_compact(CandCtx& L, int n, uint32_t bound) {
   return *L.n;
 }
 
-// Per count class, the lowest raw value (as signed 16-bit image) whose score reaches `bound`.
+// Per count class, the lowest raw value (as signed 16-bit image) whose score reaches `bound`
+// (32768 if none does).  Scores grow with the value inside a class, so warp cc searches the
+// 65,536 values of class cc 32 at a time: four rounds of one evaluation per lane and a ballot.
 __device__ void cand_thresholds(const Ctx3& c, CandCtx& L, uint32_t bound) {
-  if (threadIdx.x < 3) {
-    const int cc = threadIdx.x;
-    int lo = -32768, hi = 32767;  // find the lowest t with key(score(t, cc)) >= bound; 32768 if none
-    if (key_of(c.score_of(raw_of_t16(hi), cc)) < bound) {
-      lo = 32768;
-    } else {
-      while (lo < hi) {
-        const int mid = lo + ((hi - lo) >> 1);
-        if (key_of(c.score_of(raw_of_t16(mid), cc)) >= bound) hi = mid; else lo = mid + 1;
-      }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp < 3) {
+    const int cc = warp;
+    // every t < lo fails, every t >= hi passes (hi = 32768 stands for "none")
+    int lo = -32768, hi = 32768;
+#pragma unroll 1
+    while (lo < hi) {
+      const int step = (hi - lo + 31) >> 5;
+      const int t = lo + (lane + 1) * step - 1;  // last value of this lane's block
+      const bool pass = t >= hi || key_of(c.score_of(raw_of_t16(t), cc)) >= bound;
+      const uint32_t votes = __ballot_sync(0xffffffffu, pass);
+      if (votes == 0) { lo = hi; break; }
+      const int f = __ffs(votes) - 1;  // the answer lies in block f
+      hi = min(lo + (f + 1) * step - 1, hi);
+      lo = lo + f * step;
     }
-    // -0.0 scores like +0.0 but sits one step below it in the integer order
-    if (lo == 0) lo = -1;
-    L.thr[cc] = lo;
+    if (lane == 0) {
+      // -0.0 scores like +0.0 but sits one step below it in the integer order
+      if (lo == 0) lo = -1;
+      L.thr[cc] = lo;
+    }
   }
   __syncthreads();
 }
 
-// The k-th highest raw value (as signed 16-bit image) among the tokens of [begin, end) that
-// the history does not hold, or -32768 when there are fewer than k of them.  Two radix
-// levels over the 16 bits (2,048 buckets of 32 values, then the 32 values of one bucket).
+// A lower bound (as signed 16-bit image of a raw value) of the k-th highest raw value among
+// the tokens of [begin, end) that the history does not hold, or -32768 when none is found.
+// The sampled tokens are cut into groups of eight (one 128-bit load); the k highest group
+// maxima are k different tokens, so the k-th highest maximum is such a bound, and with
+// k much smaller than the number of groups it is about as tight as the k-th highest token.
+// Each thread keeps its (at most four) group maxima in registers; the k-th highest of them
+// is found with two count-only radix levels of eight bits.
 __device__ int sample_kth_t16(const Ctx3& c, CandCtx& L, int begin, int end, int k) {
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kGroups = 4;  // per thread: kSample = kGroups * 8 * kThreads
+  static_assert(kSample == kGroups * 8 * kThreads, "one 128-bit load per group");
   const bool vec = c.vec && (begin & 7) == 0;
   const int n8 = vec ? (end - begin) / 8 : 0;  // whole 8-token chunks read as 128-bit words
   const uint4* src4 = reinterpret_cast<const uint4*>(c.logits) + (begin >> 3);
   const unsigned short* cls16p = c.cls ? reinterpret_cast<const unsigned short*>(c.cls) + (begin >> 3) : nullptr;
-  int prefix = -1;
-  int want = k;
-  for (int level = 0; level < 2; ++level) {
-    for (int b = tid; b < kBins; b += kThreads) L.count[b] = 0;
-    __syncthreads();
-    auto see = [&](uint32_t raw) {
-      const int v = t16_of_raw(raw) + 32768;  // 0 .. 65535, float order
-      if (level == 0) atomicAdd(&L.count[v >> 5], 1u);
-      else if ((v >> 5) == prefix) atomicAdd(&L.count[v & 31], 1u);
-    };
-    for (int i0 = tid; i0 < n8; i0 += 4 * kThreads) {
-      uint4 w[4];
-      uint32_t cl[4];
+  int top[kGroups];  // value + 32768 of the group maximum, 0 = no token
+  {
+    uint4 w[kGroups];
+    uint32_t cl[kGroups];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * kThreads;
-        if (i < n8) { w[u] = src4[i]; cl[u] = cls16p ? cls16p[i] : 0u; }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (i0 + u * kThreads >= n8) break;
-        const uint32_t words[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-          if (((cl[u] >> (2 * q)) & 3u) == 0) see((words[q >> 1] >> (16 * (q & 1))) & 0xffffu);
-      }
+    for (int u = 0; u < kGroups; ++u) {
+      const int i = tid + u * kThreads;
+      if (i < n8) { w[u] = src4[i]; cl[u] = cls16p ? cls16p[i] : 0u; }
     }
-    for (int id = begin + n8 * 8 + tid; id < end; id += kThreads)
-      if (c.class_of(id) == 0) see(c.logits[id]);
+#pragma unroll
+    for (int u = 0; u < kGroups; ++u) {
+      top[u] = 0;
+      if (tid + u * kThreads >= n8) continue;
+      const uint32_t words[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (((cl[u] >> (2 * q)) & 3u) == 0)
+          top[u] = max(top[u], t16_of_raw((words[q >> 1] >> (16 * (q & 1))) & 0xffffu) + 32768);
+    }
+  }
+  if (!vec) {
+    // a part that is not 16-byte aligned: thread-strided groups over the scalar view
+    for (int id = begin + tid; id < end; id += kThreads)
+      if (c.class_of(id) == 0) top[0] = max(top[0], t16_of_raw(c.logits[id]) + 32768);
+  }
+  // k-th highest of the positive maxima: bins of L.count, 256 per level
+  int prefix = 0, want = k;
+  for (int level = 0; level < 2; ++level) {
+    if (tid < 256) L.count[tid] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < kGroups; ++u) {
+      if (top[u] <= 0) continue;
+      if (level == 0) atomicAdd(&L.count[top[u] >> 8], 1u);
+      else if ((top[u] >> 8) == prefix) atomicAdd(&L.count[top[u] & 255], 1u);
+    }
     if (tid == 0) L.thr[3] = -1;
     __syncthreads();
-    constexpr int kPer = kBins / kThreads;
-    const int hi = kBins - 1 - kPer * tid;
-    u64 sum = 0;
+    if (warp == 0) {
+      // lane l owns bins 255 - 8 l ... 248 - 8 l (descending)
+      const int hi = 255 - 8 * lane;
+      uint32_t sum = 0;
 #pragma unroll
-    for (int u = 0; u < kPer; ++u) sum += L.count[hi - u];
-    const u64 incl = warp_scan_u64(sum);
-    u64 pre, pu, tot, tu;
-    block_warp_prefix2(*c.x, shfl_u64(incl, 31), 0, pre, pu, tot, tu);
-    u64 ex = pre + incl - sum;
-    if (ex < (u64)want && (u64)want <= ex + sum) {
+      for (int u = 0; u < 8; ++u) sum += L.count[hi - u];
+      uint32_t incl = sum;
 #pragma unroll
-      for (int u = 0; u < kPer; ++u) {
-        const u64 bc = L.count[hi - u];
-        if ((u64)want <= ex + bc) {
-          L.thr[3] = hi - u;
-          c.x->bcast[1] = ex;
-          break;
+      for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t o = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += o;
+      }
+      uint32_t ex = incl - sum;
+      if (ex < (uint32_t)want && (uint32_t)want <= incl) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint32_t bc = L.count[hi - u];
+          if ((uint32_t)want <= ex + bc) {
+            L.thr[3] = hi - u;
+            c.x->bcast[1] = ex;
+            break;
+          }
+          ex += bc;
         }
-        ex += bc;
       }
     }
     __syncthreads();
     const int found = L.thr[3];
     const int above = (int)c.x->bcast[1];
     __syncthreads();
-    if (found < 0) return -32768;  // fewer than k such tokens
+    if (found < 0) return -32768;  // fewer than k groups with a token outside the history
     want -= above;
-    if (level == 0) prefix = found; else return ((prefix << 5) | found) - 32768;
+    if (level == 0) prefix = found; else return ((prefix << 8) | found) - 32768;
   }
   return -32768;
 }
@@ -249,15 +294,20 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
   if (c.cls) {
     const int n_heavy = min(c.pool.n_heavy[c.slot], c.pool.unique_cap);
     const int32_t* heavy = c.pool.heavy + (size_t)c.slot * c.pool.unique_cap;
+    const int2* pairs = c.pool.pairs + (size_t)c.slot * c.pool.unique_cap;
     for (int j = tid; j < n_heavy; j += kThreads) {
-      const int id = heavy[j];
-      if (id >= c.lo && id < c.hi) push(id, c.logits[id], 3);
+      const int q = heavy[j];
+      if (q < 0 || q >= c.pool.unique_cap) continue;
+      const int2 pr = pairs[q];  // (id, count)
+      if (pr.x < c.lo || pr.x >= c.hi) continue;
+      const int slot = atomicAdd(L.n, 1);  // stored scored: the exact count is at hand
+      if (slot < kCandCap) L.cand[slot] = cand_pack(key_of(c.score_of(c.logits[pr.x], pr.y)), pr.x);
+      else *L.lost = 1;
     }
   }
   __syncthreads();
   if (*L.lost) return -1;
   int n = min(*L.n, kCandCap);
-  score_pending(0, n);
   // the first bound: k-th highest raw value among the sampled tokens outside the history
   const int t_k = sample_kth_t16(c, L, c.lo, min(c.hi, c.lo + kSample), k);
   uint32_t bound = t_k > -32768 ? key_of(c.score_of(raw_of_t16(t_k), 0)) : 0u;
@@ -334,9 +384,25 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
 }
 
 // Sorts the first n list entries descending (bitonic, n padded to a power of two with zeros).
+// A compare-exchange step of stride <= 32 stays inside the 64 entries one warp handles, so
+// only the wider steps (and the changes between the two kinds) need the block barrier.
 __device__ void cand_sort(CandCtx& L, int n) {
+  if (n <= 128) {
+    // short list: every entry counts the entries above it (entries are distinct: they end
+    // in the token id) and moves to that position
+    const int i = threadIdx.x;
+    const u64 mine = i < n ? L.cand[i] : 0ull;
+    int rank = 0;
+    if (i < n)
+      for (int j = 0; j < n; ++j) rank += L.cand[j] > mine ? 1 : 0;
+    __syncthreads();
+    if (i < n) L.cand[rank] = mine;
+    __syncthreads();
+    return;
+  }
   int p = 1;
   while (p < n) p <<= 1;
+  if (p < 64) p = 64;
   for (int i = n + threadIdx.x; i < p; i += kThreads) L.cand[i] = 0ull;
   __syncthreads();
   for (int size = 2; size <= p; size <<= 1) {
@@ -348,9 +414,12 @@ __device__ void cand_sort(CandCtx& L, int n) {
         const u64 a = L.cand[lo], b = L.cand[hi];
         if ((a < b) == desc) { L.cand[lo] = b; L.cand[hi] = a; }
       }
-      __syncthreads();
+      // the next step: stride / 2, or size (the first stride of the next size)
+      const int next = stride > 1 ? (stride >> 1) : size;
+      if (stride > 32 || next > 32) __syncthreads(); else __syncwarp();
     }
   }
+  __syncthreads();
 }
 
 struct FinishOut {
@@ -364,86 +433,109 @@ struct FinishOut {
 
 // Everything after top-k on a list sorted by (score descending, id ascending): min-p, top-p,
 // draw, log-probabilities.  n = tokens that survived top-k (ties included), n >= 1.
-// `mass` is scratch for n 64-bit values.
-__device__ FinishOut finish_sorted(Exchange& x, const u64* cand, u64* mass, int n, const hs_row_params& P,
-                                   const float* noise_row, hs_row_out* out) {
-  const int tid = threadIdx.x;
+// `mass` is scratch for n 64-bit values.  WARP = true: run by ONE warp (reductions are
+// shuffles, no block barrier); false: by the whole CTA.
+template <bool WARP>
+__device__ FinishOut finish_impl(Exchange& x, const u64* cand, u64* mass, int n, const hs_row_params& P,
+                                 const float* noise_row, hs_row_out* out, unsigned long long* dbg) {
+  const int tid = WARP ? (int)(threadIdx.x & 31) : (int)threadIdx.x;
+  constexpr int kLanes = WARP ? 32 : kThreads;
+  auto sync = [&]() { if (WARP) __syncwarp(); else __syncthreads(); };
+  auto sum = [&](u64 v) -> u64 {
+    if (WARP) return warp_sum_u64(v);
+    u64 unused = 0;
+    block_sum2(x, v, unused);
+    return v;
+  };
   FinishOut r;
   r.status = 0;
   r.n_topk = (u64)n;
   const float m = score_of(cand_key(cand[0]));
   r.m = m;
   // masses and their inclusive prefix, each thread owning a contiguous run of entries
-  const int per = (n + kThreads - 1) / kThreads;
+  const int per = (n + kLanes - 1) / kLanes;
   const int i0 = min(tid * per, n), i1 = min(i0 + per, n);
   u64 run = 0;
   for (int i = i0; i < i1; ++i) { run += mass_of(score_of(cand_key(cand[i])), m); mass[i] = run; }
-  u64 incl = warp_scan_u64(run);
-  u64 pre, pu, z1, tu;
-  block_warp_prefix2(x, shfl_u64(incl, 31), 0, pre, pu, z1, tu);
-  const u64 my_off = pre + incl - run;
+  const u64 incl = warp_scan_u64(run);
+  u64 my_off, z1;
+  if (WARP) {
+    my_off = incl - run;
+    z1 = shfl_u64(incl, 31);
+  } else {
+    u64 pre, pu, tu;
+    block_warp_prefix2(x, shfl_u64(incl, 31), 0, pre, pu, z1, tu);
+    my_off = pre + incl - run;
+  }
   for (int i = i0; i < i1; ++i) mass[i] += my_off;  // mass[i] = inclusive cumulative mass
-  __syncthreads();
+  sync();
   // min-p: the passing tokens are a prefix
   int n1 = n;
   if (P.min_p > 0.0f) {
     const float z1f = mass_to_float(z1);
     const float thr = __fmul_rn(__fdiv_rn(1.0f, z1f), P.min_p);
-    u64 pass = 0, unused = 0;
-    for (int i = tid; i < n; i += kThreads) {
+    u64 pass = 0;
+    for (int i = tid; i < n; i += kLanes) {
       const float s = score_of(cand_key(cand[i]));
       pass += !(__fdiv_rn(expf(s - m), z1f) < thr) ? 1 : 0;
     }
-    block_sum2(x, pass, unused);
-    n1 = max(1, (int)pass);
+    n1 = max(1, (int)sum(pass));
   }
   r.n_minp = (u64)n1;
+  if (dbg && tid == 0) dbg[9] = clock64();
   // top-p: shortest prefix whose mass reaches the target
   int n2 = n1;
   r.cut_ties = -1;
   if (P.top_p < 1.0f) {
     const u64 z2 = mass[n1 - 1];
     const u64 target = top_p_target(z2, P.top_p);
-    u64 below = 0, unused = 0;
-    for (int i = tid; i < n1; i += kThreads) below += mass[i] < target ? 1 : 0;
-    block_sum2(x, below, unused);
-    n2 = min(n1, (int)below + 1);
+    u64 below = 0;
+    for (int i = tid; i < n1; i += kLanes) below += mass[i] < target ? 1 : 0;
+    n2 = min(n1, (int)sum(below) + 1);
     const uint32_t ck = cand_key(cand[n2 - 1]);
     u64 ties = 0;
-    for (int i = tid; i < n2; i += kThreads) ties += cand_key(cand[i]) == ck ? 1 : 0;
-    block_sum2(x, ties, unused);
-    r.cut_ties = (long long)ties;
+    for (int i = tid; i < n2; i += kLanes) ties += cand_key(cand[i]) == ck ? 1 : 0;
+    r.cut_ties = (long long)sum(ties);
   }
   r.n_kept = (u64)n2;
   r.cut_key = cand_key(cand[n2 - 1]);
   const u64 z3 = mass[n2 - 1];
+  if (dbg && tid == 0) dbg[10] = clock64();
   // draw
   if (noise_row) {
     const float zf = mass_to_float(z3);
     u64 best = 0;
-    for (int i = tid; i < n2; i += kThreads) {
+    for (int i = tid; i < n2; i += kLanes) {
       const int id = cand_id(cand[i]);
       const float p = __fdiv_rn(expf(score_of(cand_key(cand[i])) - m), zf);
       const float ratio = __fdiv_rn(p, noise_row[id]);
       const u64 packed = ((u64)__float_as_uint(ratio) << 32) | (uint32_t)(~(uint32_t)id);
       best = packed > best ? packed : best;
     }
-    best = block_max_u64(x, best);
+    if (WARP) {
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) {
+        const u64 o = shfl_xor_u64(best, d);
+        best = o > best ? o : best;
+      }
+    } else {
+      best = block_max_u64(x, best);
+    }
     r.token = (int)(~(uint32_t)(best & 0xffffffffu));
   } else {
     const Philox4 ph = philox4x32_10(0u, 0u, 0u, 0u, (uint32_t)P.seed, (uint32_t)(P.seed >> 32));
     const u64 target = __umul64hi(((u64)ph.v[0] << 32) | ph.v[1], z3);
-    u64 le = 0, unused = 0;
-    for (int i = tid; i < n2; i += kThreads) le += mass[i] <= target ? 1 : 0;
-    block_sum2(x, le, unused);
-    r.token = cand_id(cand[min((int)le, n2 - 1)]);
+    u64 le = 0;
+    for (int i = tid; i < n2; i += kLanes) le += mass[i] <= target ? 1 : 0;
+    r.token = cand_id(cand[min((int)sum(le), n2 - 1)]);
   }
+  if (dbg && tid == 0) dbg[11] = clock64();
   // log-probabilities over the kept set
   r.log_z = 0.f;
   if (P.n_logprobs >= 0) {
     r.log_z = (float)(log((double)z3) - (double)kMassShift * 0.6931471805599453);
     const int n_want = min(P.n_logprobs, n2);
-    for (int i = tid; i < n2; i += kThreads) {
+    for (int i = tid; i < n2; i += kLanes) {
       const float lp = (score_of(cand_key(cand[i])) - m) - r.log_z;
       if (i < n_want) { out->top_ids[i] = cand_id(cand[i]); out->top_logprobs[i] = lp; }
       if (cand_id(cand[i]) == r.token) out->logprob = lp;
@@ -453,6 +545,24 @@ __device__ FinishOut finish_sorted(Exchange& x, const u64* cand, u64* mass, int 
     out->n_top = 0;
     out->logprob = 0.f;
   }
+  return r;
+}
+
+constexpr int kWarpFinish = 1024;  // lists up to this length are finished by one warp
+
+// The finisher, called by the whole CTA (the list complete and visible to all threads);
+// every thread gets the result.
+__device__ FinishOut finish_sorted(Exchange& x, const u64* cand, u64* mass, int n, const hs_row_params& P,
+                                   const float* noise_row, hs_row_out* out, unsigned long long* dbg = nullptr) {
+  if (n > kWarpFinish) return finish_impl<false>(x, cand, mass, n, P, noise_row, out, dbg);
+  __shared__ FinishOut shared_result;
+  if (threadIdx.x < 32) {
+    const FinishOut r = finish_impl<true>(x, cand, mass, n, P, noise_row, out, dbg);
+    if (threadIdx.x == 0) shared_result = r;
+  }
+  __syncthreads();
+  const FinishOut r = shared_result;
+  __syncthreads();
   return r;
 }
 

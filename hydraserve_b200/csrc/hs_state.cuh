@@ -8,8 +8,8 @@
 //             when tokens are appended
 //   cls[]     dense 2-bit class per token, min(count, 3), sixteen tokens per 32-bit word: what
 //             the bf16 sampling kernel streams next to the logits (V/4 bytes per row)
-//   heavy[]   the ids whose count reached 3: the only tokens whose exact count the bf16
-//             kernel has to look up (through pos and pairs)
+//   heavy[]   positions in pairs of the ids whose count reached 3: the only tokens whose
+//             exact count the bf16 kernels need (one look-up gives id and count)
 #pragma once
 
 #include "hs_common.cuh"
@@ -22,7 +22,7 @@ struct Pool {
   int32_t* n;      // [slots_total]
   int32_t* pos;    // [slots_total, pos_stride]
   uint32_t* cls;   // [slots_total, cls_stride] 2-bit classes
-  int32_t* heavy;  // [slots_total, unique_cap]
+  int32_t* heavy;  // [slots_total, unique_cap] positions in pairs
   int32_t* n_heavy;  // [slots_total]
   int32_t* error;  // [1] sticky: 1 = a slot overflowed unique_cap
   int slots_total;
@@ -130,7 +130,7 @@ __global__ void slots_classify_kernel(Pool p, const int32_t* tokens, const int32
     const uint32_t before = set_class(cls, t, count);
     if (count >= 3 && before < 3u) {
       const int idx = atomicAdd(&p.n_heavy[s], 1);
-      if (idx < p.unique_cap) heavy[idx] = t;
+      if (idx < p.unique_cap) heavy[idx] = q - 1;
     }
   }
 }
@@ -158,7 +158,7 @@ __device__ __forceinline__ bool slot_append_one(const Pool& p, int s, int token)
     *word = (*word & ~(3u << shift)) | ((uint32_t)count << shift);
     if (count == 3) {
       const int h = p.n_heavy[s];
-      if (h < p.unique_cap) { (p.heavy + (size_t)s * p.unique_cap)[h] = token; p.n_heavy[s] = h + 1; }
+      if (h < p.unique_cap) { (p.heavy + (size_t)s * p.unique_cap)[h] = pos[token] - 1; p.n_heavy[s] = h + 1; }
     }
   }
   return true;
