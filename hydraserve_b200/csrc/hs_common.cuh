@@ -43,6 +43,24 @@ __device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) 
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
+// Loads the compiler must issue where they are written (it may otherwise sink a load to its
+// first use, which defeats starting a chain of dependent reads early).
+__device__ __forceinline__ int load_now_s32(const int* p) {
+  int v;
+  asm volatile("ld.global.s32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ int2 load_now_int2(const int2* p) {
+  int2 v;
+  asm volatile("ld.global.v2.s32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t load_now_u16(const unsigned short* p) {
+  unsigned short v;
+  asm volatile("ld.global.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return v;
+}
+
 // ---- probability mass as an exact integer -------------------------------------------
 // e = exp(s - m) in (0, 1]; mass = round(e * 2^40).  Sums of masses are exact and do not
 // depend on the order of accumulation, which makes every cut reproducible.

@@ -15,7 +15,7 @@ namespace hs {
 // One chunk of eight tokens the counting loop could not take in its branch-free form (a
 // value outside the bin window, a token of count class 3): token by token, out of line so
 // that the unrolled loop stays small.
-__device__ __noinline__ void count_chunk_slow(uint32_t* tab, int* rare_n, int* rare_id, uint4 w, uint32_t cl, int i) {
+__device__ __noinline__ void count_chunk_slow(uint32_t* tab, int* rare_n, int2* rare, uint4 w, uint32_t cl, int i) {
   const uint32_t words[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll 1
   for (int k = 0; k < 8; ++k) {
@@ -27,7 +27,7 @@ __device__ __noinline__ void count_chunk_slow(uint32_t* tab, int* rare_n, int* r
       atomicAdd(&tab[cc * kV3Bins + b], 1u);
     } else {
       const int slot = atomicAdd(rare_n, 1);
-      if (slot < kV3RareCap) rare_id[slot] = 8 * i + k;
+      if (slot < kV3RareCap) rare[slot] = make_int2(8 * i + k, (int)(raw | ((uint32_t)cc << 16)));
     }
   }
 }
@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
   c.hist = reinterpret_cast<LocalHist*>(smem_raw + lay.hist);
   c.gbuf = reinterpret_cast<V3Entry*>(smem_raw + lay.gbuf);
   c.list = reinterpret_cast<V3Entry*>(smem_raw + lay.list);
-  int* rare_id = reinterpret_cast<int*>(smem_raw + lay.rare);
+  int2* rare = reinterpret_cast<int2*>(smem_raw + lay.rare);  // (id, raw bits | count class << 16)
   int* small = reinterpret_cast<int*>(smem_raw + lay.small);
   c.gbuf_n = small;
   int* rare_n = small + 1;
@@ -115,6 +115,16 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
     return;
   }
 
+  // The side list needs (id, count, value) of the tokens held three times or more: three
+  // dependent reads.  Thread t starts the chain for list entry t here and takes one step of
+  // it at each stop below, so that it has run its course by the time the row is counted.
+  int n_heavy = 0, hv_q = -1;
+  int2 hv_pair = make_int2(-1, 0);
+  uint32_t hv_raw = 0;
+  if (penalised) {
+    n_heavy = a.pool.n_heavy[P.slot];
+    if (tid < a.pool.unique_cap) hv_q = load_now_s32(a.pool.heavy + (size_t)P.slot * a.pool.unique_cap + tid);
+  }
   // ask L2 for the whole row (and its class map) now: the counting loop then waits for L2,
   // not for HBM, and the later walks over the row find it there
   if (c.vec) {
@@ -135,6 +145,9 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
 
   for (int i = tid; i < kCells; i += kThreads) c.tab[i] = 0;
   __syncthreads();
+  n_heavy = min(n_heavy, min(a.pool.unique_cap, args.s_cap));
+  if (tid < n_heavy && hv_q >= 0 && hv_q < a.pool.unique_cap)
+    hv_pair = load_now_int2(a.pool.pairs + (size_t)P.slot * a.pool.unique_cap + hv_q);  // (id, count)
 
   // ---- A. the one read of the row from HBM: count tokens per (count class, value) --------
   {
@@ -145,7 +158,7 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
           atomicAdd(&c.tab[cc * kV3Bins + b], 1u);
         } else {
           const int slot = atomicAdd(rare_n, 1);
-          if (slot < kV3RareCap) rare_id[slot] = id;
+          if (slot < kV3RareCap) rare[slot] = make_int2(id, (int)(raw | ((uint32_t)cc << 16)));
         }
       };
       const int n8 = c.vec ? c.vocab / 8 : 0;
@@ -160,15 +173,32 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
       // 32-bit shared-memory addresses: one LOP3, one multiply-add, one shift-add and the
       // reduction per token
       const uint32_t tab_mid = (uint32_t)__cvta_generic_to_shared(c.tab + kV3Half);
-      // J-th token of the chunk: its 2-bit class sits at bit 2J of cl
-      auto bump = [&](uint32_t u16, uint32_t sign_mask, uint32_t cl, auto J) {
-        constexpr int kShift = 2 * decltype(J)::value;
+      // J-th token of the chunk (J even: low half of its word, odd: high half); its 2-bit
+      // class sits at bit 2J of cl.  Written as PTX so that each step is one instruction:
+      // sign mask (byte permute with sign replication), (lo & 0x7fff) ^ mask (one LOP3),
+      // class offset and table address (two multiply-adds on the FMA pipe), the reduction.
+      auto bump = [&](uint32_t lo_word, uint32_t word, uint32_t cl, auto J) {
+        constexpr int kJ = decltype(J)::value;
+        constexpr int kShift = 2 * kJ;
         constexpr uint32_t kClassBytes = (uint32_t)(kV3Bins * 4);  // 3 << 13
+        uint32_t sign_mask, idx, rel, base, addr;
+        if (kJ & 1) {
+          asm("prmt.b32 %0, %1, 0, 0xBBBB;" : "=r"(sign_mask) : "r"(word));   // sign of byte 3
+          asm("prmt.b32 %0, %1, 0, 0x4432;" : "=r"(idx) : "r"(lo_word));      // high half
+        } else {
+          asm("prmt.b32 %0, %1, 0, 0x9999;" : "=r"(sign_mask) : "r"(word));   // sign of byte 1
+          idx = lo_word;
+        }
         // bin = kV3Half + idx for x >= 0, kV3Half - 1 - idx = kV3Half + ~idx for x < 0
-        const uint32_t rel = (u16 & 0x7fffu) ^ sign_mask;
-        const uint32_t base = kShift < 14 ? (cl & (3u << kShift)) * (kClassBytes >> kShift) + tab_mid
-                                          : (cl >> 14) * kClassBytes + tab_mid;
-        const uint32_t addr = base + (rel << 2);
+        asm("lop3.b32 %0, %1, 0x7fff, %2, 0x6a;" : "=r"(rel) : "r"(idx), "r"(sign_mask));  // (a & b) ^ c
+        if (kShift < 14) {
+          const uint32_t field = cl & (3u << kShift);
+          asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(base) : "r"(field), "n"(kClassBytes >> kShift), "r"(tab_mid));
+        } else {
+          const uint32_t field = cl >> 14;
+          asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(base) : "r"(field), "n"(kClassBytes), "r"(tab_mid));
+        }
+        asm("mad.lo.u32 %0, %1, 4, %2;" : "=r"(addr) : "r"(rel), "r"(base));
         asm volatile("red.shared.add.u32 [%0], 1;" ::"r"(addr) : "memory");
       };
       auto take_chunk = [&](const uint4& w4, uint32_t cl4, int i) {
@@ -181,13 +211,13 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
           bad |= (~lo[k] | (mag + kHiAdd)) & 0x80008000u;
         }
         if (bad == 0) {
-#define HS_BUMP_WORD(K)                                                                                    \
-  bump(lo[K], (uint32_t)((int)(words[K] << 16) >> 31), cl4, std::integral_constant<int, 2 * K>{});         \
-  bump(lo[K] >> 16, (uint32_t)((int)words[K] >> 31), cl4, std::integral_constant<int, 2 * K + 1>{});
+#define HS_BUMP_WORD(K)                                                           \
+  bump(lo[K], words[K], cl4, std::integral_constant<int, 2 * K>{});               \
+  bump(lo[K], words[K], cl4, std::integral_constant<int, 2 * K + 1>{});
           HS_BUMP_WORD(0) HS_BUMP_WORD(1) HS_BUMP_WORD(2) HS_BUMP_WORD(3)
 #undef HS_BUMP_WORD
         } else {
-          count_chunk_slow(c.tab, rare_n, rare_id, w4, cl4, i);
+          count_chunk_slow(c.tab, rare_n, rare, w4, cl4, i);
         }
       };
       // two batches of loads: the next one is on its way while this one is counted
@@ -205,6 +235,7 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
         }
       };
       fetch(w, cl, tid);
+      if (hv_pair.x >= 0 && hv_pair.x < c.vocab) hv_raw = load_now_u16(c.logits + hv_pair.x);
       for (int i0 = tid; i0 < n8; i0 += kInFlight * kThreads) {
         fetch(wn, cn, i0 + kInFlight * kThreads);
   #pragma unroll
@@ -221,33 +252,43 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
   mark(1);
 
   // ---- B. the side list: tokens with history count >= 3, and values outside the bin window
+  // It is walked by every selection, so it lives in shared memory when it fits: first in the
+  // (still unused) histogram area, after the class list is built in the count table's.
   u64 side_best = 0;
+  const int n_rare = *rare_n;
+  const bool side_shared = n_rare <= kV3RareCap && n_heavy + kV3RareCap <= kV3SideShared;
+  if (side_shared) {
+    c.s_pair = reinterpret_cast<int2*>(c.hist);
+    c.s_cap = kV3SideShared;
+  }
   {
     auto put = [&](int slot, int id, float s) {
-      if (slot >= args.s_cap) { status |= 4; return; }
+      if (slot >= c.s_cap) { status |= 4; return; }
       c.s_pair[slot] = make_int2(id, __float_as_int(s));
       const u64 packed = ((u64)key_of(s) << 32) | (uint32_t)(~(uint32_t)id);
       side_best = packed > side_best ? packed : side_best;
     };
-    int n_heavy = 0;
     if (penalised) {
-      n_heavy = min(a.pool.n_heavy[P.slot], min(a.pool.unique_cap, args.s_cap));
+      if (tid < n_heavy) {  // the entry whose reads were started early
+        if (hv_pair.x < 0 || hv_pair.x >= c.vocab) c.s_pair[tid] = make_int2(-1, 0);
+        else put(tid, hv_pair.x, c.score_of(hv_raw, hv_pair.y));
+      }
       const int32_t* heavy = a.pool.heavy + (size_t)P.slot * a.pool.unique_cap;
       const int2* pairs = a.pool.pairs + (size_t)P.slot * a.pool.unique_cap;
-      for (int j = tid; j < n_heavy; j += kThreads) {
+      for (int j = tid + kThreads; j < n_heavy; j += kThreads) {
         const int q = heavy[j];
         const int2 pr = q >= 0 && q < a.pool.unique_cap ? pairs[q] : make_int2(-1, 0);  // (id, count)
         if (pr.x < 0 || pr.x >= c.vocab) { c.s_pair[j] = make_int2(-1, 0); continue; }
         put(j, pr.x, c.score_of(c.logits[pr.x], pr.y));
       }
     }
-    const int n_rare = *rare_n;
+    if (clocks && tid == 0) clocks[10] = clock64();
     if (n_rare <= kV3RareCap) {
       for (int t = tid; t < n_rare; t += kThreads) {
-        const int id = rare_id[t];
-        put(n_heavy + t, id, c.score_of(c.logits[id], c.class_of(id)));
+        const int2 e = rare[t];
+        put(n_heavy + t, e.x, c.score_of((uint32_t)e.y & 0xffffu, (e.y >> 16) & 3));
       }
-      c.n_s = min(n_heavy + n_rare, args.s_cap);
+      c.n_s = min(n_heavy + n_rare, c.s_cap);
     } else {
       // too many to remember: sweep the row again for out-of-window values
       for (int id = tid; id < c.vocab; id += kThreads) {
@@ -257,9 +298,10 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
         put(n_heavy + atomicAdd(side_n, 1), id, c.score_of(raw, cc));
       }
       __syncthreads();
-      c.n_s = min(n_heavy + *side_n, args.s_cap);
+      c.n_s = min(n_heavy + *side_n, c.s_cap);
     }
   }
+  if (clocks && tid == 0) clocks[11] = clock64();
   side_best = block_max_u64(*c.x, side_best);  // (its barriers also publish the side list)
   mark(2);
 
@@ -310,8 +352,14 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
     c.n_cl = (int)tot;
     __syncthreads();
   }
+  if (side_shared) {
+    // the count table has served: the side list moves there and frees the histogram area
+    int2* moved = reinterpret_cast<int2*>(c.tab);
+    for (int j = tid; j < c.n_s; j += kThreads) moved[j] = c.s_pair[j];
+    c.s_pair = moved;
+    __syncthreads();
+  }
   mark(3);
-  if (clocks && tid == 0) { clocks[10] = (unsigned long long)c.n_cl; clocks[11] = (unsigned long long)c.n_s; }
 
   KeptSet kept{0u, 0x7fffffff};
   int token = -1;

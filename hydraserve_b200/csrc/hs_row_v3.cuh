@@ -38,6 +38,7 @@ constexpr int kCells = 3 * kV3Bins;           // count classes 0, 1, 2
 constexpr uint32_t kV3Base = 113u << 7;       // smallest binned magnitude: 2^-14
 constexpr int kV3ListCap = 128;               // members resolved by sorting
 constexpr int kV3RareCap = 512;               // out-of-window tokens remembered before a sweep
+constexpr int kV3SideShared = 4096;           // side-list entries kept in shared memory (else global scratch)
 constexpr int kV3PhaseSlots = 16;
 constexpr int kSplitCap = 4096;               // candidate entries one CTA of a split row can hand over
 
@@ -116,7 +117,7 @@ __host__ __device__ inline LayoutV3 layout_v3() {
   l.hist = take(sizeof(LocalHist));
   l.gbuf = take(sizeof(V3Entry) * kV3ListCap);
   l.list = take(sizeof(V3Entry) * kV3ListCap);
-  l.rare = take(sizeof(int) * kV3RareCap);
+  l.rare = take(sizeof(int2) * kV3RareCap);
   l.small = take(sizeof(int) * 16);
   l.scl = take(sizeof(ClassPacked) * kV3SharedClasses);
   l.total = off;
