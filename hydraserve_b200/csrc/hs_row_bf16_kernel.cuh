@@ -533,7 +533,9 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
           if (members > (u64)kV3ListCap) {
             const u64 per_round = ((u64)c.vocab + members - 1) / members;  // probes for ~63 % success
             const int trials = (int)min((u64)kRandomTrials, max(1ull, (per_round + kThreads - 1) / kThreads));
-            token = random_in_class(c, cell, trials, P.seed, 32);
+            // a class the scan can hold gets a few rounds, then the scan; a larger one many
+            token = random_in_class(c, cell, trials, P.seed, members <= (u64)kV3ScanCap ? 4 : 32);
+            if (token < 0 && members <= (u64)kV3ScanCap) token = nth_in_small_class(c, cell, nth);
           } else {
             token = nth_in_small_class(c, cell, nth);
           }

@@ -37,6 +37,7 @@ constexpr int kV3Bins = 2 * kV3Half;          // per count class
 constexpr int kCells = 3 * kV3Bins;           // count classes 0, 1, 2
 constexpr uint32_t kV3Base = 113u << 7;       // smallest binned magnitude: 2^-14
 constexpr int kV3ListCap = 128;               // members resolved by sorting
+constexpr int kV3ScanCap = 1024;              // ids one class scan can hold (in the gather and list buffers)
 constexpr int kV3RareCap = 512;               // out-of-window tokens remembered before a sweep
 constexpr int kV3SideShared = 4096;           // side-list entries kept in shared memory (else global scratch)
 constexpr int kV3PhaseSlots = 16;
@@ -628,11 +629,12 @@ __device__ int nth_in_group(Ctx3& c, const Group& g, u64 n) {
 }
 
 // Token id of the n-th (1-based, ascending id) token of ONE class (count class and
-// one-value bin `cell`), for classes of at most kV3ListCap tokens, or -1 when the row has
+// one-value bin `cell`), for classes of at most kV3ScanCap tokens, or -1 when the row has
 // no 16-byte aligned view or the class turns out larger.  One pass over the row: a class
 // is one bf16 bit pattern, so eight tokens are screened with four XORs and a zero-half
-// test, and only words with a matching half look at the class map.  The few ids found are
-// ranked among themselves.
+// test, and only words with a matching half look at the class map.  The ids found (kept in
+// the gather and list buffers, which are contiguous) are ranked among themselves.
+static_assert(kV3ScanCap * sizeof(int) <= 2 * kV3ListCap * sizeof(V3Entry), "scan ids fit the two buffers");
 __device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
   if (!c.vec) return -1;
   const int tid = threadIdx.x;
@@ -656,7 +658,7 @@ __device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
   auto probe = [&](int id, uint32_t r) {
     if (r == raw && c.class_of(id) == cc) {
       const int slot = atomicAdd(c.gbuf_n, 1);
-      if (slot < kV3ListCap) ids[slot] = id;
+      if (slot < kV3ScanCap) ids[slot] = id;
     }
   };
   constexpr int kInFlight = 8;  // 64 KB per SM on the way: the row may have left L2
@@ -684,16 +686,18 @@ __device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
   if (tid == 0) c.x->bcast[6] = 0;
   __syncthreads();
   const int found = *c.gbuf_n;
-  if (found <= kV3ListCap && tid < found) {
-    const int mine = ids[tid];
-    u64 rank = 1;
-    for (int j = 0; j < found; ++j) rank += ids[j] < mine ? 1 : 0;
-    if (rank == n) c.x->bcast[6] = (u64)mine + 1;
+  if (found <= kV3ScanCap) {
+    for (int t = tid; t < found; t += kThreads) {
+      const int mine = ids[t];
+      u64 rank = 1;
+      for (int j = 0; j < found; ++j) rank += ids[j] < mine ? 1 : 0;
+      if (rank == n) c.x->bcast[6] = (u64)mine + 1;
+    }
   }
   __syncthreads();
   const u64 hit = c.x->bcast[6];
   __syncthreads();
-  if (found > kV3ListCap) return -1;
+  if (found > kV3ScanCap) return -1;
   return hit ? (int)(hit - 1) : 0x7fffffff;
 }
 
