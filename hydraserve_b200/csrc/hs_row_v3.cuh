@@ -30,6 +30,9 @@
 #include "hs_row_kernel.cuh"
 #include "../../include/hs_sampler.h"
 
+#ifndef HS_SCAN_BATCH
+#define HS_SCAN_BATCH 8
+#endif
 namespace hs {
 
 constexpr int kV3Half = 3072;                 // 24 binades x 128 mantissas
@@ -655,19 +658,26 @@ __device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
   const int n8 = c.vocab / 8;
   const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
   auto zero_half = [](uint32_t x) { return (x - 0x00010001u) & ~x & 0x80008000u; };
-  auto probe = [&](int id, uint32_t r) {
-    if (r == raw && c.class_of(id) == cc) {
+  auto probe = [&](int id, uint32_t r, uint32_t klass) {
+    if (r == raw && (int)klass == cc) {
       const int slot = atomicAdd(c.gbuf_n, 1);
       if (slot < kV3ScanCap) ids[slot] = id;
     }
   };
-  constexpr int kInFlight = 8;  // 64 KB per SM on the way: the row may have left L2
+  // The class map is read along with the logits: the value alone is held by tokens of every
+  // count class, and looking a class up only on a hit costs a dependent scattered read per
+  // hit, serialised inside each warp.
+  const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
+  constexpr int kInFlight = HS_SCAN_BATCH;  // 16-byte loads in flight per thread
   for (int i0 = tid; i0 < n8; i0 += kInFlight * kThreads) {
     uint4 w[kInFlight];
+    uint32_t cl[kInFlight];
 #pragma unroll
     for (int u = 0; u < kInFlight; ++u) {
       const int i = i0 + u * kThreads;
-      w[u] = i < n8 ? src4[i] : make_uint4(~vv, ~vv, ~vv, ~vv);
+      // past L1: with this kernel's shared memory there is too little of it for the loads in flight
+      w[u] = i < n8 ? __ldcg(src4 + i) : make_uint4(~vv, ~vv, ~vv, ~vv);
+      cl[u] = (cls16p && i < n8) ? (uint32_t)__ldcg(cls16p + i) : 0u;
     }
 #pragma unroll
     for (int u = 0; u < kInFlight; ++u) {
@@ -675,14 +685,14 @@ __device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
                          zero_half(w[u].w ^ vv);
       if (z) {
         const int id = 8 * (i0 + u * kThreads);
-        probe(id, w[u].x & 0xffffu); probe(id + 1, w[u].x >> 16);
-        probe(id + 2, w[u].y & 0xffffu); probe(id + 3, w[u].y >> 16);
-        probe(id + 4, w[u].z & 0xffffu); probe(id + 5, w[u].z >> 16);
-        probe(id + 6, w[u].w & 0xffffu); probe(id + 7, w[u].w >> 16);
+        probe(id, w[u].x & 0xffffu, cl[u] & 3u); probe(id + 1, w[u].x >> 16, (cl[u] >> 2) & 3u);
+        probe(id + 2, w[u].y & 0xffffu, (cl[u] >> 4) & 3u); probe(id + 3, w[u].y >> 16, (cl[u] >> 6) & 3u);
+        probe(id + 4, w[u].z & 0xffffu, (cl[u] >> 8) & 3u); probe(id + 5, w[u].z >> 16, (cl[u] >> 10) & 3u);
+        probe(id + 6, w[u].w & 0xffffu, (cl[u] >> 12) & 3u); probe(id + 7, w[u].w >> 16, (cl[u] >> 14) & 3u);
       }
     }
   }
-  for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) probe(id, c.logits[id]);
+  for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) probe(id, c.logits[id], (uint32_t)c.class_of(id));
   if (tid == 0) c.x->bcast[6] = 0;
   __syncthreads();
   const int found = *c.gbuf_n;
