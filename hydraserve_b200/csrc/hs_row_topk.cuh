@@ -320,9 +320,19 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
   const int first8 = c.lo / 8;  // lo is a multiple of 8
   const int n8 = c.vec ? c.hi / 8 : first8;
   const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
-  constexpr int kInFlight = 8;
+  constexpr int kBatch = 4;  // two batches of loads: the next is on its way while this one is compared
   int n_scored = n;
-  for (int base = first8; base < n8; base += kInFlight * kThreads) {
+  uint4 w[kBatch], wn[kBatch];
+  auto fetch = [&](uint4 (&dst)[kBatch], int base) {
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int i = base + tid + u * kThreads;
+      if (i < n8) dst[u] = __ldcs(src4 + i);
+    }
+  };
+  fetch(w, first8);
+  int iteration = 0;
+  for (int base = first8; base < n8; base += kBatch * kThreads, ++iteration) {
     // threshold as a bf16 value (NaN = nothing passes, -inf = everything passes)
     int t_min = L.thr[0];
     if (c.cls) t_min = min(t_min, min(L.thr[1], L.thr[2]));
@@ -330,14 +340,9 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
     if (t_min <= -32641) tb = 0xff80u;
     const uint32_t pair = tb * 0x10001u;
     const __nv_bfloat162 thr2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
-    uint4 w[kInFlight];
+    fetch(wn, base + kBatch * kThreads);
 #pragma unroll
-    for (int u = 0; u < kInFlight; ++u) {
-      const int i = base + tid + u * kThreads;
-      if (i < n8) w[u] = __ldcs(src4 + i);
-    }
-#pragma unroll
-    for (int u = 0; u < kInFlight; ++u) {
+    for (int u = 0; u < kBatch; ++u) {
       const int i = base + tid + u * kThreads;
       if (i >= n8) break;
       const uint32_t m0 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].x), thr2);
@@ -356,6 +361,9 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
         push(8 * i + q, raw, 4);
       }
     }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) w[u] = wn[u];
+    if ((iteration & 1) == 0) continue;  // look at the list every other batch
     // raise the bound when the list is getting long (block-uniform decision)
     if (__syncthreads_or(*L.n >= kCandSoft)) {
       if (*L.lost) return -1;
