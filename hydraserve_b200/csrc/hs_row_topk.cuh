@@ -178,31 +178,40 @@ __device__ void cand_thresholds(const Ctx3& c, CandCtx& L, uint32_t bound) {
 // k much smaller than the number of groups it is about as tight as the k-th highest token.
 // Each thread keeps its (at most four) group maxima in registers; the k-th highest of them
 // is found with two count-only radix levels of eight bits.
-__device__ int sample_kth_t16(const Ctx3& c, CandCtx& L, int begin, int end, int k) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  constexpr int kGroups = 4;  // per thread: kSample = kGroups * 8 * kThreads
-  static_assert(kSample == kGroups * 8 * kThreads, "one 128-bit load per group");
+constexpr int kSampleGroups = 4;  // per thread: kSample = kSampleGroups * 8 * kThreads
+static_assert(kSample == kSampleGroups * 8 * kThreads, "one 128-bit load per group");
+struct SampleRegs {
+  uint4 w[kSampleGroups];
+  uint32_t cl[kSampleGroups];
+};
+// Starts the loads of the sample (nothing waits for them here).
+__device__ __forceinline__ void sample_fetch(const Ctx3& c, int begin, int end, SampleRegs& r) {
+  const int tid = threadIdx.x;
   const bool vec = c.vec && (begin & 7) == 0;
   const int n8 = vec ? (end - begin) / 8 : 0;  // whole 8-token chunks read as 128-bit words
   const uint4* src4 = reinterpret_cast<const uint4*>(c.logits) + (begin >> 3);
   const unsigned short* cls16p = c.cls ? reinterpret_cast<const unsigned short*>(c.cls) + (begin >> 3) : nullptr;
+#pragma unroll
+  for (int u = 0; u < kSampleGroups; ++u) {
+    const int i = tid + u * kThreads;
+    if (i < n8) { r.w[u] = src4[i]; r.cl[u] = cls16p ? cls16p[i] : 0u; }
+  }
+}
+__device__ int sample_kth_t16(const Ctx3& c, CandCtx& L, int begin, int end, int k, const SampleRegs& r) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kGroups = kSampleGroups;
+  const bool vec = c.vec && (begin & 7) == 0;
+  const int n8 = vec ? (end - begin) / 8 : 0;
   int top[kGroups];  // value + 32768 of the group maximum, 0 = no token
   {
-    uint4 w[kGroups];
-    uint32_t cl[kGroups];
-#pragma unroll
-    for (int u = 0; u < kGroups; ++u) {
-      const int i = tid + u * kThreads;
-      if (i < n8) { w[u] = src4[i]; cl[u] = cls16p ? cls16p[i] : 0u; }
-    }
 #pragma unroll
     for (int u = 0; u < kGroups; ++u) {
       top[u] = 0;
       if (tid + u * kThreads >= n8) continue;
-      const uint32_t words[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+      const uint32_t words[4] = {r.w[u].x, r.w[u].y, r.w[u].z, r.w[u].w};
 #pragma unroll
       for (int q = 0; q < 8; ++q)
-        if (((cl[u] >> (2 * q)) & 3u) == 0)
+        if (((r.cl[u] >> (2 * q)) & 3u) == 0)
           top[u] = max(top[u], t16_of_raw((words[q >> 1] >> (16 * (q & 1))) & 0xffffu) + 32768);
     }
   }
@@ -291,25 +300,45 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
   };
   // 1. Tokens the history holds three times or more are candidates by definition (their score
   // does not follow from a class threshold); they come from the request's list, not the stream.
+  // The chain heavy -> pairs -> logits is three dependent reads; it is started for list entry
+  // `tid` before the sample is fetched and worked off between the sample's steps, so that
+  // the waits overlap.
+  const int sample_end = min(c.hi, c.lo + kSample);
+  int n_heavy = 0, hv_q = -1;
   if (c.cls) {
-    const int n_heavy = min(c.pool.n_heavy[c.slot], c.pool.unique_cap);
+    n_heavy = load_now_s32(c.pool.n_heavy + c.slot);
+    if (tid < c.pool.unique_cap) hv_q = load_now_s32(c.pool.heavy + (size_t)c.slot * c.pool.unique_cap + tid);
+  }
+  SampleRegs sample;
+  sample_fetch(c, c.lo, sample_end, sample);
+  n_heavy = min(n_heavy, c.pool.unique_cap);
+  const int2* pairs = c.pool.pairs + (size_t)c.slot * c.pool.unique_cap;
+  int2 hv_pair = make_int2(-1, 0);
+  if (tid < n_heavy && hv_q >= 0 && hv_q < c.pool.unique_cap) hv_pair = load_now_int2(pairs + hv_q);  // (id, count)
+  const bool hv_mine = hv_pair.x >= c.lo && hv_pair.x < c.hi;
+  uint32_t hv_raw = 0;
+  if (hv_mine) hv_raw = load_now_u16(c.logits + hv_pair.x);
+  // the first bound: from the group maxima of the sampled tokens outside the history
+  const int t_k = sample_kth_t16(c, L, c.lo, sample_end, k, sample);
+  if (c.cls) {
+    auto add_scored = [&](int id, uint32_t raw, int count) {  // the exact count is at hand
+      const int slot = atomicAdd(L.n, 1);
+      if (slot < kCandCap) L.cand[slot] = cand_pack(key_of(c.score_of(raw, count)), id);
+      else *L.lost = 1;
+    };
+    if (hv_mine) add_scored(hv_pair.x, hv_raw, hv_pair.y);
     const int32_t* heavy = c.pool.heavy + (size_t)c.slot * c.pool.unique_cap;
-    const int2* pairs = c.pool.pairs + (size_t)c.slot * c.pool.unique_cap;
-    for (int j = tid; j < n_heavy; j += kThreads) {
+    for (int j = tid + kThreads; j < n_heavy; j += kThreads) {
       const int q = heavy[j];
       if (q < 0 || q >= c.pool.unique_cap) continue;
       const int2 pr = pairs[q];  // (id, count)
       if (pr.x < c.lo || pr.x >= c.hi) continue;
-      const int slot = atomicAdd(L.n, 1);  // stored scored: the exact count is at hand
-      if (slot < kCandCap) L.cand[slot] = cand_pack(key_of(c.score_of(c.logits[pr.x], pr.y)), pr.x);
-      else *L.lost = 1;
+      add_scored(pr.x, c.logits[pr.x], pr.y);
     }
   }
   __syncthreads();
   if (*L.lost) return -1;
   int n = min(*L.n, kCandCap);
-  // the first bound: k-th highest raw value among the sampled tokens outside the history
-  const int t_k = sample_kth_t16(c, L, c.lo, min(c.hi, c.lo + kSample), k);
   uint32_t bound = t_k > -32768 ? key_of(c.score_of(raw_of_t16(t_k), 0)) : 0u;
   if (L.dbg && tid == 0) L.dbg[3] = clock64();
   cand_thresholds(c, L, bound);
