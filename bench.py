@@ -43,7 +43,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the two kernels of one step, from the ncu
 # capture summarised in profiles/ (same workload, one step)
 NCU_DRAM_BYTES_PER_STEP = 149.8e6
-ROTATING_SETS = 3
+ROTATING_SETS = 8
 
 
 def workload_config(batch, vocab, history_len, n_gpus, extra=None):

@@ -741,22 +741,25 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args a
     if (small[6] != split - 1) return;
     mark(12);
     __threadfence();
-    if (tid == 0) { args.split_ticket[c.row] = 0; *L.n = 0; small[7] = 0; }
+    if (tid == 0) args.split_ticket[c.row] = 0;
+    // all parts' lengths first, then all copies at once (one wait instead of one per part)
+    if (tid < split) small[12 + tid] = ((volatile int*)args.split_n)[c.row * split + tid];  // -1: that part overflowed
     __syncthreads();
-    for (int g = 0; g < split; ++g) {
-      const int ng = ((volatile int*)args.split_n)[c.row * split + g];
-      if (ng < 0) { if (tid == 0) small[7] = 1; continue; }
-      const u64* theirs = args.split_lists + ((size_t)c.row * split + g) * kSplitCap;
-      if (tid == 0) small[9] = atomicAdd(L.n, ng);
-      __syncthreads();
-      const int at = small[9];
-      for (int i = tid; i < ng; i += kThreads)
-        if (at + i < kCandCap) L.cand[at + i] = ((volatile const u64*)theirs)[i];
-      __syncthreads();
+    {
+      int at = 0;
+      bool overflow = false;
+      for (int g = 0; g < split; ++g) {
+        const int ng = small[12 + g];
+        if (ng < 0) { overflow = true; continue; }
+        const u64* theirs = args.split_lists + ((size_t)c.row * split + g) * kSplitCap;
+        for (int i = tid; i < ng; i += kThreads)
+          if (at + i < kCandCap) L.cand[at + i] = ((volatile const u64*)theirs)[i];
+        at += ng;
+      }
+      n = (overflow || at > kCandCap) ? -1 : at;
     }
-    n = *L.n;
+    __syncthreads();
     mark(13);
-    if (small[7] || n > kCandCap) n = -1;
     if (n > kSortAll) {
       const uint32_t cut = cand_kth_key(*c.x, L, n, P.top_k);
       n = cand_compact(L, n, cut);

@@ -58,11 +58,13 @@ struct CandCtx {
   unsigned long long* dbg;  // optional phase clocks of this row (tuning aid), or null
 };
 
-// The k-th highest key among the n list entries (n >= k >= 1): count-only radix levels of
-// 11 + 11 + 10 bits.  Candidates lie close together, so a level whose bits are the same in
-// the lowest and the highest key is skipped.
+// The k-th highest key among the n list entries (n >= k >= 1).  The keys of a candidate list
+// lie close together, so the 2,048 counters are laid over [lowest key, highest key] instead of
+// over fixed bit fields: one counting pass usually leaves a bucket with a handful of keys,
+// which are then ranked among themselves; a fuller bucket is counted again over its own range.
 __device__ uint32_t cand_kth_key(Exchange& x, CandCtx& L, int n, int k) {
   const int tid = threadIdx.x;
+  constexpr int kResolve = 64;  // in-bucket keys ranked directly
   uint32_t lo_key = 0xffffffffu, hi_key = 0u;
   for (int i = tid; i < n; i += kThreads) {
     const uint32_t key = cand_key(L.cand[i]);
@@ -71,21 +73,17 @@ __device__ uint32_t cand_kth_key(Exchange& x, CandCtx& L, int n, int k) {
   }
   hi_key = block_max_u32(x, hi_key);
   lo_key = ~block_max_u32(x, ~lo_key);
-  uint32_t prefix = 0;
   int want = k;
-  for (int level = 0; level < 3; ++level) {
-    const int shift = level_shift(level), bits = level_bits(level);
-    const uint32_t mask = (1u << bits) - 1u;
-    if ((lo_key >> shift) == (hi_key >> shift)) {  // one bucket holds everything that is left
-      prefix = hi_key >> shift;
-      continue;
-    }
+  for (int pass = 0; pass < 4; ++pass) {
+    if (lo_key == hi_key) return lo_key;
+    const uint32_t span = hi_key - lo_key;
+    const int shift = max(0, 32 - __clz(span) - 11);  // (span >> shift) < 2048
     for (int b = tid; b < kBins; b += kThreads) L.count[b] = 0;
+    if (tid == 0) L.thr[3] = 0;
     __syncthreads();
     for (int i = tid; i < n; i += kThreads) {
       const uint32_t key = cand_key(L.cand[i]);
-      if (level > 0 && (key >> (shift + bits)) != prefix) continue;
-      atomicAdd(&L.count[(key >> shift) & mask], 1u);
+      if (key >= lo_key && key <= hi_key) atomicAdd(&L.count[(key - lo_key) >> shift], 1u);
     }
     __syncthreads();
     constexpr int kPer = kBins / kThreads;
@@ -104,20 +102,48 @@ __device__ uint32_t cand_kth_key(Exchange& x, CandCtx& L, int n, int k) {
         if ((u64)want <= ex + bc) {
           x.bcast[0] = (u64)(hi - u);
           x.bcast[1] = ex;
+          x.bcast[2] = bc;
           break;
         }
         ex += bc;
       }
     }
     __syncthreads();
-    prefix = (prefix << bits) | (uint32_t)x.bcast[0];
+    const uint32_t bucket = (uint32_t)x.bcast[0];
+    const int in_bucket = (int)x.bcast[2];
     want -= (int)x.bcast[1];
+    // the bucket's key range (clamped to the range that was counted)
+    const uint32_t b_lo = lo_key + (bucket << shift);
+    const uint32_t b_hi = shift == 0 ? b_lo : min(hi_key, b_lo + ((1u << shift) - 1u));
     __syncthreads();
-    // keys outside the chosen bucket no longer matter for the remaining levels
-    lo_key = max(lo_key, prefix << shift);
-    hi_key = min(hi_key, (prefix << shift) | ((1u << shift) - 1u));
+    lo_key = b_lo;
+    hi_key = b_hi;
+    if (shift == 0) return b_lo;  // a bucket was one key
+    if (in_bucket <= kResolve) {
+      // rank the bucket's keys among themselves (the counters have served: they hold the keys now)
+      for (int i = tid; i < n; i += kThreads) {
+        const uint32_t key = cand_key(L.cand[i]);
+        if (key >= lo_key && key <= hi_key) L.count[atomicAdd(&L.thr[3], 1)] = key;
+      }
+      __syncthreads();
+      if (tid < in_bucket) {
+        const uint32_t mine = L.count[tid];
+        int greater = 0, at_least = 0;
+        for (int j = 0; j < in_bucket; ++j) {
+          const uint32_t other = L.count[j];
+          greater += other > mine ? 1 : 0;
+          at_least += other >= mine ? 1 : 0;
+        }
+        if (greater < want && want <= at_least) x.bcast[0] = (u64)mine;  // equal keys write the same value
+      }
+      __syncthreads();
+      const uint32_t key = (uint32_t)x.bcast[0];
+      __syncthreads();
+      return key;
+    }
   }
-  return prefix;
+  // not reached: every pass narrows the range by a factor of 2,048
+  return lo_key;
 }
 
 // Drops list entries with key < bound (in place).  Returns the new length.
