@@ -31,7 +31,7 @@
 #include "../../include/hs_sampler.h"
 
 #ifndef HS_SCAN_BATCH
-#define HS_SCAN_BATCH 8
+#define HS_SCAN_BATCH 4
 #endif
 namespace hs {
 
@@ -668,19 +668,24 @@ __device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
   // count class, and looking a class up only on a hit costs a dependent scattered read per
   // hit, serialised inside each warp.
   const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
-  constexpr int kInFlight = HS_SCAN_BATCH;  // 16-byte loads in flight per thread
-  for (int i0 = tid; i0 < n8; i0 += kInFlight * kThreads) {
-    uint4 w[kInFlight];
-    uint32_t cl[kInFlight];
+  // two batches of loads: the next is on its way while this one is screened
+  constexpr int kBatch = HS_SCAN_BATCH;
+  uint4 w[kBatch], wn[kBatch];
+  uint32_t cl[kBatch], cn[kBatch];
+  auto fetch = [&](uint4 (&dw)[kBatch], uint32_t (&dc)[kBatch], int i0) {
 #pragma unroll
-    for (int u = 0; u < kInFlight; ++u) {
+    for (int u = 0; u < kBatch; ++u) {
       const int i = i0 + u * kThreads;
       // past L1: with this kernel's shared memory there is too little of it for the loads in flight
-      w[u] = i < n8 ? __ldcg(src4 + i) : make_uint4(~vv, ~vv, ~vv, ~vv);
-      cl[u] = (cls16p && i < n8) ? (uint32_t)__ldcg(cls16p + i) : 0u;
+      dw[u] = i < n8 ? __ldcg(src4 + i) : make_uint4(~vv, ~vv, ~vv, ~vv);
+      dc[u] = (cls16p && i < n8) ? (uint32_t)__ldcg(cls16p + i) : 0u;
     }
+  };
+  fetch(w, cl, tid);
+  for (int i0 = tid; i0 < n8; i0 += kBatch * kThreads) {
+    fetch(wn, cn, i0 + kBatch * kThreads);
 #pragma unroll
-    for (int u = 0; u < kInFlight; ++u) {
+    for (int u = 0; u < kBatch; ++u) {
       const uint32_t z = zero_half(w[u].x ^ vv) | zero_half(w[u].y ^ vv) | zero_half(w[u].z ^ vv) |
                          zero_half(w[u].w ^ vv);
       if (z) {
@@ -691,6 +696,8 @@ __device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
         probe(id + 6, w[u].w & 0xffffu, (cl[u] >> 12) & 3u); probe(id + 7, w[u].w >> 16, (cl[u] >> 14) & 3u);
       }
     }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) { w[u] = wn[u]; cl[u] = cn[u]; }
   }
   for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) probe(id, c.logits[id], (uint32_t)c.class_of(id));
   if (tid == 0) c.x->bcast[6] = 0;
