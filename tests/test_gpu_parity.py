@@ -255,3 +255,98 @@ def test_philox_draws_are_reproducible_and_follow_the_distribution(sampler):
         obs, exp = obs[:-1], exp[:-1]
     chi2, pvalue = stats.chisquare(obs, exp * obs.sum() / exp.sum())
     assert pvalue > 1e-4, f"chi-square p={pvalue:.3g} over {total} draws"
+
+
+def _bf16_round(x):
+    """fp32 values rounded to bf16 (round to nearest even), as fp32 and as raw bits."""
+    u = np.asarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    bits = u.astype(np.uint16)
+    return (bits.astype(np.uint32) << 16).view(np.float32), bits
+
+
+@pytest.mark.parametrize("kind", ["fine", "coarse", "two_values"])
+def test_bf16_philox_draws_follow_the_distribution(sampler, kind):
+    """The counting kernel's seeded draw (class by inverse CDF, then a uniformly chosen
+    member: by scanning the row for small classes, by rejection for large ones) against the
+    checker's distribution.  fine: every class has a few members (scan); coarse: classes of
+    tens to hundreds of members (scan, and rejection with the scan as fall-back);
+    two_values: classes of about a thousand members (rejection)."""
+    from scipy import stats
+
+    from hydraserve_b200.engine.sampling import SamplingParams
+
+    rng = np.random.default_rng({"fine": 21, "coarse": 22, "two_values": 23}[kind])
+    vocab, rows, reps = 2048, 64, 400
+    raw = rng.standard_normal(vocab).astype(np.float32)
+    if kind == "coarse":
+        raw = np.round(raw * 4.0) / 4.0 + 0.125
+    elif kind == "two_values":
+        raw = np.where(rng.random(vocab) < 0.5, 0.5, 1.0).astype(np.float32)
+    x, bits = _bf16_round(raw)
+    history = rng.integers(0, vocab, 600).astype(np.int32)  # count classes 0, 1, 2 and a few higher
+    base = SamplingParams(temperature=1.0, top_p=0.98, seed=0, repetition_penalty=1.1, presence_penalty=0.3,
+                          frequency_penalty=0.1)
+    o = O.sample_row(x, history, base, 0, draws=np.ones(vocab, np.float32))
+    probs = o.probabilities[o.kept]
+    logits = torch.from_numpy(np.tile(bits.view(np.int16), (rows, 1))).view(torch.bfloat16).cuda()
+    assert sampler.query(4, vocab) == 1, "bf16 rows must take the counting / candidate kernels"
+    counts = np.zeros(vocab, np.int64)
+    total = 0
+    for rep in range(reps):
+        params = [base.with_seed(rep * rows + i) for i in range(rows)]
+        records, _ = sampler.sample(logits, [history] * rows, params, [rep] * rows, None)
+        assert int((records["status"] != 0).sum()) == 0
+        if rep == 0:
+            again, _ = sampler.sample(logits, [history] * rows, params, [rep] * rows, None)
+            np.testing.assert_array_equal(records["token"], again["token"])
+        np.add.at(counts, records["token"], 1)
+        total += rows
+    assert counts.sum() == counts[o.kept].sum(), "a token outside the candidate set was drawn"
+    expected = probs * total
+    big = expected >= 5
+    obs = np.append(counts[o.kept][big], counts[o.kept][~big].sum())
+    exp = np.append(expected[big], expected[~big].sum())
+    if exp[-1] == 0:
+        obs, exp = obs[:-1], exp[:-1]
+    chi2, pvalue = stats.chisquare(obs, exp * obs.sum() / exp.sum())
+    assert pvalue > 1e-4, f"{kind}: chi-square p={pvalue:.3g} over {total} draws ({obs.size} cells)"
+
+
+def test_candidate_path_ties_and_long_lists(sampler):
+    """Rows of the candidate kernel (0 < top_k <= 256) whose lists take the less common
+    routes: hundreds of exact ties at the k-th value (all kept; the k-th key is found in a
+    bucket of equal keys), top_k = 256 (lists longer than the short-list sort), top_k = 1,
+    and the same with penalties; the rows are wide enough to be split over two CTAs."""
+    from hydraserve_b200.engine.sampling import SamplingParams
+    from hydraserve_b200.workloads import Workload
+
+    rng = np.random.default_rng(31)
+    vocab, batch = 70_000, 5
+    raw = (rng.standard_normal((batch, vocab)) * 3.0).astype(np.float32)
+    # row 0: 30 clear leaders, then 300 tokens tied exactly at the value where k = 50 falls
+    raw[0] = np.minimum(raw[0], 5.0)
+    lead = rng.choice(vocab, 330, replace=False)
+    raw[0, lead[:30]] = 9.0 + np.arange(30, dtype=np.float32) * 0.25
+    raw[0, lead[30:]] = 7.0
+    x = np.empty_like(raw)
+    bits = np.empty(raw.shape, np.uint16)
+    for r in range(batch):
+        x[r], bits[r] = _bf16_round(raw[r])
+    params = [
+        SamplingParams(temperature=0.8, top_k=50, top_p=0.95, seed=1, logprobs=20),
+        SamplingParams(temperature=1.1, top_k=256, top_p=0.9, min_p=0.01, seed=2, logprobs=5),
+        SamplingParams(temperature=0.7, top_k=1, seed=3, logprobs=3),
+        SamplingParams(temperature=1.0, top_k=256, seed=4, repetition_penalty=1.2, presence_penalty=0.5,
+                       frequency_penalty=0.3, logprobs=20),
+        SamplingParams(temperature=0.9, top_k=200, top_p=0.5, seed=5, frequency_penalty=0.4),
+    ]
+    hist = [rng.integers(0, vocab, 4000).astype(np.int32) for _ in range(batch)]
+    # make the leaders of rows 3 and 4 part of their histories, some of them many times
+    for r in (3, 4):
+        top_ids = np.argsort(-x[r])[:40].astype(np.int32)
+        hist[r] = np.concatenate([hist[r], np.repeat(top_ids, rng.integers(1, 6, top_ids.size))])
+    w = Workload("candidate_edges", bits, "bf16", hist, params, [0, 1, 2, 3, 4])
+    assert sampler.query(4, vocab) == 1
+    report = compare_case(sampler, w)
+    report.assert_ok(max_sensitive_fraction=0.4)
