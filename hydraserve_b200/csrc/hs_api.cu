@@ -149,7 +149,7 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
                 uint32_t flags, cudaStream_t stream) {
   Plan plan;
   if (dtype == HS_DTYPE_BF16 && !h->force_general) {
-    // one CTA per row, two CTAs per SM
+    // counting rows: one CTA per row and per SM; candidate rows: 1-4 CTAs per row, two per SM
     hs::RowKernelArgs a{};
     a.logits = logits; a.dtype = dtype; a.row_stride = row_stride; a.vocab = vocab; a.slice = 0;
     a.params = params; a.out = out; a.noise = noise; a.scores_out = scores_out; a.gstage = nullptr;

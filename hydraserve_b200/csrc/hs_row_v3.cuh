@@ -18,10 +18,15 @@
 // so all sums are exact and order-independent.
 //
 // Token ids are only needed at the very end ("a uniformly chosen member of this class",
-// "the lowest ids of this tie group").  A large class is sampled by rejection: Philox-drawn
-// positions are probed until one belongs to the class (exactly uniform over its members,
-// a handful of random reads).  Small classes and lowest-id tie-breaks walk the row a
-// second time; that walk reads what the first pass just brought through L2.
+// "the lowest ids of this tie group").  A class of more than kV3ListCap tokens is sampled by
+// rejection: Philox-drawn positions are probed until one belongs to the class (exactly
+// uniform over its members); a lone CTA issues scattered reads slowly, so a smaller class,
+// or one the probes keep missing, is found by scanning the row once more for its bit
+// pattern.  Lowest-id tie-breaks walk the row hierarchically.
+//
+// The kernel keeps the count table, the row's class list, its side list and the selection
+// histograms in shared memory (about 224 KB, one CTA per SM); what is left of L1 is too
+// small for its streaming loads, which therefore go past it.
 #pragma once
 
 #include "hs_common.cuh"
@@ -30,9 +35,6 @@
 #include "hs_row_kernel.cuh"
 #include "../../include/hs_sampler.h"
 
-#ifndef HS_SCAN_BATCH
-#define HS_SCAN_BATCH 4
-#endif
 namespace hs {
 
 constexpr int kV3Half = 3072;                 // 24 binades x 128 mantissas
@@ -669,7 +671,7 @@ __device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
   // hit, serialised inside each warp.
   const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
   // two batches of loads: the next is on its way while this one is screened
-  constexpr int kBatch = HS_SCAN_BATCH;
+  constexpr int kBatch = 4;
   uint4 w[kBatch], wn[kBatch];
   uint32_t cl[kBatch], cn[kBatch];
   auto fetch = [&](uint4 (&dw)[kBatch], uint32_t (&dc)[kBatch], int i0) {
