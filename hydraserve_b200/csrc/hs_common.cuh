@@ -43,15 +43,6 @@ __device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) 
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
-// The same with an L2 eviction priority: keep = true marks the lines evict-last (data this
-// CTA reads again later while other CTAs stream through L2).
-__device__ __forceinline__ void prefetch_l2_bulk_keep(const void* p, uint32_t bytes) {
-  unsigned long long policy;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
-  asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;" ::"l"(p), "r"(bytes), "l"(policy)
-               : "memory");
-}
-
 // Loads the compiler must issue where they are written (it may otherwise sink a load to its
 // first use, which defeats starting a chain of dependent reads early).
 __device__ __forceinline__ int load_now_s32(const int* p) {

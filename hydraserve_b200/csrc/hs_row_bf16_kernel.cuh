@@ -128,8 +128,8 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
     constexpr uint32_t kPiece = 16384;
     const size_t row_bytes = ((size_t)c.vocab * 2) & ~(size_t)15;
     for (size_t at = (size_t)tid * kPiece; at < row_bytes; at += (size_t)kThreads * kPiece)
-      prefetch_l2_bulk_keep(reinterpret_cast<const unsigned char*>(c.logits) + at,
-                            (uint32_t)min((size_t)kPiece, row_bytes - at));
+      prefetch_l2_bulk(reinterpret_cast<const unsigned char*>(c.logits) + at,
+                       (uint32_t)min((size_t)kPiece, row_bytes - at));
     if (c.cls && (reinterpret_cast<uintptr_t>(c.cls) & 15u) == 0) {
       const size_t cls_bytes = ((size_t)c.vocab / 4) & ~(size_t)15;
       for (size_t at = (size_t)tid * kPiece; at < cls_bytes; at += (size_t)kThreads * kPiece)
