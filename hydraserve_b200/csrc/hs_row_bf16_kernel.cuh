@@ -378,9 +378,20 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
     }
   };
 
+  // per-class raw thresholds of a score bound (see cand_thresholds), for the walks that only
+  // need the few tokens at or above a key
+  CandCtx bound_ctx{nullptr, nullptr, nullptr, nullptr, small + 8, nullptr};
+  int* low_id = small + 3;
   if (c.greedy) {
-    const Group g = find_group(c, max_key);
-    token = nth_in_group(c, g, 1);
+    // arg max with penalties: the lowest id among the tokens whose score key is the maximum
+    if (tid == 0) *low_id = side_key == max_key ? side_arg : 0x7fffffff;
+    cand_thresholds(c, bound_ctx, max_key);  // (ends with a barrier)
+    stream_at_or_above(c, bound_ctx.thr, [&](int id, uint32_t raw, int cc) {
+      if (v3_bin_of_raw(raw) >= 0 && key_of(c.score_of(raw, cc)) == max_key) atomicMin(low_id, id);
+    });
+    __syncthreads();
+    token = *low_id;
+    __syncthreads();
     if (token == 0x7fffffff) { token = any_side ? side_arg : 0; status |= 1; }
     if (P.n_logprobs >= 0) {
       u64 cn;
@@ -570,50 +581,49 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
       Selection sn = select_union3<false, false>(c, kept.cut_key, (u64)n_want, 1.0f);
       if (sn.ok) {
         const int need = n_want - (int)sn.above_cnt;  // lowest ids of the group at the N-th key
-        // members above the N-th key: fewer than N tokens in a few classes and side elements
-        if (tid == 0) *c.gbuf_n = 0;
+        // The tokens above the N-th key (fewer than N) and the group at it: side elements come
+        // from the side list, the rest from one walk of the row against per-class raw
+        // thresholds.  The group's ids go to a list of their own (the member list's memory);
+        // a group too large for it is walked the slow way.
+        int* tie_ids = reinterpret_cast<int*>(c.list);
+        constexpr int kTieCap = (int)(kV3ListCap * sizeof(V3Entry) / sizeof(int));
+        int* tie_n = small + 3;
+        if (tid == 0) { *c.gbuf_n = 0; *tie_n = 0; }
         __syncthreads();
-        for_each_side3(c, [&](int id, float s) {
-          const uint32_t k = key_of(s);
+        auto take = [&](uint32_t k, int id) {
           if (k > sn.key) {
             const int slot = atomicAdd(c.gbuf_n, 1);
             if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{k, id, 1u, 0u, 0ull};
+          } else if (k == sn.key && need > 0) {
+            const int slot = atomicAdd(tie_n, 1);
+            if (slot < kTieCap) tie_ids[slot] = id;
           }
+        };
+        for_each_side3(c, [&](int id, float s) { take(key_of(s), id); });
+        cand_thresholds(c, bound_ctx, sn.key);  // (ends with a barrier)
+        stream_at_or_above(c, bound_ctx.thr, [&](int id, uint32_t raw, int cc) {
+          if (v3_bin_of_raw(raw) < 0) return;  // outside the bin window: a side element, taken above
+          take(key_of(c.score_of(raw, cc)), id);
         });
-        // mark the classes above the N-th key in the (free) histogram area, then walk the row
-        uint32_t* marked = reinterpret_cast<uint32_t*>(c.hist);  // kCells bits
-        for (int i = tid; i < (kCells + 31) / 32; i += kThreads) marked[i] = 0;
-        __syncthreads();
-        int any_marked = 0;
-        for_each_class(c, [&](const ClassEntry& e) {
-          if (e.key > sn.key) { atomicOr(&marked[e.cell >> 5], 1u << (e.cell & 31)); any_marked = 1; }
-        });
-        any_marked = __syncthreads_or(any_marked);
-        if (any_marked) {
-          auto probe = [&](int id, uint32_t raw, int cc) {
-            if (cc == 3) return;
-            const int b = v3_bin_of_raw(raw);
-            if (b < 0) return;
-            const int cell = cc * kV3Bins + b;
-            if ((marked[cell >> 5] >> (cell & 31)) & 1u) {
-              const int slot = atomicAdd(c.gbuf_n, 1);
-              if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{key_of(c.cell_score(cell)), id, 1u, 0u, 0ull};
-            }
-          };
-          const int n8 = c.vec ? c.vocab / 8 : 0;
-          for (int i = tid; i < n8; i += kThreads) {
-            uint32_t raw[8], cls16;
-            load_chunk(c, i, raw, cls16);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) probe(8 * i + k, raw[k], (cls16 >> (2 * k)) & 3);
-          }
-          for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) probe(id, c.logits[id], c.class_of(id));
-        }
         __syncthreads();
         if (need > 0) {
-          const Group g = sn.key == kept.cut_key && have_cut_group ? cut_group : find_group(c, sn.key);
-          const int last_id = nth_in_group(c, g, (u64)need);
-          emit_group_upto(c, g, last_id == 0x7fffffff ? -1 : last_id);
+          const int n_tie = *tie_n;
+          if (n_tie <= kTieCap) {
+            // the `need` lowest ids of the group: each id counts the ids below it
+            for (int t = tid; t < n_tie; t += kThreads) {
+              const int mine = tie_ids[t];
+              int below = 0;
+              for (int j = 0; j < n_tie; ++j) below += tie_ids[j] < mine ? 1 : 0;
+              if (below < need) {
+                const int slot = atomicAdd(c.gbuf_n, 1);
+                if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{sn.key, mine, 1u, 0u, 0ull};
+              }
+            }
+          } else {
+            const Group g = sn.key == kept.cut_key && have_cut_group ? cut_group : find_group(c, sn.key);
+            const int last_id = nth_in_group(c, g, (u64)need);
+            emit_group_upto(c, g, last_id == 0x7fffffff ? -1 : last_id);
+          }
         }
         __syncthreads();
         if (tid < 32) {

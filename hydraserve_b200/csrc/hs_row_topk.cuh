@@ -197,6 +197,62 @@ __device__ void cand_thresholds(const Ctx3& c, CandCtx& L, uint32_t bound) {
   __syncthreads();
 }
 
+// Calls hit(id, raw, count class) for every token of the row whose score key can reach the
+// bound the thresholds stand for: raw value (as signed 16-bit image) >= thr[class] for the
+// classes 0, 1, 2; tokens of class 3 are never reported (they are listed per request).
+// One pass, eight tokens per 128-bit load and one native bf16x2 comparison per two tokens
+// against the most permissive threshold; a hit looks its class up.  Loads go past L1 (the
+// counting kernel, which also uses this, has almost none).
+template <class Hit>
+__device__ void stream_at_or_above(const Ctx3& c, const int* thr, Hit&& hit) {
+  const int tid = threadIdx.x;
+  int t_min = thr[0];
+  if (c.cls) t_min = min(t_min, min(thr[1], thr[2]));
+  // threshold as a bf16 value (NaN = nothing passes, -inf = everything passes)
+  uint32_t tb = t_min > 32640 ? 0x7fc0u : raw_of_t16(t_min);
+  if (t_min <= -32641) tb = 0xff80u;
+  const uint32_t pair = tb * 0x10001u;
+  const __nv_bfloat162 thr2 = *reinterpret_cast<const __nv_bfloat162*>(&pair);
+  auto look = [&](int id, uint32_t raw) {
+    const int cc = c.class_of(id);
+    if (cc != 3 && t16_of_raw(raw) >= thr[cc]) hit(id, raw, cc);
+  };
+  const int n8 = c.vec ? c.vocab / 8 : 0;
+  const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
+  constexpr int kInFlight = 8;
+  for (int base = 0; base < n8; base += kInFlight * kThreads) {
+    uint4 w[kInFlight];
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      const int i = base + tid + u * kThreads;
+      if (i < n8) w[u] = __ldcg(src4 + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kInFlight; ++u) {
+      const int i = base + tid + u * kThreads;
+      if (i >= n8) break;
+      const uint32_t m0 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].x), thr2);
+      const uint32_t m1 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].y), thr2);
+      const uint32_t m2 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].z), thr2);
+      const uint32_t m3 = __hge2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].w), thr2);
+      if (!(m0 | m1 | m2 | m3)) continue;  // the common case
+      uint32_t hits = ((m0 & 1u) | ((m0 >> 15) & 2u)) | (((m1 & 1u) | ((m1 >> 15) & 2u)) << 2) |
+                      (((m2 & 1u) | ((m2 >> 15) & 2u)) << 4) | (((m3 & 1u) | ((m3 >> 15) & 2u)) << 6);
+#pragma unroll 1
+      while (hits) {
+        const int q = __ffs(hits) - 1;
+        hits &= hits - 1;
+        const uint32_t word = q < 2 ? w[u].x : (q < 4 ? w[u].y : (q < 6 ? w[u].z : w[u].w));
+        look(8 * i + q, (word >> (16 * (q & 1))) & 0xffffu);
+      }
+    }
+  }
+  for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) {
+    const uint32_t raw = c.logits[id];
+    if (t16_of_raw(raw) >= t_min) look(id, raw);
+  }
+}
+
 // A lower bound (as signed 16-bit image of a raw value) of the k-th highest raw value among
 // the tokens of [begin, end) that the history does not hold, or -32768 when none is found.
 // The sampled tokens are cut into groups of eight (one 128-bit load); the k highest group
