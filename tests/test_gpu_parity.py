@@ -350,3 +350,66 @@ def test_candidate_path_ties_and_long_lists(sampler):
     assert sampler.query(4, vocab) == 1
     report = compare_case(sampler, w)
     report.assert_ok(max_sensitive_fraction=0.4)
+
+
+def test_full_size_config3_properties(built_library):
+    """Config 3 at its full size (256 x 248,320 bf16, all penalties over 32,768-token
+    histories), where the checker is too slow for every row: the two independent CUDA
+    implementations (count classes / candidates vs the fp32-resident general kernel) must
+    agree row by row on everything that is exact, the call must be reproducible and
+    independent of the batch order, every drawn token must lie in its candidate set, and four
+    rows (first and last of each half) are checked against the checker itself."""
+    import os
+
+    from hydraserve_b200 import workloads
+    from hydraserve_b200.engine import _device
+
+    w = workloads.config3()
+    B, V = w.batch, w.vocab
+    logits = device_logits(w)
+    fast = _device.DeviceSampler("cuda:0", vocab_max=V, batch_max=B, resident_slots=B)
+    os.environ["HS_FORCE_GENERAL"] = "1"
+    try:
+        general = _device.DeviceSampler("cuda:0", vocab_max=V, batch_max=B, resident_slots=B)
+    finally:
+        del os.environ["HS_FORCE_GENERAL"]
+    try:
+        assert fast.query(4, V) == 1 and general.query(4, V) == 0
+        # one shared set of reference-style draws so that both kernels face the same race
+        gen = torch.Generator(device="cuda").manual_seed(1234)
+        noise = torch.empty((B, V), dtype=torch.float32, device="cuda").exponential_(1.0, generator=gen)
+        a, _ = fast.sample(logits, w.histories, w.params, w.steps, None, noise=noise)
+        b, _ = general.sample(logits, w.histories, w.params, w.steps, None, noise=noise)
+        assert int((a["status"] != 0).sum()) == 0 and int((b["status"] != 0).sum()) == 0
+        for field in ("token", "n_kept", "n_after_topk", "n_after_minp", "n_after_topp", "cut_bits", "n_cut_ties"):
+            np.testing.assert_array_equal(a[field], b[field], err_msg=field)
+        np.testing.assert_array_equal(a["row_max"].view(np.uint32), b["row_max"].view(np.uint32))
+        # reproducible, and independent of where a row sits in the batch (seeded Philox draws)
+        p1, _ = fast.sample(logits, w.histories, w.params, w.steps, None)
+        p2, _ = fast.sample(logits, w.histories, w.params, w.steps, None)
+        np.testing.assert_array_equal(p1["token"], p2["token"])
+        perm = np.random.default_rng(0).permutation(B)
+        wp = w.rows(perm.tolist())
+        p3, _ = fast.sample(device_logits(wp), wp.histories, wp.params, wp.steps, None)
+        np.testing.assert_array_equal(p3["token"], p1["token"][perm])
+        np.testing.assert_array_equal(p3["n_kept"], p1["n_kept"][perm])
+        # a drawn token lies in its candidate set: its score is at or above the cut
+        scored, scores = fast.sample(logits, w.histories, w.params, w.steps, None, want_scores=True)
+        picked = scores[torch.arange(B, device=scores.device), torch.from_numpy(scored["token"].astype(np.int64)).to(scores.device)]
+        assert bool(torch.isfinite(picked).all()), "a drawn token is outside its candidate set"
+        kept_counts = torch.isfinite(scores).sum(dim=1).cpu().numpy()
+        np.testing.assert_array_equal(kept_counts, scored["n_kept"])
+        del scores
+        # the near-flat half keeps more than 10,000 tokens per row, the peaked half at least top_k
+        assert int(a["n_kept"][: B // 2].min()) > 10_000
+        assert all(int(a["n_after_topk"][r]) >= w.params[r].top_k for r in range(B // 2, B))
+    finally:
+        fast.close()
+        general.close()
+    # four rows against the checker
+    sub = w.rows([0, B // 2 - 1, B // 2, B - 1])
+    s = _device.DeviceSampler("cuda:0", vocab_max=V, batch_max=8, resident_slots=8)
+    try:
+        compare_case(s, sub).assert_ok(max_sensitive_fraction=0.5)
+    finally:
+        s.close()
