@@ -2,7 +2,7 @@
 
 Run where the reference checkout is available (it is not on the GPU box):
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 Inputs are never stored: each fixture names a seeded generator of
 ``hydraserve_b200.workloads`` (or ``tests/cases.py``) and its arguments, and holds only what
@@ -22,7 +22,9 @@ import torch
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
-REFERENCE = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+REFERENCE = Path(sys.argv[1])
 sys.path.insert(0, str(REFERENCE))
 
 import hydraserve.engine.sampling as ref  # noqa: E402  (the reference)
