@@ -85,6 +85,7 @@ class DeviceSampler:
         _lib.check(self.lib, None, st, "hs_create")
         self.handle = handle
         self.lock = threading.RLock()
+        self._pinned = threading.local()
         self.requests: dict = {}  # request id -> [slot, tokens already counted]
         self.free_slots = list(range(self.resident_slots - 1, -1, -1))
 
@@ -210,17 +211,30 @@ class DeviceSampler:
             scores.data_ptr() if scores is not None else None,
             _lib.HS_SAMPLE_APPEND_TOKEN if append_token else 0, self._stream())
         _lib.check(self.lib, self.handle, st, "hs_sample")
-        host = torch.empty((batch, _lib.ROW_OUT.itemsize), dtype=torch.uint8).pin_memory()
+        host = self._pinned_records(batch)
         host.copy_(d_out, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
-        records = host.numpy().view(_lib.ROW_OUT).reshape(batch)
+        records = host.numpy().view(_lib.ROW_OUT).reshape(batch).copy()  # the pinned buffer is reused
         return records, scores
+
+    def _pinned_records(self, batch: int):
+        """A pinned host buffer for the result records (pinning per call costs more than the copy);
+        one per thread, since calls on different streams may overlap."""
+        cache = self._pinned.__dict__.setdefault("buffers", {})
+        buf = cache.get(batch)
+        if buf is None:
+            buf = self.torch.empty((batch, _lib.ROW_OUT.itemsize), dtype=self.torch.uint8).pin_memory()
+            cache[batch] = buf
+        return buf
 
     def sample(self, logits, histories, params, steps, request_ids=None, *, noise=None,
                want_scores: bool = False):
         """Stateless (histories rebuilt on the device for this call) or, with
         ``request_ids``, incremental sampling.  Returns (records, scores)."""
         batch, vocab = logits.shape
+        # start the host-to-device copy of the logits (if they are on the host) first: the
+        # bookkeeping below then runs while they travel
+        logits, _, _ = self.prepare_logits(logits)
         with self.lock:
             slots = [-1] * batch
             resets, appends = [], []
