@@ -42,7 +42,7 @@ UNIT = "rows/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the two kernels of one step, from the ncu
 # capture summarised in profiles/ (same workload, one step)
-NCU_DRAM_BYTES_PER_STEP = 149.8e6
+NCU_DRAM_BYTES_PER_STEP = 152.8e6
 ROTATING_SETS = 8
 
 
