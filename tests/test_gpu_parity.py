@@ -413,3 +413,38 @@ def test_full_size_config3_properties(built_library):
         compare_case(s, sub).assert_ok(max_sensitive_fraction=0.5)
     finally:
         s.close()
+
+
+def test_rows_with_more_classes_than_shared_memory_holds(sampler):
+    """Logits spread over every bf16 value of the bin window, two thirds of the tokens in the
+    history once or twice: far more than 6,144 non-empty (count class, value) classes per row,
+    so the class list spills from shared memory into its global scratch."""
+    from hydraserve_b200.engine.sampling import SamplingParams
+    from hydraserve_b200.workloads import Workload
+
+    rng = np.random.default_rng(41)
+    vocab, batch = 120_000, 4
+    # uniformly random bf16 patterns with 2^-14 <= |x| < 2^4 (sign, 18 binades, 7 mantissa bits)
+    exponent = rng.integers(113, 131, (batch, vocab)).astype(np.uint16)
+    mantissa = rng.integers(0, 128, (batch, vocab)).astype(np.uint16)
+    sign = rng.integers(0, 2, (batch, vocab)).astype(np.uint16)
+    bits = (sign << 15) | (exponent << 7) | mantissa
+    hist = []
+    for r in range(batch):
+        once = rng.choice(vocab, vocab // 3, replace=False)
+        twice = rng.choice(vocab, vocab // 3, replace=False)
+        hist.append(np.concatenate([once, twice, twice]).astype(np.int32))
+    params = [
+        SamplingParams(temperature=1.0, top_p=0.97, seed=1, repetition_penalty=1.3, presence_penalty=0.7,
+                       frequency_penalty=0.4, logprobs=20),
+        SamplingParams(temperature=0.6, top_k=2000, top_p=0.9, seed=2, presence_penalty=1.0, frequency_penalty=0.5),
+        SamplingParams(temperature=1.5, min_p=0.001, seed=3, repetition_penalty=0.8, frequency_penalty=0.2, logprobs=4),
+        SamplingParams(temperature=0.0, repetition_penalty=1.5, presence_penalty=0.2, logprobs=10),
+    ]
+    w = Workload("many_classes", bits, "bf16", hist, params, [3, 2, 1, 0])
+    x = w.logits_f32()
+    for r in range(batch):
+        y = O.penalise(x[r], hist[r], params[r])
+        classes = {(int(c), float(v)) for c, v in zip(np.minimum(np.bincount(hist[r], minlength=vocab), 3), x[r])}
+        assert len(classes) > 6144 and np.isfinite(y).all()
+    compare_case(sampler, w).assert_ok(max_sensitive_fraction=0.5)
