@@ -448,3 +448,37 @@ def test_rows_with_more_classes_than_shared_memory_holds(sampler):
         classes = {(int(c), float(v)) for c, v in zip(np.minimum(np.bincount(hist[r], minlength=vocab), 3), x[r])}
         assert len(classes) > 6144 and np.isfinite(y).all()
     compare_case(sampler, w).assert_ok(max_sensitive_fraction=0.5)
+
+
+def test_rows_with_thousands_of_often_repeated_tokens(sampler):
+    """Histories in which 3,000 tokens occur three to six times: their exact counts matter
+    (frequency penalty), the list of such tokens is longer than one thread-per-entry pass and
+    than the side list's shared-memory form, in the counting and in the candidate kernel."""
+    from hydraserve_b200.engine.sampling import SamplingParams
+    from hydraserve_b200.workloads import Workload
+
+    rng = np.random.default_rng(43)
+    vocab, batch = 60_000, 4
+    raw = (rng.standard_normal((batch, vocab)) * 2.5).astype(np.float32)
+    bits = np.empty(raw.shape, np.uint16)
+    for r in range(batch):
+        _, bits[r] = _bf16_round(raw[r])
+    hist = []
+    for r in range(batch):
+        often = rng.choice(vocab, 3000, replace=False)
+        # the highest logits are among the often repeated ones, so that they decide the cuts
+        often[:50] = np.argsort(-raw[r])[:50]
+        reps = rng.integers(3, 7, often.size)
+        rest = rng.integers(0, vocab, 5000)
+        h = np.concatenate([np.repeat(often, reps), rest]).astype(np.int32)
+        rng.shuffle(h)
+        hist.append(h)
+    params = [
+        SamplingParams(temperature=1.0, top_p=0.9, seed=1, frequency_penalty=0.15, presence_penalty=0.1, logprobs=20),
+        SamplingParams(temperature=0.9, top_k=64, top_p=0.95, seed=2, frequency_penalty=0.2, repetition_penalty=1.1,
+                       logprobs=20),
+        SamplingParams(temperature=0.0, frequency_penalty=0.3, logprobs=5),
+        SamplingParams(temperature=1.2, top_k=256, min_p=0.002, seed=4, frequency_penalty=0.1),
+    ]
+    w = Workload("often_repeated", bits, "bf16", hist, params, [0, 1, 2, 3])
+    compare_case(sampler, w).assert_ok(max_sensitive_fraction=0.5)
