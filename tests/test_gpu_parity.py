@@ -482,3 +482,34 @@ def test_rows_with_thousands_of_often_repeated_tokens(sampler):
     ]
     w = Workload("often_repeated", bits, "bf16", hist, params, [0, 1, 2, 3])
     compare_case(sampler, w).assert_ok(max_sensitive_fraction=0.5)
+
+
+def test_candidate_list_overflow_falls_back_to_counting(sampler):
+    """More tokens tied at the k-th value than a candidate list holds: the candidate kernel
+    hands the row back and the second counting pass serves it (all ties are kept, as in the
+    reference).  One row is wide enough to be split over two CTAs, one is not."""
+    from hydraserve_b200.engine.sampling import SamplingParams
+    from hydraserve_b200.workloads import Workload
+
+    rng = np.random.default_rng(47)
+    for vocab in (20_000, 90_000):
+        batch = 3
+        raw = (rng.standard_normal((batch, vocab)) * 1.5).astype(np.float32)
+        raw = np.minimum(raw, 3.0)
+        tied = rng.choice(vocab, 9000, replace=False)
+        raw[0, tied] = 4.0                      # 9,000 tokens share the maximum: top_k = 50 keeps them all
+        raw[1, tied[:6000]] = 4.0               # 20 leaders, then 6,000 tied at the value where k = 40 falls
+        raw[1, tied[6000:6020]] = 6.0 + np.arange(20, dtype=np.float32) * 0.5
+        bits = np.empty(raw.shape, np.uint16)
+        for r in range(batch):
+            _, bits[r] = _bf16_round(raw[r])
+        params = [
+            SamplingParams(temperature=1.0, top_k=50, seed=1, logprobs=20),
+            SamplingParams(temperature=0.8, top_k=40, top_p=0.9, seed=2, presence_penalty=0.5, logprobs=5),
+            SamplingParams(temperature=1.0, top_k=50, top_p=0.95, seed=3),  # an ordinary row beside them
+        ]
+        hist = [rng.integers(0, vocab, 500).astype(np.int32) for _ in range(batch)]
+        w = Workload("overflow", bits, "bf16", hist, params, [0, 1, 2])
+        rows, _ = oracle_rows(w)
+        assert rows[0].n_after_topk >= 9000 and rows[1].n_after_topk >= 5000  # (a few tied tokens are penalised)
+        compare_case(sampler, w).assert_ok(max_sensitive_fraction=0.67)
