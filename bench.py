@@ -1,19 +1,32 @@
 #!/usr/bin/env python
 """Benchmark of the per-step token sampler.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|3|4|5]
 
-A step is one pass of the sampler over one batch of the large-vocabulary stress
-configuration (256 rows x 248,320 bf16 logits, repetition / presence / frequency
-penalties over 32,768-token histories held in device-resident histograms, top-k / top-p /
-min-p, seeded Philox draw), each rank working on its own 256 rows (weak scaling, no
-inter-GPU traffic).  Prints one JSON line on rank 0.
+A step is one pass of the sampler over one batch of synthetic logits.  The default workload
+(``--config 3``) is the large-vocabulary stress configuration: 256 rows x 248,320 bf16 logits,
+repetition / presence / frequency penalties over 32,768-token histories held in
+device-resident histograms, top-k / top-p / min-p, seeded Philox draw; under ``--gpus N``
+each rank works on its own 256 rows (weak scaling, no inter-GPU traffic).  The other
+configurations of the same path:
+
+  --config 2   decode step, 64 x 151,936 bf16, mixed parameters, 20 logprobs per row
+               (small and launch-bound: the single-step latency is reported too)
+  --config 4   1,024 x 151,936 bf16 with per-row random parameters, the rows split evenly
+               over the N GPUs (fixed total work: strong scaling), no inter-GPU traffic
+  --config 5   128 x 248,320 bf16 split by VOCABULARY over the N GPUs: per-slice candidate
+               records, an NCCL all-gather of 536 bytes per row and rank, and a merge kernel;
+               the three parts are timed separately and NVLink bytes reported apart from HBM
+
+Prints one JSON line on rank 0.
 
 value   rows/s with the logits already in HBM (CUDA events around K back-to-back steps
-        over rotating input sets, max over ranks)
+        over rotating input sets larger than L2, max over ranks)
 e2e     rows/s through the Python drop-in ``sample_logits`` with the logits in pinned host
         memory: host-to-device copy of the step's logits, histogram delta and parameters,
         and device-to-host copy of the result records, all inside the timed region
+        (``e2e_device_logits``: the same call with the logits already on the device, which
+        is where a serving worker's LM head leaves them)
 roofline  HBM: algorithmic bytes of one launch / average launch time, against the measured
         copy bandwidth in MEASURED_PEAKS.json
 cpu_baseline  the reference's CPU operator sequence (oracle/reference_port.py) timed on a
@@ -40,24 +53,44 @@ if str(ROOT) not in sys.path:
 METRIC = "sampled rows/sec"
 UNIT = "rows/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of the two kernels of one step, from the ncu
-# capture summarised in profiles/ (same workload, one step)
-NCU_DRAM_BYTES_PER_STEP = 152.8e6
-ROTATING_SETS = 8
+# dram__bytes_read.sum + dram__bytes_write.sum of one step's kernel on config 3, from the ncu
+# capture summarised in profiles/bf16_row_kernel_config3.md (None until one is taken)
+NCU_DRAM_BYTES_PER_STEP = {3: None}
+
+WORKLOADS = {
+    2: dict(batch=64, vocab=151_936, history=4096, sets=8, scaling="weak",
+            text="config2: decode step, 64 x 151,936 bf16 N(0,3^2) + Zipf bias, rows cycle through greedy / "
+                 "top_p 0.95 / top_k 20 + min_p 0.05 / top_k 40 + top_p 0.8 + T 1.2, presence 0.5 and frequency 0.3 "
+                 "over histories of 1-4,096 tokens, 20 logprobs per row"),
+    3: dict(batch=256, vocab=248_320, history=32_768, sets=8, scaling="weak",
+            text="config3: large-vocab stress, 256 x 248,320 bf16, all penalties over 32,768-token "
+                 "histories, half near-flat rows (top_p 0.99), half peaked rows with ties at the top-k "
+                 "boundary (top_k 50, top_p 0.9, min_p 0.02), seeded Philox"),
+    4: dict(batch=1024, vocab=151_936, history=8192, sets=2, scaling="strong",
+            text="config4: row-sharded decode, 1,024 x 151,936 bf16 N(0,3^2) in total, per-row parameters drawn "
+                 "from a seed (T 0.3-1.5, top_k in {0,20,50,200}, top_p 0.7-1, min_p in {0,0.05}, penalties 0-0.6), "
+                 "histories of 512-8,192 tokens, rows split evenly over the GPUs"),
+    5: dict(batch=128, vocab=248_320, history=0, sets=8, scaling="strong",
+            text="config5: vocabulary-sharded sampling, 128 x 248,320 bf16 N(0,3^2) cut into one contiguous slice "
+                 "per GPU, top_k 50, top_p 0.9, T 0.8, 20 logprobs; per-slice records merged after an NCCL all-gather"),
+}
 
 
-def workload_config(batch, vocab, history_len, n_gpus, extra=None):
-    cfg = {
-        "workload": "config3: large-vocab stress, 256 x 248,320 bf16, all penalties over 32,768-token "
-                    "histories, half near-flat rows (top_p 0.99), half peaked rows with ties at the top-k "
-                    "boundary (top_k 50, top_p 0.9, min_p 0.02), seeded Philox",
-        "batch_per_gpu": batch, "vocab": vocab, "history_len": history_len,
-        "sharding": f"rows x{n_gpus}, no inter-GPU traffic",
-        "cache": f"{ROTATING_SETS} rotating input sets of {batch * vocab * 2 / 1e6:.0f} MB each (> 126 MB L2)",
-    }
-    if extra:
-        cfg.update(extra)
-    return cfg
+def workload_config(cfg: int, n_gpus: int, batch=None, vocab=None, history=None, sets=None):
+    """The `config` object of the JSON line; the same for both arms of one configuration."""
+    w = WORKLOADS[cfg]
+    batch = w["batch"] if batch is None else batch
+    vocab = w["vocab"] if vocab is None else vocab
+    history = w["history"] if history is None else history
+    sets = w["sets"] if sets is None else sets
+    if cfg == 4:
+        sharding = f"{batch} rows in total, {batch // n_gpus} per GPU, no inter-GPU traffic"
+    elif cfg == 5:
+        sharding = f"vocabulary x{n_gpus} ({(vocab + n_gpus - 1) // n_gpus} tokens per GPU), NCCL all-gather of the records"
+    else:
+        sharding = f"rows x{n_gpus} ({batch} per GPU), no inter-GPU traffic"
+    return {"workload": w["text"], "batch": batch, "vocab": vocab, "history_len": history, "sharding": sharding,
+            "cache": f"GPU arm: {sets} rotating input sets, together larger than the 126 MB L2; reference arm: host memory"}
 
 
 # --------------------------------------------------------------------------- clocks
@@ -77,7 +110,7 @@ class ClockSampler:
 
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
@@ -98,8 +131,29 @@ class ClockSampler:
             for name, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        # "under load": the samples in the upper half of the observed clock range (the sampler
+        # also runs while the host prepares inputs and the GPU idles at a low clock)
+        busy = [v for v in sm if v >= 0.5 * max(sm)] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons),
+                "window": "from before the warm-up to after the end-to-end leg"}
+
+
+# --------------------------------------------------------------------------- workloads
+def make_workload(cfg: int, rank: int, world: int, args):
+    from hydraserve_b200 import workloads
+
+    w = WORKLOADS[cfg]
+    batch = args.batch or w["batch"]
+    vocab = args.vocab or w["vocab"]
+    if cfg == 2:
+        return workloads.config2(seed=2 + 1000 * rank, batch=batch, vocab=vocab)
+    if cfg == 3:
+        return workloads.config3(seed=3 + 1000 * rank, batch=batch, vocab=vocab,
+                                 history_len=args.history if args.history is not None else w["history"])
+    if cfg == 4:
+        return workloads.config4(seed=4 + 1000 * rank, batch=max(1, batch // world), vocab=vocab)
+    return workloads.config5(seed=5, batch=batch, vocab=vocab)  # the same rows on every rank
 
 
 # --------------------------------------------------------------------------- CPU arms
@@ -121,11 +175,15 @@ def _cpu_rows_worker(index_range):
 
 
 def cpu_sample_of(w, n_rows):
-    """A bounded sample of the workload's rows covering both row classes evenly."""
+    """A bounded sample of the workload's rows, evenly spread over the batch (config 3's two
+    halves, near-flat and peaked, are covered evenly)."""
     import torch
 
-    half = w.batch // 2
-    take = list(range(n_rows // 2)) + list(range(half, half + n_rows - n_rows // 2))
+    take = sorted({int(i) for i in np.linspace(0, w.batch - 1, min(n_rows, w.batch))})
+    if w.name == "config3" and w.batch >= 2:
+        half = w.batch // 2
+        n = min(n_rows, w.batch)
+        take = list(range(n // 2)) + list(range(half, half + n - n // 2))
     sub = w.rows(take)
     logits = torch.from_numpy(sub.logits.view(np.int16)).view(torch.bfloat16)
     return logits, [h.tolist() for h in sub.histories], sub.params, sub.steps
@@ -139,11 +197,12 @@ def time_cpu_single(w, n_rows):
     from oracle import reference_port
 
     logits, histories, params, steps = cpu_sample_of(w, n_rows)
+    n_rows = logits.shape[0]
     reference_port.sample_batch(logits[:2], histories[:2], params[:2], steps[:2])
     t0 = time.perf_counter()
     reference_port.sample_batch(logits, histories, params, steps)
     dt = time.perf_counter() - t0
-    return n_rows / dt, torch.get_num_threads(), dt
+    return n_rows / dt, torch.get_num_threads(), dt, n_rows
 
 
 def run_reference_arm(args, world, rank):
@@ -154,13 +213,16 @@ def run_reference_arm(args, world, rank):
         return
     import multiprocessing as mp
 
-    from hydraserve_b200 import workloads
-
     cores = os.cpu_count() or 1
     procs = max(1, min(cores, 64))
     rows_per_step = max(16, 2 * procs)
-    w = workloads.config3(batch=max(rows_per_step, 2))
+    cfg = args.config
+    spec = dict(WORKLOADS[cfg])
+    # only the sampled rows are generated: the reference arm never needs the whole batch
+    ns = argparse.Namespace(batch=max(rows_per_step, 2), vocab=args.vocab, history=args.history)
+    w = make_workload(cfg, 0, 1, ns)
     _CPU_ROWS = cpu_sample_of(w, rows_per_step)
+    rows_per_step = int(_CPU_ROWS[0].shape[0])
     bounds = np.linspace(0, rows_per_step, procs + 1).astype(int)
     ranges = [(int(bounds[i]), int(bounds[i + 1])) for i in range(procs)]
     ctx = mp.get_context("fork")
@@ -172,34 +234,36 @@ def run_reference_arm(args, world, rank):
             pool.map(_cpu_rows_worker, ranges)
         dt = time.perf_counter() - t0
     value = rows_per_step * args.steps / dt
-    sample = (f"{rows_per_step} rows per step (half near-flat, half peaked) of the 256 x 248,320 workload, "
+    full = args.batch or spec["batch"]
+    sample = (f"{rows_per_step} rows per step, evenly spread over the {full} x {args.vocab or spec['vocab']} workload, "
               f"split over {procs} single-threaded processes")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3 * 256 / rows_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(256, 248_320, 32_768, args.gpus, {"cache": "host memory"}),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "rows_per_step": rows_per_step, "ms_per_full_batch": dt / args.steps * 1e3 * full / rows_per_step,
+        "higher_is_better": True, "scaling": spec["scaling"], "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, args.gpus, args.batch, args.vocab, args.history, args.sets),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": procs, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
         "note": "the reference is Python and does not travel to this box; its CPU operator sequence is timed "
                 "through oracle/reference_port.py (checked against the reference's outputs in tests/test_oracle.py); "
-                "ms_per_step is scaled to the full 256-row step",
+                "a step is the bounded sample named in cpu_baseline.sample, ms_per_step is that step's own time",
     }
     print(json.dumps(line), flush=True)
 
 
 # --------------------------------------------------------------------------- GPU arm
-def run_ours(args, world, rank, local_rank):
+def _peak():
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        return float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured copy bandwidth (MEASURED_PEAKS.json)"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def _setup_dist(world, device):
     import torch
 
-    from hydraserve_b200 import _lib, workloads
-    from hydraserve_b200.engine import _device, sample_logits
-
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA GPU (there is no CPU sampling path)")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
@@ -212,19 +276,54 @@ def run_ours(args, world, rank, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    w = workloads.config3(seed=3 + 1000 * rank, batch=args.batch, vocab=args.vocab, history_len=args.history)
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    return dist, barrier, max_over_ranks
+
+
+def run_ours(args, world, rank, local_rank):
+    import torch
+
+    from hydraserve_b200 import _lib
+    from hydraserve_b200.engine import _device, sample_logits
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA GPU (there is no CPU sampling path)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist, barrier, max_over_ranks = _setup_dist(world, device)
+    if args.config == 5:
+        run_vocab_sharded(args, world, rank, device, dist, barrier, max_over_ranks)
+        return
+    cfg = args.config
+    spec = WORKLOADS[cfg]
+    n_sets = args.sets or spec["sets"]
+
+    uuid = str(torch.cuda.get_device_properties(device).uuid)
+    clocks = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid) if rank == 0 else None
+
+    w = make_workload(cfg, rank, world, args)
     batch, vocab = w.batch, w.vocab
-    sampler = _device.DeviceSampler(device, vocab_max=vocab, batch_max=batch, resident_slots=batch)
+    history_len = max((int(h.size) for h in w.histories), default=0)
+    sampler = _device.DeviceSampler(device, vocab_max=vocab, batch_max=batch, resident_slots=batch,
+                                    hist_cap=min(vocab, max(history_len, 4096)))
     lib, handle = sampler.lib, sampler.handle
 
     # device-resident histograms, one slot per row (request); built once, outside the timed region
-    slots = list(range(batch))
-    sampler.reset_slots(slots)
-    sampler.append_tokens(slots, w.histories, vocab)
-    uniques = [int(np.unique(h[(h >= 0) & (h < vocab)]).size) for h in w.histories]
+    slots = [i if _device._has_penalties(p) and w.histories[i].size else -1 for i, p in enumerate(w.params)]
+    live = [s for s in slots if s >= 0]
+    sampler.reset_slots(live)
+    sampler.append_tokens(live, [w.histories[s] for s in live], vocab)
+    uniques = [int(np.unique(h[(h >= 0) & (h < vocab)]).size) if slots[i] >= 0 else 0
+               for i, h in enumerate(w.histories)]
 
     host_logits = torch.from_numpy(w.logits.view(np.int16)).view(torch.bfloat16).pin_memory()
-    sets = [host_logits.to(device, non_blocking=True).clone() for _ in range(ROTATING_SETS)]
+    sets = [host_logits.to(device, non_blocking=True).clone() for _ in range(n_sets)]
     total_steps = args.steps + args.warmup
     # one parameter set per step: the step number advances the seeded stream, as in serving.
     # (Replaying a few sets round robin while the sampled tokens are appended makes every
@@ -233,13 +332,13 @@ def run_ours(args, world, rank, local_rank):
     param_sets = []
     for i in range(n_param_sets):
         rec = _device.pack_params(w.params, [s + i for s in w.steps], slots)
-        param_sets.append(sampler._to_device(rec.view(np.uint8).reshape(batch, -1)))
+        param_sets.append(torch.from_numpy(rec.view(np.uint8).copy()).to(device))
     d_out = torch.empty((batch, _lib.ROW_OUT.itemsize), dtype=torch.uint8, device=device)
     stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
     torch.cuda.synchronize()
 
     def step(i):
-        st = lib.hs_sample(handle, sets[i % ROTATING_SETS].data_ptr(), _lib.HS_DTYPE_BF16, vocab, batch, vocab,
+        st = lib.hs_sample(handle, sets[i % n_sets].data_ptr(), _lib.HS_DTYPE_BF16, vocab, batch, vocab,
                            param_sets[i % n_param_sets].data_ptr(), d_out.data_ptr(), None, None,
                            _lib.HS_SAMPLE_APPEND_TOKEN, stream)
         if st != 0:
@@ -248,8 +347,6 @@ def run_ours(args, world, rank, local_rank):
     for i in range(args.warmup):
         step(i)
     launches0 = sampler.query(3, vocab)
-    uuid = str(torch.cuda.get_device_properties(device).uuid)
-    clocks = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid) if rank == 0 else None
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -259,90 +356,226 @@ def run_ours(args, world, rank, local_rank):
     barrier()
     elapsed_ms = e0.elapsed_time(e1)
     launches = sampler.query(3, vocab) - launches0
-    clock_info = clocks.stop() if clocks else None
     records = d_out.cpu().numpy().view(_lib.ROW_OUT).reshape(batch)
     if int((records["status"] != 0).sum()):
         raise RuntimeError("a row reported a non-zero status")
-    if dist is not None:
-        t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
+    elapsed_ms = max_over_ranks(elapsed_ms)
     ms_per_step = elapsed_ms / args.steps
     value = world * batch * args.steps / (elapsed_ms * 1e-3)
 
-    # ---- end to end through the drop-in Python API, logits in pinned host memory -------
+    # single steps with the GPU idle before each: the kernel's own duration; what a back-to-back
+    # step takes beyond it is time the GPU waited for the host between launches
+    single = []
+    for i in range(16):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step(total_steps + i)
+        b.record()
+        torch.cuda.synchronize()
+        single.append(a.elapsed_time(b))
+    single_ms = statistics.median(single)
+
+    # ---- end to end through the drop-in Python API ------------------------------------
     e2e_steps = 0 if args.kernel_only else max(1, min(args.steps, args.e2e_steps))
-    histories = [h.tolist() for h in w.histories]
-    request_ids = [f"bench-{rank}-{i}" for i in range(batch)]
-    e2e_sampler = _device.sampler_for(device, vocab, batch) if e2e_steps else None
-    steps_now = list(w.steps)
     h2d = host_logits.numel() * 2 + batch * _lib.ROW_PARAMS.itemsize + batch * 4 * 3
     d2h = batch * _lib.ROW_OUT.itemsize
 
-    def e2e_step():
-        out = sample_logits(host_logits, histories, w.params, steps=steps_now, request_ids=request_ids)
-        for i, s in enumerate(out):
-            histories[i].append(s.token_id)
-            steps_now[i] += 1
+    def e2e_leg(logits, tag):
+        histories = [h.tolist() for h in w.histories]
+        request_ids = [f"bench-{tag}-{rank}-{i}" for i in range(batch)]
+        steps_now = list(w.steps)
 
-    e2e_s = float("inf")
-    if e2e_steps:
+        def one():
+            out = sample_logits(logits, histories, w.params, steps=steps_now, request_ids=request_ids)
+            for i, s in enumerate(out):
+                histories[i].append(s.token_id)
+                steps_now[i] += 1
+
         for _ in range(2):
-            e2e_step()  # the first call uploads the full histories; later calls only the new token
+            one()  # the first call uploads the full histories; later calls only the new token
         barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            e2e_step()
+            one()
         torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
-    if dist is not None:
-        t = torch.tensor([e2e_s], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_value = world * batch * e2e_steps / e2e_s
-    del e2e_sampler
+        dt = max_over_ranks(time.perf_counter() - t0)
+        for rid in request_ids:
+            _device.release_request(rid)
+        return world * batch * e2e_steps / dt, dt / e2e_steps * 1e3
+
+    e2e_value = e2e_ms = dev_value = dev_ms = None
+    if e2e_steps:
+        e2e_value, e2e_ms = e2e_leg(host_logits, "host")
+        dev_value, dev_ms = e2e_leg(sets[0], "device")
+    clock_info = clocks.stop() if clocks else None
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
-    peaks_file = ROOT / "MEASURED_PEAKS.json"
-    if peaks_file.exists():
-        peak, peak_src = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured copy bandwidth (MEASURED_PEAKS.json)"
-    else:
-        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    peak, peak_src = _peak()
     logits_bytes = batch * vocab * 2
     algo_bytes = logits_bytes + 8 * sum(uniques) + batch * (_lib.ROW_PARAMS.itemsize + _lib.ROW_OUT.itemsize)
     achieved = algo_bytes / (ms_per_step * 1e-3) / 1e9
+    default_shape = (batch, vocab) == (spec["batch"] // (world if cfg == 4 else 1), spec["vocab"])
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-        "traffic": NCU_DRAM_BYTES_PER_STEP if (batch, vocab, args.history) == (256, 248_320, 32_768) else None,
-        "kernel": "hs::row_kernel_v3 (counting rows) and hs::row_kernel_topk (small top_k rows), side by side on "
-                  "two streams; one step = both",
+        "traffic": NCU_DRAM_BYTES_PER_STEP.get(cfg) if default_shape else None,
+        "kernel": "hs::row_kernel_bf16 (one launch per step: counting rows and candidate-row parts, two CTAs per SM)",
         "peak_source": peak_src,
         "algorithmic_bytes_per_launch": algo_bytes, "logits_bytes_per_launch": logits_bytes,
         "logits_only_gbs": logits_bytes / (ms_per_step * 1e-3) / 1e9,
     }
     cpu = None
     if world == 1 and not args.no_cpu and not args.kernel_only:
-        rows = args.cpu_rows
-        v, threads, dt = time_cpu_single(w, rows)
+        v, threads, dt, rows = time_cpu_single(w, args.cpu_rows)
         cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-               "sample": f"{rows} of the {batch} rows (half near-flat, half peaked), one process, the reference's "
-                         f"per-row loop, {dt:.1f} s", "host_cores": os.cpu_count()}
+               "sample": f"{rows} of the {batch} rows, evenly spread, one process, the reference's per-row loop, "
+                         f"{dt:.1f} s", "host_cores": os.cpu_count()}
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": spec["scaling"],
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(batch, vocab, args.history, world, {"cluster_ctas_per_row": sampler.query(0, vocab),
-                                             "row_staged_in_shared_memory": bool(sampler.query(1, vocab))}),
+        "config": workload_config(cfg, world, args.batch, args.vocab, args.history, n_sets),
         "roofline": roofline,
         "cpu_baseline": cpu,
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "steps": e2e_steps, "path": "hydraserve_b200.engine.sample_logits(pinned host logits, request_ids=...)"},
+        "e2e": None if e2e_value is None else {
+            "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "steps": e2e_steps, "ms_per_step": e2e_ms,
+            "path": "hydraserve_b200.engine.sample_logits(pinned host logits, request_ids=...)"},
+        "e2e_device_logits": None if dev_value is None else {
+            "value": dev_value, "unit": UNIT, "ms_per_step": dev_ms, "steps": e2e_steps,
+            "h2d_bytes_per_step": h2d - host_logits.numel() * 2, "d2h_bytes_per_step": d2h,
+            "path": "the same call with the logits already on the device (where the LM head leaves them)"},
         "gpu_launches": launches,
+        "single_step": {"ms": single_ms, "what": "one launch with the GPU idle before it (median of 16)",
+                        "gpu_wait_for_host_us_per_step": max(0.0, (ms_per_step - single_ms) * 1e3)},
+        "rows_per_gpu": batch,
+        "hbm_held_mb": sampler.device_bytes() / 1e6,
         "clocks": clock_info,
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def run_vocab_sharded(args, world, rank, device, dist, barrier, max_over_ranks):
+    """Config 5: every rank holds a contiguous slice of the vocabulary of all 128 rows."""
+    import torch
+
+    from hydraserve_b200 import _lib
+    from hydraserve_b200.engine import _device, sharded
+
+    spec = WORKLOADS[5]
+    n_sets = args.sets or spec["sets"]
+    uuid = str(torch.cuda.get_device_properties(device).uuid)
+    clocks = ClockSampler(uuid if uuid.startswith("GPU-") else "GPU-" + uuid) if rank == 0 else None
+    w = make_workload(5, rank, world, args)
+    batch, vocab = w.batch, w.vocab
+    lo, hi = sharded.shard_bounds(vocab, world)[rank]
+    width = hi - lo
+    sampler = _device.DeviceSampler(device, vocab_max=width, batch_max=batch, resident_slots=4, hist_cap=4096)
+    lib, handle = sampler.lib, sampler.handle
+    local = np.ascontiguousarray(w.logits[:, lo:hi])
+    host = torch.from_numpy(local.view(np.int16)).view(torch.bfloat16).pin_memory()
+    # a slice is 8 MB at 8 GPUs: enough rotating sets to exceed L2 would be 16+; the sets rotate
+    # all the same, and the slice size is stated in the line
+    sets = [host.to(device, non_blocking=True).clone() for _ in range(n_sets)]
+    total_steps = args.steps + args.warmup
+    n_param_sets = min(total_steps, 512)
+    param_sets = []
+    for i in range(n_param_sets):
+        rec = _device.pack_params(w.params, [s + i for s in w.steps], [-1] * batch)
+        param_sets.append(torch.from_numpy(rec.view(np.uint8).copy()).to(device))
+    recs = torch.empty((batch, _lib.SHARD_REC.itemsize), dtype=torch.uint8, device=device)
+    gathered = torch.empty((world, batch, _lib.SHARD_REC.itemsize), dtype=torch.uint8, device=device)
+    d_out = torch.empty((batch, _lib.ROW_OUT.itemsize), dtype=torch.uint8, device=device)
+    stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    marks = []
+
+    def step(i, timed):
+        p = param_sets[i % n_param_sets]
+        m = [ev() for _ in range(4)] if timed else None
+        if timed:
+            m[0].record()
+        st = lib.hs_sharded_partial(handle, sets[i % n_sets].data_ptr(), _lib.HS_DTYPE_BF16, width, batch, width, lo,
+                                    p.data_ptr(), recs.data_ptr(), stream)
+        if st != 0:
+            raise RuntimeError(lib.hs_last_error(handle).decode())
+        if timed:
+            m[1].record()
+        if dist is not None:
+            dist.all_gather_into_tensor(gathered, recs)
+        else:
+            gathered[0].copy_(recs)
+        if timed:
+            m[2].record()
+        st = lib.hs_sharded_merge(handle, gathered.data_ptr(), world, batch, vocab, p.data_ptr(), d_out.data_ptr(),
+                                  None, None, stream)
+        if st != 0:
+            raise RuntimeError(lib.hs_last_error(handle).decode())
+        if timed:
+            m[3].record()
+            marks.append(m)
+
+    for i in range(args.warmup):
+        step(i, False)
+    launches0 = sampler.query(3)
+    barrier()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for i in range(args.warmup, total_steps):
+        step(i, False)
+    e1.record()
+    barrier()
+    elapsed_ms = max_over_ranks(e0.elapsed_time(e1))
+    launches = sampler.query(3) - launches0
+    ms_per_step = elapsed_ms / args.steps
+    # the three parts, timed apart on a second, shorter pass (events between them cost a little)
+    n_parts = min(args.steps, 100)
+    for i in range(n_parts):
+        step(total_steps + i, True)
+    torch.cuda.synchronize()
+    part_ms = [statistics.median(m[k].elapsed_time(m[k + 1]) for m in marks) for k in range(3)]
+    part_ms = [max_over_ranks(v) for v in part_ms]
+    records = d_out.cpu().numpy().view(_lib.ROW_OUT).reshape(batch)
+    sharded.check_records(records)
+    tokens = torch.from_numpy(records["token"].astype(np.int64)).to(device)
+    if dist is not None:
+        everyone = [torch.empty_like(tokens) for _ in range(world)]
+        dist.all_gather(everyone, tokens)
+        if not all(bool((t == everyone[0]).all()) for t in everyone):
+            raise RuntimeError("ranks disagree on the sampled tokens")
+    clock_info = clocks.stop() if clocks else None
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    peak, peak_src = _peak()
+    rec_b = _lib.SHARD_REC.itemsize
+    hbm_bytes = batch * width * 2 + batch * rec_b + batch * world * rec_b + batch * (_lib.ROW_PARAMS.itemsize * 2 + _lib.ROW_OUT.itemsize)
+    achieved = hbm_bytes / (ms_per_step * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": batch * args.steps / (elapsed_ms * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(5, world, args.batch, args.vocab, 0, n_sets),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_src, "kernel": "hs::shard_partial_kernel + hs::shard_merge_kernel",
+                     "algorithmic_bytes_per_launch": hbm_bytes, "logits_bytes_per_launch": batch * width * 2,
+                     "note": "per GPU; the step is latency-bound (three dependent operations on one stream)"},
+        "parts_ms": {"partial_kernel": part_ms[0], "all_gather": part_ms[1], "merge_kernel": part_ms[2],
+                     "what": "median per step, max over ranks, CUDA events between the parts"},
+        "nvlink_bytes_per_step_per_gpu": {"sent": batch * rec_b, "received": batch * rec_b * (world - 1)},
+        "cpu_baseline": None, "e2e": None,
+        "gpu_launches": launches, "clocks": clock_info,
+        "slice_tokens_per_gpu": width, "all_ranks_agree": True,
     }
     print(json.dumps(line), flush=True)
     if dist is not None:
@@ -355,9 +588,12 @@ def main():
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--batch", type=int, default=256)
-    ap.add_argument("--vocab", type=int, default=248_320)
-    ap.add_argument("--history", type=int, default=32_768)
+    ap.add_argument("--config", type=int, choices=[2, 3, 4, 5], default=3)
+    ap.add_argument("--batch", type=int, default=None, help="rows (config 4: in total over all GPUs)")
+    ap.add_argument("--vocab", type=int, default=None)
+    ap.add_argument("--history", type=int, default=None, help="history length (config 3)")
+    ap.add_argument("--sets", type=int, default=None,
+                    help="rotating input sets held on the device (profiler runs: 2)")
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--cpu-rows", type=int, default=64)
     ap.add_argument("--no-cpu", action="store_true")

@@ -16,6 +16,15 @@ HS_MAX_LOGPROBS = 20
 HS_DTYPE_F32, HS_DTYPE_BF16 = 0, 1
 HS_ROW_PLAIN_GREEDY = 1
 HS_SAMPLE_APPEND_TOKEN = 1
+HS_SAMPLE_GENERAL_KERNEL = 2
+HS_CREATE_FORCE_GENERAL = 1
+HS_CREATE_PHASE_CLOCKS = 2
+
+
+def HS_CREATE_CLUSTER(n: int) -> int:
+    return (int(n) & 0xF) << 8
+
+
 HS_NOALLOC_MAX_BATCH = 1024
 
 # Mirrors of struct hs_row_params / hs_row_out (natural C alignment, no padding needed).
@@ -43,6 +52,7 @@ EXPORTS = {
     "hs_status_string": (C.c_char_p, [C.c_int]),
     "hs_last_error": (C.c_char_p, [C.c_void_p]),
     "hs_create": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
+    "hs_create_ex": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint32, C.POINTER(C.c_void_p)]),
     "hs_destroy": (C.c_int, [C.c_void_p]),
     "hs_slots_reset": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "hs_slots_append": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
@@ -50,6 +60,8 @@ EXPORTS = {
     "hs_slot_unique_count": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_int)]),
     "hs_sample": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_void_p,
                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "hs_sample_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_void_p,
+                               C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "hs_greedy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_void_p,
                             C.c_void_p]),
     "hs_greedy_noalloc": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
@@ -62,6 +74,7 @@ EXPORTS = {
                                    C.c_void_p, C.c_void_p, C.c_void_p]),
     "hs_query": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int]),
     "hs_debug_phase_clocks": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "hs_debug_set": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
 }
 
 _lib = None

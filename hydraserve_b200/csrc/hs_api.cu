@@ -25,7 +25,8 @@ namespace {
 using hs::u64;
 
 constexpr int kGreedyMaxChunks = 64;
-constexpr int kMaxSplit = 4;  // CTAs per row of the candidate kernel
+constexpr int kMaxSplit = 4;  // CTAs per row on the candidate path
+constexpr int kSideCapMax = 16384;  // side-list entries a CTA can keep in global scratch
 
 struct DeviceGuard {
   int prev = -1;
@@ -65,16 +66,16 @@ struct hs_sampler {
   int smem_optin = 0;
   int force_cluster = 0;
   int force_general = 0;  // route bf16 rows through the general (fp32-stage) kernel too
-  int2* side_pair = nullptr;  // [batch_max, side_cap] side lists of the bf16 kernel
-  hs::ClassPacked* clist = nullptr;
-  unsigned char* needs_count = nullptr;  // [batch_max]
+  int force_split = 0;    // CTAs per candidate row (0 = chosen per call)
+  int resident_bf16 = 0;  // CTAs of the bf16 kernel that can be resident at once: CTAs per SM x SMs
+  int2* side_pair = nullptr;  // [resident_bf16, side_cap] side lists too long for shared memory
+  hs::ClassPacked* clist = nullptr;  // [resident_bf16, kCells] class list of the row a CTA works on
+  int* scratch_busy = nullptr;  // [resident_bf16] which of those scratch sets are in use
   unsigned long long* split_lists = nullptr;  // [batch_max, kMaxSplit, kSplitCap]
   int* split_n = nullptr;
   int* split_ticket = nullptr;
-  cudaStream_t aux_stream = nullptr;  // the candidate kernel runs here, next to the counting kernel
-  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;  // [batch_max, kCells] class lists of the bf16 kernel
   int side_cap = 0;
-  unsigned long long* phase_clocks = nullptr;  // HS_PHASE_CLOCKS=1: per-row phase timestamps
+  unsigned long long* phase_clocks = nullptr;  // HS_CREATE_PHASE_CLOCKS: per-row phase timestamps
   hs::Pool pool{};
   u64* greedy_partials = nullptr;
   float* gstage = nullptr;  // global stand-in for the on-chip row copy (very wide rows only)
@@ -90,22 +91,28 @@ struct hs_sampler {
   int32_t* d_slots = nullptr;
   hs_row_params* h_params = nullptr;  // pinned
   int32_t* h_small = nullptr;         // pinned: offsets[batch_max+1] then slots[batch_max]
-  std::mutex mu;
-  std::string err;
+  std::mutex mu;         // the staging buffers of hs_sample_host
+  // Every launching call takes launch_mu, and work of one call is ordered after the previous
+  // call's on the GPU (an event when the stream changed), because all calls share the
+  // sampler's scratch memory and its histograms.
+  std::mutex launch_mu;
+  cudaEvent_t ev_done = nullptr;
+  cudaStream_t last_stream = nullptr;
+  bool have_last = false;
+  size_t device_bytes = 0;
   unsigned long long launches = 0;
 };
 
 namespace {
 
-int fail(hs_sampler* h, int code, const char* what, cudaError_t e = cudaSuccess) {
-  if (h) {
-    char buf[512];
-    if (e != cudaSuccess)
-      std::snprintf(buf, sizeof buf, "%s: %s", what, cudaGetErrorString(e));
-    else
-      std::snprintf(buf, sizeof buf, "%s", what);
-    h->err = buf;
-  }
+// The text of the calling thread's last failure (calls may come from several threads).
+thread_local char g_last_error[512] = "";
+
+int fail(hs_sampler*, int code, const char* what, cudaError_t e = cudaSuccess) {
+  if (e != cudaSuccess)
+    std::snprintf(g_last_error, sizeof g_last_error, "%s: %s", what, cudaGetErrorString(e));
+  else
+    std::snprintf(g_last_error, sizeof g_last_error, "%s", what);
   return code;
 }
 
@@ -114,6 +121,32 @@ int fail(hs_sampler* h, int code, const char* what, cudaError_t e = cudaSuccess)
     cudaError_t e_ = (call);                                          \
     if (e_ != cudaSuccess) return fail((h), HS_ERR_CUDA, #call, e_);  \
   } while (0)
+
+// Holds the sampler for one call's launches: calls on one sampler are serialised on the host
+// (the mutex) and on the GPU (a call on another stream than the previous one first waits for
+// that one's work), so they may come from any thread on any stream.
+struct Serial {
+  hs_sampler* h;
+  cudaStream_t stream;
+  std::unique_lock<std::mutex> lock;
+  cudaError_t status = cudaSuccess;
+  Serial(hs_sampler* h_, cudaStream_t s) : h(h_), stream(s), lock(h_->launch_mu) {
+    if (h->have_last && h->last_stream != stream) status = cudaStreamWaitEvent(stream, h->ev_done, 0);
+  }
+  // records the end of this call's work; call once, after the last launch
+  cudaError_t done() {
+    const cudaError_t e = cudaEventRecord(h->ev_done, stream);
+    if (e == cudaSuccess) { h->last_stream = stream; h->have_last = true; }
+    return e;
+  }
+};
+
+template <class T>
+bool dmalloc(hs_sampler* h, T** p, size_t bytes) {
+  if (cudaMalloc(reinterpret_cast<void**>(p), bytes ? bytes : 1) != cudaSuccess) return false;
+  h->device_bytes += bytes;
+  return true;
+}
 
 bool make_plan(const hs_sampler* h, int vocab, Plan& p) {
   static const int sizes[4] = {1, 2, 4, 8};
@@ -146,38 +179,24 @@ int check_common(hs_sampler* h, const void* logits, int dtype, int batch, int vo
 
 int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch, int vocab,
                 const hs_row_params* params, hs_row_out* out, const float* noise, float* scores_out,
-                uint32_t flags, cudaStream_t stream) {
+                int32_t* tokens_out, uint32_t flags, cudaStream_t stream) {
   Plan plan;
-  if (dtype == HS_DTYPE_BF16 && !h->force_general) {
-    // counting rows: one CTA per row and per SM; candidate rows: 1-4 CTAs per row, two per SM
-    hs::RowKernelArgs a{};
-    a.logits = logits; a.dtype = dtype; a.row_stride = row_stride; a.vocab = vocab; a.slice = 0;
-    a.params = params; a.out = out; a.noise = noise; a.scores_out = scores_out; a.gstage = nullptr;
-    a.pool = h->pool; a.flags = flags;
-    // small batches: several CTAs stream each row so that every SM has work
-    int split = (2 * h->sm_count + batch - 1) / batch;
+  hs::RowKernelArgs a{};
+  a.logits = logits; a.dtype = dtype; a.row_stride = row_stride; a.vocab = vocab; a.slice = 0;
+  a.params = params; a.out = out; a.noise = noise; a.scores_out = scores_out; a.gstage = nullptr;
+  a.pool = h->pool; a.flags = flags & HS_SAMPLE_APPEND_TOKEN; a.tokens_out = tokens_out;
+  if (dtype == HS_DTYPE_BF16 && !h->force_general && !(flags & HS_SAMPLE_GENERAL_KERNEL)) {
+    // One launch: a CTA per counting row and per part of a candidate row, two resident per
+    // SM.  Small batches: several CTAs stream each candidate row so that every SM has work.
+    int split = h->force_split ? h->force_split : (h->resident_bf16 + batch - 1) / batch;
     split = std::max(1, std::min(split, kMaxSplit));
     if (vocab < split * 2 * hs::kSample) split = 1;
-    hs::RowV3Args a3{a, h->clist, h->side_pair, h->side_cap, h->phase_clocks, h->needs_count,
-                     split, h->split_lists, h->split_n, h->split_ticket, 0, batch};
-    // The kernels serve disjoint rows and run side by side.  The counting kernel goes first:
-    // its rows are the long ones and take an SM each, while the candidate kernel (on an
-    // auxiliary stream forked from the caller's) fills the SMs that are left and those that
-    // free up.  The second counting pass for a row whose candidate list overflowed (rare;
-    // otherwise an empty launch) follows the candidate kernel on its stream.
-    HS_CUDA(h, cudaEventRecord(h->ev_fork, stream));
-    HS_CUDA(h, cudaStreamWaitEvent(h->aux_stream, h->ev_fork, 0));
-    a3.pass = 0;
-    hs::row_kernel_v3<<<(unsigned)batch, hs::kThreads, hs::layout_v3().total, stream>>>(a3);
+    hs::RowV3Args a3{a, h->clist, h->side_pair, h->side_cap, h->resident_bf16, h->scratch_busy, h->phase_clocks,
+                     split, h->split_lists, h->split_n, h->split_ticket, batch};
+    const unsigned grid = (unsigned)batch * (unsigned)(1 + split);
+    hs::row_kernel_bf16<<<grid, hs::kThreads, hs::bf16_kernel_smem(), stream>>>(a3);
     HS_CUDA(h, cudaGetLastError());
-    hs::row_kernel_topk<<<dim3((unsigned)split, (unsigned)batch), hs::kThreads, hs::layout_cand().total, h->aux_stream>>>(a3);
-    HS_CUDA(h, cudaGetLastError());
-    a3.pass = 1;
-    hs::row_kernel_v3<<<(unsigned)batch, hs::kThreads, hs::layout_v3().total, h->aux_stream>>>(a3);
-    HS_CUDA(h, cudaGetLastError());
-    HS_CUDA(h, cudaEventRecord(h->ev_join, h->aux_stream));
-    HS_CUDA(h, cudaStreamWaitEvent(stream, h->ev_join, 0));
-    h->launches += 3;
+    h->launches += 1;
     return HS_OK;
   }
   if (!make_plan(h, vocab, plan)) return fail(h, HS_ERR_CAPACITY, "vocabulary too wide for the row kernel");
@@ -185,19 +204,8 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
     const size_t need = (size_t)batch * plan.slice * plan.cluster;
     if (need > h->gstage_elems) return fail(h, HS_ERR_CAPACITY, "global stage too small for this batch x vocab");
   }
-  hs::RowKernelArgs a{};
-  a.logits = logits;
-  a.dtype = dtype;
-  a.row_stride = row_stride;
-  a.vocab = vocab;
   a.slice = plan.slice;
-  a.params = params;
-  a.out = out;
-  a.noise = noise;
-  a.scores_out = scores_out;
   a.gstage = plan.global_stage ? h->gstage : nullptr;
-  a.pool = h->pool;
-  a.flags = flags;
 
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)plan.cluster, (unsigned)batch, 1);
@@ -249,11 +257,10 @@ int launch_append(hs_sampler* h, const int32_t* tokens, const int32_t* offsets, 
 
 void release(hs_sampler* h) {
   cudaFree(h->pool.pairs); cudaFree(h->pool.cls); cudaFree(h->pool.heavy); cudaFree(h->pool.n_heavy); cudaFree(h->pool.n); cudaFree(h->pool.pos);
-  cudaFree(h->side_pair); cudaFree(h->clist); cudaFree(h->needs_count);
+  cudaFree(h->side_pair); cudaFree(h->clist); cudaFree(h->scratch_busy);
   cudaFree(h->split_lists); cudaFree(h->split_n); cudaFree(h->split_ticket);
-  if (h->aux_stream) cudaStreamDestroy(h->aux_stream);
-  if (h->ev_fork) cudaEventDestroy(h->ev_fork);
-  if (h->ev_join) cudaEventDestroy(h->ev_join); cudaFree(h->phase_clocks);
+  if (h->ev_done) cudaEventDestroy(h->ev_done);
+  cudaFree(h->phase_clocks);
   cudaFree(h->pool.error); cudaFree(h->greedy_partials); cudaFree(h->gstage); cudaFree(h->d_logits);
   cudaFree(h->d_params); cudaFree(h->d_out); cudaFree(h->d_hist); cudaFree(h->d_offsets); cudaFree(h->d_slots);
   if (h->h_params) cudaFreeHost(h->h_params);
@@ -356,12 +363,17 @@ const char* hs_status_string(int status) {
   }
 }
 
-const char* hs_last_error(hs_sampler* h) { return h ? h->err.c_str() : "null sampler"; }
+const char* hs_last_error(hs_sampler* h) { return h ? g_last_error : "null sampler"; }
 
 int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batch_max, hs_sampler** out) {
+  return hs_create_ex(device, vocab_max, slots_max, unique_cap, batch_max, 0u, out);
+}
+
+int hs_create_ex(int device, int vocab_max, int slots_max, int hist_cap, int batch_max, uint32_t flags,
+                 hs_sampler** out) {
   if (!out) return HS_ERR_INVALID;
   *out = nullptr;
-  if (vocab_max < 1 || slots_max < 0 || batch_max < 1 || unique_cap < 0) return HS_ERR_INVALID;
+  if (vocab_max < 1 || slots_max < 0 || batch_max < 1 || hist_cap < 0) return HS_ERR_INVALID;
   if (batch_max > 65535) return HS_ERR_CAPACITY;
   hs_sampler* h = new (std::nothrow) hs_sampler();
   if (!h) return HS_ERR_INVALID;
@@ -371,21 +383,27 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   h->vocab_max = vocab_max;
   h->slots_user = slots_max;
   h->slots_total = slots_max + batch_max;  // the tail serves per-call (stateless) histories
-  h->unique_cap = unique_cap == 0 ? vocab_max : std::min(unique_cap, vocab_max);
+  h->unique_cap = hist_cap == 0 ? vocab_max : std::min(hist_cap, vocab_max);
   h->batch_max = batch_max;
-  if (const char* fc = std::getenv("HS_FORCE_CLUSTER")) {
-    const int v = std::atoi(fc);
+  h->force_general = (flags & HS_CREATE_FORCE_GENERAL) ? 1 : 0;
+  {
+    const int v = (int)((flags >> 8) & 0xfu);
     if (v == 1 || v == 2 || v == 4 || v == 8) h->force_cluster = v;
   }
   auto bail = [&](int code) { release(h); delete h; return code; };
   if (cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaDeviceGetAttribute(&h->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_optin) != cudaSuccess) return bail(HS_ERR_CUDA);
-  if (cudaFuncSetAttribute(hs::row_kernel_v3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_v3().total) != cudaSuccess) return bail(HS_ERR_CUDA);
-  if (cudaFuncSetAttribute(hs::row_kernel_topk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_cand().total) != cudaSuccess) return bail(HS_ERR_CUDA);
+  if (cudaFuncSetAttribute(hs::row_kernel_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::bf16_kernel_smem()) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::shard_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_cand().total) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::shard_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_cand().total) != cudaSuccess) return bail(HS_ERR_CUDA);
-  if (const char* fg = std::getenv("HS_FORCE_GENERAL")) h->force_general = std::atoi(fg) != 0;
+  {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, hs::row_kernel_bf16, hs::kThreads,
+                                                      hs::bf16_kernel_smem()) != cudaSuccess || per_sm < 1)
+      return bail(HS_ERR_CUDA);
+    h->resident_bf16 = per_sm * h->sm_count;
+  }
 
   const size_t st = (size_t)h->slots_total;
   h->pool.slots_total = h->slots_total;
@@ -393,40 +411,37 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   h->pool.pos_stride = vocab_max;
   h->pool.cls_stride = (vocab_max + 15) / 16 + 4;  // words; padded so 128-bit reads of the tail stay inside
   bool ok = true;
-  ok = ok && cudaMalloc(&h->pool.pairs, st * h->unique_cap * sizeof(int2)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->pool.n, st * sizeof(int32_t)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->pool.n_heavy, st * sizeof(int32_t)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->pool.heavy, st * h->unique_cap * sizeof(int32_t)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->pool.cls, st * (size_t)h->pool.cls_stride * sizeof(uint32_t)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->pool.pos, st * (size_t)vocab_max * sizeof(int32_t)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->pool.error, sizeof(int32_t)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->greedy_partials, (size_t)batch_max * kGreedyMaxChunks * sizeof(u64)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->d_params, (size_t)batch_max * sizeof(hs_row_params)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->d_out, (size_t)batch_max * sizeof(hs_row_out)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->d_offsets, ((size_t)batch_max + 1) * sizeof(int32_t)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->d_slots, (size_t)batch_max * sizeof(int32_t)) == cudaSuccess;
-  h->side_cap = (vocab_max + 7) & ~7;
-  ok = ok && cudaMalloc(&h->side_pair, (size_t)batch_max * h->side_cap * sizeof(int2)) == cudaSuccess;
-  ok = ok && cudaStreamCreateWithFlags(&h->aux_stream, cudaStreamNonBlocking) == cudaSuccess;
-  ok = ok && cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming) == cudaSuccess;
-  ok = ok && cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->needs_count, (size_t)batch_max) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->split_lists, (size_t)batch_max * kMaxSplit * hs::kSplitCap * sizeof(unsigned long long)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->split_n, (size_t)batch_max * kMaxSplit * sizeof(int)) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->split_ticket, (size_t)batch_max * sizeof(int)) == cudaSuccess;
-  ok = ok && cudaMemset(h->split_ticket, 0, (size_t)batch_max * sizeof(int)) == cudaSuccess;
-  ok = ok && cudaMemset(h->needs_count, 0, (size_t)batch_max) == cudaSuccess;
-  ok = ok && cudaMalloc(&h->clist, (size_t)batch_max * (hs::kCells - hs::kV3SharedClasses) * sizeof(hs::ClassPacked)) == cudaSuccess;
+  ok = ok && dmalloc(h, &h->pool.pairs, st * h->unique_cap * sizeof(int2));
+  ok = ok && dmalloc(h, &h->pool.n, st * sizeof(int32_t));
+  ok = ok && dmalloc(h, &h->pool.n_heavy, st * sizeof(int32_t));
+  ok = ok && dmalloc(h, &h->pool.heavy, st * h->unique_cap * sizeof(int32_t));
+  ok = ok && dmalloc(h, &h->pool.cls, st * (size_t)h->pool.cls_stride * sizeof(uint32_t));
+  ok = ok && dmalloc(h, &h->pool.pos, st * (size_t)vocab_max * sizeof(int32_t));
+  ok = ok && dmalloc(h, &h->pool.error, sizeof(int32_t));
+  ok = ok && dmalloc(h, &h->greedy_partials, (size_t)batch_max * kGreedyMaxChunks * sizeof(u64));
+  ok = ok && dmalloc(h, &h->d_params, (size_t)batch_max * sizeof(hs_row_params));
+  ok = ok && dmalloc(h, &h->d_out, (size_t)batch_max * sizeof(hs_row_out));
+  ok = ok && dmalloc(h, &h->d_offsets, ((size_t)batch_max + 1) * sizeof(int32_t));
+  ok = ok && dmalloc(h, &h->d_slots, (size_t)batch_max * sizeof(int32_t));
+  // scratch of the bf16 kernel, per resident CTA (not per row of the batch)
+  h->side_cap = std::min((vocab_max + 7) & ~7, kSideCapMax);
+  ok = ok && dmalloc(h, &h->side_pair, (size_t)h->resident_bf16 * h->side_cap * sizeof(int2));
+  ok = ok && dmalloc(h, &h->clist, (size_t)h->resident_bf16 * hs::kCells * sizeof(hs::ClassPacked));
+  ok = ok && dmalloc(h, &h->scratch_busy, (size_t)h->resident_bf16 * sizeof(int));
+  ok = ok && cudaEventCreateWithFlags(&h->ev_done, cudaEventDisableTiming) == cudaSuccess;
+  ok = ok && dmalloc(h, &h->split_lists, (size_t)batch_max * kMaxSplit * hs::kSplitCap * sizeof(unsigned long long));
+  ok = ok && dmalloc(h, &h->split_n, (size_t)batch_max * kMaxSplit * sizeof(int));
+  ok = ok && dmalloc(h, &h->split_ticket, (size_t)batch_max * sizeof(int));
   ok = ok && cudaMallocHost(&h->h_params, (size_t)batch_max * sizeof(hs_row_params)) == cudaSuccess;
   ok = ok && cudaMallocHost(&h->h_small, (2 * (size_t)batch_max + 1) * sizeof(int32_t)) == cudaSuccess;
-  if (const char* pc = std::getenv("HS_PHASE_CLOCKS")) {
-    if (std::atoi(pc) != 0) {
-      const size_t bytes = (size_t)batch_max * hs::kV3PhaseSlots * sizeof(unsigned long long);
-      ok = ok && cudaMalloc(&h->phase_clocks, bytes) == cudaSuccess;
-      ok = ok && cudaMemset(h->phase_clocks, 0, bytes) == cudaSuccess;
-    }
+  if (flags & HS_CREATE_PHASE_CLOCKS) {
+    const size_t bytes = (size_t)batch_max * hs::kV3PhaseSlots * sizeof(unsigned long long);
+    ok = ok && dmalloc(h, &h->phase_clocks, bytes);
+    ok = ok && cudaMemset(h->phase_clocks, 0, bytes) == cudaSuccess;
   }
   if (!ok) return bail(HS_ERR_CUDA);
+  ok = ok && cudaMemset(h->split_ticket, 0, (size_t)batch_max * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMemset(h->scratch_busy, 0, (size_t)h->resident_bf16 * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMemset(h->pool.n, 0, st * sizeof(int32_t)) == cudaSuccess;
   ok = ok && cudaMemset(h->pool.n_heavy, 0, st * sizeof(int32_t)) == cudaSuccess;
   ok = ok && cudaMemset(h->pool.cls, 0, st * (size_t)h->pool.cls_stride * sizeof(uint32_t)) == cudaSuccess;
@@ -437,7 +452,7 @@ int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batc
   if (!make_plan(h, vocab_max, plan)) return bail(HS_ERR_CAPACITY);
   if (plan.global_stage) {
     h->gstage_elems = (size_t)batch_max * plan.slice * plan.cluster;
-    if (cudaMalloc(&h->gstage, h->gstage_elems * sizeof(float)) != cudaSuccess) return bail(HS_ERR_CUDA);
+    if (!dmalloc(h, &h->gstage, h->gstage_elems * sizeof(float))) return bail(HS_ERR_CUDA);
   }
   if (cudaDeviceSynchronize() != cudaSuccess) return bail(HS_ERR_CUDA);
   *out = h;
@@ -459,9 +474,12 @@ int hs_slots_reset(hs_sampler* h, const int32_t* slots, int n_slots, void* strea
   if (!h || n_slots < 0 || (!slots && n_slots)) return HS_ERR_INVALID;
   if (n_slots == 0) return HS_OK;
   DeviceGuard guard(h->device);
+  Serial serial(h, (cudaStream_t)stream);
+  HS_CUDA(h, serial.status);
   hs::slots_reset_kernel<<<n_slots, 256, 0, (cudaStream_t)stream>>>(h->pool, slots, n_slots);
   HS_CUDA(h, cudaGetLastError());
   h->launches += 1;
+  HS_CUDA(h, serial.done());
   return HS_OK;
 }
 
@@ -471,12 +489,19 @@ int hs_slots_append(hs_sampler* h, const int32_t* tokens, const int32_t* offsets
   if (vocab < 1 || vocab > h->vocab_max) return fail(h, HS_ERR_CAPACITY, "vocab exceeds vocab_max");
   if (n_slots > 65535) return fail(h, HS_ERR_CAPACITY, "too many slots in one call");
   DeviceGuard guard(h->device);
-  return launch_append(h, tokens, offsets, slots, n_slots, vocab, max_tokens_per_slot, (cudaStream_t)stream);
+  Serial serial(h, (cudaStream_t)stream);
+  HS_CUDA(h, serial.status);
+  const int rc = launch_append(h, tokens, offsets, slots, n_slots, vocab, max_tokens_per_slot, (cudaStream_t)stream);
+  if (rc != HS_OK) return rc;
+  HS_CUDA(h, serial.done());
+  return HS_OK;
 }
 
 int hs_slot_unique_count(hs_sampler* h, int slot, void* stream, int* out) {
   if (!h || !out || slot < 0 || slot >= h->slots_total) return HS_ERR_INVALID;
   DeviceGuard guard(h->device);
+  Serial serial(h, (cudaStream_t)stream);
+  HS_CUDA(h, serial.status);
   int32_t v = 0;
   HS_CUDA(h, cudaMemcpyAsync(&v, h->pool.n + slot, sizeof v, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
   HS_CUDA(h, cudaStreamSynchronize((cudaStream_t)stream));
@@ -487,14 +512,26 @@ int hs_slot_unique_count(hs_sampler* h, int slot, void* stream, int* out) {
 int hs_sample(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch, int vocab,
               const hs_row_params* params, hs_row_out* out, const float* noise, float* scores_out,
               uint32_t flags, void* stream) {
+  return hs_sample_ex(h, logits, dtype, row_stride, batch, vocab, params, out, noise, scores_out, nullptr,
+                      flags, stream);
+}
+
+int hs_sample_ex(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch, int vocab,
+                 const hs_row_params* params, hs_row_out* out, const float* noise, float* scores_out,
+                 int32_t* tokens_out, uint32_t flags, void* stream) {
   int rc = check_common(h, logits, dtype, batch, vocab);
   if (rc != HS_OK) return rc;
   if (batch == 0) return HS_OK;
   if (!params || !out) return fail(h, HS_ERR_INVALID, "params / out is null");
   if (row_stride < vocab) return fail(h, HS_ERR_INVALID, "row_stride smaller than vocab");
   DeviceGuard guard(h->device);
-  return launch_rows(h, logits, dtype, row_stride, batch, vocab, params, out, noise, scores_out, flags,
-                     (cudaStream_t)stream);
+  Serial serial(h, (cudaStream_t)stream);
+  HS_CUDA(h, serial.status);
+  rc = launch_rows(h, logits, dtype, row_stride, batch, vocab, params, out, noise, scores_out, tokens_out,
+                   flags, (cudaStream_t)stream);
+  if (rc != HS_OK) return rc;
+  HS_CUDA(h, serial.done());
+  return HS_OK;
 }
 
 int hs_greedy(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch, int vocab,
@@ -505,7 +542,12 @@ int hs_greedy(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, 
   if (!tokens_out) return fail(h, HS_ERR_INVALID, "tokens_out is null");
   if (row_stride < vocab) return fail(h, HS_ERR_INVALID, "row_stride smaller than vocab");
   DeviceGuard guard(h->device);
-  return launch_greedy(h, logits, dtype, row_stride, batch, vocab, tokens_out, (cudaStream_t)stream);
+  Serial serial(h, (cudaStream_t)stream);
+  HS_CUDA(h, serial.status);
+  rc = launch_greedy(h, logits, dtype, row_stride, batch, vocab, tokens_out, (cudaStream_t)stream);
+  if (rc != HS_OK) return rc;
+  HS_CUDA(h, serial.done());
+  return HS_OK;
 }
 
 int hs_sample_host(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch, int vocab,
@@ -519,6 +561,8 @@ int hs_sample_host(hs_sampler* h, const void* logits, int dtype, int64_t row_str
   cudaStream_t stream = (cudaStream_t)stream_;
   std::lock_guard<std::mutex> lock(h->mu);  // one user of the staging buffers at a time
   DeviceGuard guard(h->device);
+  Serial serial(h, stream);
+  HS_CUDA(h, serial.status);
 
   const size_t esz = dtype == HS_DTYPE_BF16 ? 2 : 4;
   const size_t need = (size_t)batch * vocab * esz;
@@ -589,9 +633,10 @@ int hs_sample_host(hs_sampler* h, const void* logits, int dtype, int64_t row_str
     if (rc != HS_OK) return rc;
   }
   HS_CUDA(h, cudaMemcpyAsync(h->d_params, h->h_params, (size_t)batch * sizeof(hs_row_params), cudaMemcpyHostToDevice, stream));
-  rc = launch_rows(h, h->d_logits, dtype, vocab, batch, vocab, h->d_params, h->d_out, nullptr, nullptr, flags, stream);
+  rc = launch_rows(h, h->d_logits, dtype, vocab, batch, vocab, h->d_params, h->d_out, nullptr, nullptr, nullptr, flags, stream);
   if (rc != HS_OK) return rc;
   HS_CUDA(h, cudaMemcpyAsync(out, h->d_out, (size_t)batch * sizeof(hs_row_out), cudaMemcpyDeviceToHost, stream));
+  HS_CUDA(h, serial.done());
   HS_CUDA(h, cudaStreamSynchronize(stream));
   return HS_OK;
 }
@@ -611,9 +656,12 @@ int hs_sharded_partial(hs_sampler* h, const void* logits, int dtype, int64_t row
   a.base.params = params; a.base.pool = h->pool;
   a.vocab_offset = vocab_offset;
   a.recs = recs_out;
+  Serial serial(h, (cudaStream_t)stream);
+  HS_CUDA(h, serial.status);
   hs::shard_partial_kernel<<<(unsigned)batch, hs::kThreads, hs::layout_cand().total, (cudaStream_t)stream>>>(a);
   HS_CUDA(h, cudaGetLastError());
   h->launches += 1;
+  HS_CUDA(h, serial.done());
   return HS_OK;
 }
 
@@ -627,19 +675,33 @@ int hs_sharded_merge(hs_sampler* h, const hs_shard_rec* recs, int ranks, int bat
   if (!recs || !params || !out) return fail(h, HS_ERR_INVALID, "recs / params / out is null");
   DeviceGuard guard(h->device);
   hs::MergeArgs a{recs, ranks, batch, vocab_total, params, out, noise, full_lse};
+  Serial serial(h, (cudaStream_t)stream);
+  HS_CUDA(h, serial.status);
   hs::shard_merge_kernel<<<(unsigned)batch, hs::kThreads, hs::layout_cand().total, (cudaStream_t)stream>>>(a);
   HS_CUDA(h, cudaGetLastError());
   h->launches += 1;
+  HS_CUDA(h, serial.done());
   return HS_OK;
 }
 
 int hs_debug_phase_clocks(hs_sampler* h, int batch, unsigned long long* out_host) {
   if (!h || !out_host || batch < 0 || batch > h->batch_max) return HS_ERR_INVALID;
-  if (!h->phase_clocks) return fail(h, HS_ERR_UNSUPPORTED, "create the sampler with HS_PHASE_CLOCKS=1");
+  if (!h->phase_clocks) return fail(h, HS_ERR_UNSUPPORTED, "create the sampler with HS_CREATE_PHASE_CLOCKS");
   DeviceGuard guard(h->device);
   HS_CUDA(h, cudaMemcpy(out_host, h->phase_clocks, (size_t)batch * hs::kV3PhaseSlots * sizeof(unsigned long long),
                         cudaMemcpyDeviceToHost));
   return HS_OK;
+}
+
+int hs_debug_set(hs_sampler* h, int what, int value) {
+  if (!h) return HS_ERR_INVALID;
+  std::lock_guard<std::mutex> lock(h->launch_mu);
+  if (what == 0) {
+    if (value != 0 && value != 1 && value != 2 && value != 4) return fail(h, HS_ERR_INVALID, "split must be 0, 1, 2 or 4");
+    h->force_split = value;
+    return HS_OK;
+  }
+  return fail(h, HS_ERR_INVALID, "unknown setting");
 }
 
 int hs_query(hs_sampler* h, int what, int vocab, int dtype) {
@@ -652,6 +714,14 @@ int hs_query(hs_sampler* h, int what, int vocab, int dtype) {
     case 4: return v3 ? 1 : 0;
     case 2: return h->sm_count;
     case 3: return (int)(h->launches & 0x7fffffffull);
+    case 5: return (int)std::min<size_t>(h->device_bytes >> 10, 0x7fffffffu);
+    case 6: {
+      const size_t per_slot = (size_t)h->unique_cap * (sizeof(int2) + sizeof(int32_t)) +
+                              (size_t)h->pool.cls_stride * sizeof(uint32_t) + (size_t)h->vocab_max * sizeof(int32_t) +
+                              2 * sizeof(int32_t);
+      return (int)std::min<size_t>(per_slot, 0x7fffffffu);
+    }
+    case 7: return h->resident_bf16;
     default: return HS_ERR_INVALID;
   }
 }

@@ -1,5 +1,9 @@
-// The bf16 row kernel: dispatches each row to the candidate path (small top_k), the
-// plain arg-max path, or the counting path (hs_row_v3.cuh).
+// The bf16 row kernel: one launch per step, one CTA per work item, two CTAs resident per SM.
+// An item is a row for the counting path (hs_row_v3.cuh; also the plain arg-max rows of a
+// mixed batch) or one part of a row for the candidate path (small top_k, hs_row_topk.cuh);
+// the hardware hands the items out in grid order as SMs free up, the long ones first.  No CTA
+// waits for another: the last part of a candidate row to arrive finishes that row, and a row
+// whose candidate list overflowed is counted by the CTA that found out.
 #pragma once
 #include <type_traits>
 
@@ -29,23 +33,24 @@ __device__ __noinline__ void count_chunk_slow(uint32_t* tab, int* rare_n, int2* 
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args args) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+// The counting path for one row (also: plain arg max of a row in a mixed batch).
+__device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* smem_raw, int row_index) {
   const RowKernelArgs& a = args.base;
   const LayoutV3 lay = layout_v3();
   Ctx3 c;
   c.x = reinterpret_cast<Exchange*>(smem_raw + lay.x);
   c.tab = reinterpret_cast<uint32_t*>(smem_raw + lay.tab);
-  c.hist = reinterpret_cast<LocalHist*>(smem_raw + lay.hist);
+  c.hist = reinterpret_cast<LocalHist*>(smem_raw + lay.hist);   // in the count table's place, once it has served
   c.gbuf = reinterpret_cast<V3Entry*>(smem_raw + lay.gbuf);
   c.list = reinterpret_cast<V3Entry*>(smem_raw + lay.list);
+  int2* side_shared = reinterpret_cast<int2*>(smem_raw + lay.side);
   int2* rare = reinterpret_cast<int2*>(smem_raw + lay.rare);  // (id, raw bits | count class << 16)
   int* small = reinterpret_cast<int*>(smem_raw + lay.small);
   c.gbuf_n = small;
   int* rare_n = small + 1;
   int* side_n = small + 2;
   const int tid = threadIdx.x;
-  c.row = blockIdx.x;
+  c.row = row_index;
   c.vocab = a.vocab;
   c.logits = reinterpret_cast<const unsigned short*>(a.logits) + (long long)c.row * a.row_stride;
   c.vec = (reinterpret_cast<uintptr_t>(c.logits) & 15u) == 0;
@@ -58,14 +63,14 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
   c.fp = P.frequency_penalty;
   c.pool = a.pool;
   c.slot = P.slot;
-  const bool penalised = P.slot >= 0 && (P.repetition_penalty != 1.0f || P.presence_penalty != 0.0f ||
-                                          P.frequency_penalty != 0.0f);
+  const bool slot_ok = P.slot >= 0 && P.slot < a.pool.slots_total;
+  const bool penalised = slot_ok && (P.repetition_penalty != 1.0f || P.presence_penalty != 0.0f ||
+                                     P.frequency_penalty != 0.0f);
   c.cls = penalised ? a.pool.cls + (size_t)P.slot * a.pool.cls_stride : nullptr;
-  c.s_pair = args.s_pair + (size_t)c.row * args.s_cap;
-  c.s_cap = args.s_cap;
+  c.s_pair = nullptr;
+  c.s_cap = 0;
   c.n_s = 0;
-  c.scl = reinterpret_cast<ClassPacked*>(smem_raw + lay.scl);
-  c.cl = args.clist + (size_t)c.row * (kCells - kV3SharedClasses);
+  c.cl = nullptr;
   c.n_cl = 0;
   c.m = 0.f;
   unsigned long long* clocks = args.phase_clocks ? args.phase_clocks + (size_t)c.row * kV3PhaseSlots : nullptr;
@@ -73,14 +78,8 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
   auto mark = [&](int slot) {
     if (clocks && tid == 0) clocks[slot] = clock64();
   };
-  // rows with a small top_k belong to row_kernel_topk; it hands back (pass 1) the rare row
-  // whose candidate list overflowed
-  {
-    const bool small_k = !c.greedy && P.top_k > 0 && P.top_k <= kTopKMax && P.top_k < a.vocab;
-    if (args.pass == 0 ? small_k : !(small_k && args.needs_count[c.row])) return;
-  }
   mark(0);
-  int status = 0;
+  int status = P.slot >= a.pool.slots_total ? 64 : 0;  // a slot this sampler does not have: no penalties
 
   // ---- plain greedy rows of a mixed batch: arg max only -----------------------------------
   if (c.greedy && !penalised && P.n_logprobs < 0) {
@@ -104,7 +103,8 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
     }
     if (tid == 0) {
       out->token = (int)(~(uint32_t)(best & 0xffffffffu));
-      out->logprob = 0.f; out->n_top = 0; out->status = 0;
+      if (a.tokens_out) a.tokens_out[c.row] = out->token;
+      out->logprob = 0.f; out->n_top = 0; out->status = status;
       out->n_kept = a.vocab; out->n_after_topk = a.vocab; out->n_after_minp = a.vocab; out->n_after_topp = a.vocab;
       out->cut_bits = 0xff800000u; out->n_cut_ties = -1;
       out->row_max = score_of((uint32_t)(best >> 32)); out->log_z = 0.f;
@@ -139,6 +139,32 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
   }
   if (tid < 16) small[tid] = 0;
   __syncthreads();
+  // Global scratch (class list, long side lists) is held per RESIDENT CTA: a CTA claims one of
+  // the n_scratch sets (as many as CTAs can be resident, so one is always free), starting its
+  // search at the pair of its SM, and gives it back at the end.
+  if (tid == 0) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    int got = -1;
+    for (int k = 0; k < 2 * args.n_scratch && got < 0; ++k) {
+      const int at = (int)((2u * smid + (unsigned)k) % (unsigned)args.n_scratch);
+      if (atomicCAS(&args.scratch_busy[at], 0, 1) == 0) got = at;
+    }
+    small[15] = got;
+  }
+  __syncthreads();
+  const int scratch = small[15];
+  if (scratch < 0) {  // cannot happen while n_scratch covers the resident CTAs; fail the row, do not wait
+    if (tid == 0) { out->token = 0; out->status = 128; out->n_top = 0; out->n_kept = 0; }
+    return;
+  }
+  auto release_scratch = [&]() {
+    __syncthreads();
+    if (tid == 0) { __threadfence(); atomicExch(&args.scratch_busy[scratch], 0); }
+  };
+  c.s_pair = args.s_pair + (size_t)scratch * args.s_cap;
+  c.s_cap = args.s_cap;
+  c.cl = args.clist + (size_t)scratch * kCells;
 
   for (int i = tid; i < kCells; i += kThreads) c.tab[i] = 0;
   __syncthreads();
@@ -249,13 +275,11 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
   mark(1);
 
   // ---- B. the side list: tokens with history count >= 3, and values outside the bin window
-  // It is walked by every selection, so it lives in shared memory when it fits: first in the
-  // (still unused) histogram area, after the class list is built in the count table's.
+  // It is walked by every selection, so it lives in shared memory when it fits.
   u64 side_best = 0;
   const int n_rare = *rare_n;
-  const bool side_shared = n_rare <= kV3RareCap && n_heavy + kV3RareCap <= kV3SideShared;
-  if (side_shared) {
-    c.s_pair = reinterpret_cast<int2*>(c.hist);
+  if (n_rare <= kV3RareCap && n_heavy + kV3RareCap <= kV3SideShared) {
+    c.s_pair = side_shared;
     c.s_cap = kV3SideShared;
   }
   {
@@ -342,21 +366,13 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
       if (!n) continue;
       const float s = c.cell_score(cell);
       const u64 q = mass_of(s, m);
-      ClassPacked* dst = at < kV3SharedClasses ? c.scl + at : c.cl + (at - kV3SharedClasses);
-      *reinterpret_cast<uint4*>(dst) = pack_class(key_of(s), n, (uint32_t)cell, q);
+      reinterpret_cast<uint4*>(c.cl)[at] = pack_class(key_of(s), n, (uint32_t)cell, q);
       ++at;
     }
     c.n_cl = (int)tot;
     __syncthreads();
   }
-  if (side_shared) {
-    // the count table has served: the side list moves there and frees the histogram area
-    int2* moved = reinterpret_cast<int2*>(c.tab);
-    for (int j = tid; j < c.n_s; j += kThreads) moved[j] = c.s_pair[j];
-    c.s_pair = moved;
-    __syncthreads();
-  }
-  mark(3);
+  mark(3);  // (the count table has served: the selection histograms take its place)
 
   KeptSet kept{0u, 0x7fffffff};
   int token = -1;
@@ -677,19 +693,26 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel_v3(const RowV3Args arg
     out->n_cut_ties = (int32_t)cut_ties;
     out->row_max = m;
     out->log_z = log_z;
-    if ((a.flags & HS_SAMPLE_APPEND_TOKEN) && P.slot >= 0 && token >= 0 && token < a.vocab) {
+    if (a.tokens_out) a.tokens_out[c.row] = token;
+    if ((a.flags & HS_SAMPLE_APPEND_TOKEN) && slot_ok && token >= 0 && token < a.vocab) {
       if (!slot_append_one(a.pool, P.slot, token)) out->status = status | 2;
     }
   }
   (void)cut_group_cnt;
+  release_scratch();
   mark(9);
 }
 
 
-// Rows with 0 < top_k <= kTopKMax: the candidate path.  A row whose candidate list overflows
-// is flagged in needs_count and left to row_kernel_v3, which is launched next.
-__global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args args) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+// Rows with 0 < top_k <= kTopKMax take the candidate path.
+__device__ __forceinline__ bool is_candidate_row(const hs_row_params& P, int vocab) {
+  return P.temperature != 0.0f && P.top_k > 0 && P.top_k <= kTopKMax && P.top_k < vocab;
+}
+
+// One part of a candidate row (a contiguous range of its tokens).  The CTA that brings in the
+// row's last part finishes the row.  Returns true when the row's candidate list overflowed
+// and the caller (the finishing CTA) has to count the row after all.
+__device__ __forceinline__ bool cand_part(const RowV3Args& args, unsigned char* smem_raw, int row_index, int part) {
   const RowKernelArgs& a = args.base;
   const LayoutCand lay = layout_cand();
   Ctx3 c;
@@ -698,13 +721,12 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args a
   CandCtx L{reinterpret_cast<u64*>(smem_raw + lay.cand), small + 4, small + 5,
             reinterpret_cast<uint32_t*>(smem_raw + lay.count), small + 8, nullptr};
   const int tid = threadIdx.x;
-  c.row = blockIdx.y;
+  c.row = row_index;
   c.vocab = a.vocab;
   const hs_row_params P = a.params[c.row];
-  c.greedy = P.temperature == 0.0f;
-  if (c.greedy || P.top_k <= 0 || P.top_k > kTopKMax || P.top_k >= a.vocab) return;  // not this kernel's row
+  c.greedy = false;
   // the row is streamed by args.split CTAs, each taking a contiguous range of tokens
-  const int split = args.split, part = blockIdx.x;
+  const int split = args.split;
   const int width = (((a.vocab + split - 1) / split) + 7) & ~7;
   c.lo = min(part * width, a.vocab);
   c.hi = min(c.lo + width, a.vocab);
@@ -714,9 +736,10 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args a
   c.T = P.temperature; c.rp = P.repetition_penalty; c.pp = P.presence_penalty; c.fp = P.frequency_penalty;
   c.pool = a.pool;
   c.slot = P.slot;
-  const bool penalised = P.slot >= 0 && (c.rp != 1.0f || c.pp != 0.0f || c.fp != 0.0f);
+  const bool slot_ok = P.slot >= 0 && P.slot < a.pool.slots_total;
+  const bool penalised = slot_ok && (c.rp != 1.0f || c.pp != 0.0f || c.fp != 0.0f);
   c.cls = penalised ? a.pool.cls + (size_t)P.slot * a.pool.cls_stride : nullptr;
-  c.s_pair = nullptr; c.n_s = 0; c.s_cap = 0; c.scl = nullptr; c.cl = nullptr; c.n_cl = 0; c.m = 0.f;
+  c.s_pair = nullptr; c.n_s = 0; c.s_cap = 0; c.cl = nullptr; c.n_cl = 0; c.m = 0.f;
   c.tab = nullptr; c.hist = nullptr; c.gbuf = nullptr; c.list = nullptr; c.gbuf_n = nullptr;
   unsigned long long* clocks = args.phase_clocks ? args.phase_clocks + (size_t)c.row * kV3PhaseSlots : nullptr;
   auto mark = [&](int slot) {
@@ -745,7 +768,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args a
     __syncthreads();
     if (tid == 0) small[6] = atomicAdd(&args.split_ticket[c.row], 1);
     __syncthreads();
-    if (small[6] != split - 1) return;
+    if (small[6] != split - 1) return false;
     mark(12);
     __threadfence();
     if (tid == 0) args.split_ticket[c.row] = 0;
@@ -772,11 +795,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args a
       n = cand_compact(L, n, cut);
     }
   }
-  if (n < 0) {
-    if (tid == 0) args.needs_count[c.row] = 1;
-    return;
-  }
-  if (tid == 0) args.needs_count[c.row] = 0;
+  if (n < 0) return true;  // more ties than a candidate list holds: the row is counted instead
   mark(14);
   cand_sort(L, n);
   mark(15);
@@ -790,7 +809,8 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args a
   }
   mark(2);
   const float* noise_row = a.noise ? a.noise + (size_t)c.row * a.vocab : nullptr;
-  const FinishOut r = finish_sorted(*c.x, L.cand, reinterpret_cast<u64*>(smem_raw + lay.mass), n, P, noise_row, out, clocks);
+  FinishOut r = finish_sorted(*c.x, L.cand, reinterpret_cast<u64*>(smem_raw + lay.mass), n, P, noise_row, out, clocks);
+  if (P.slot >= a.pool.slots_total) r.status |= 64;  // a slot this sampler does not have: no penalties
   if (a.scores_out) {
     float* dst = a.scores_out + (size_t)c.row * a.vocab;
     for (int id = tid; id < c.vocab; id += kThreads) dst[id] = __int_as_float(0xff800000);
@@ -799,11 +819,37 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_topk(const RowV3Args a
   }
   if (tid == 0) {
     write_finish(r, out);
-    if ((a.flags & HS_SAMPLE_APPEND_TOKEN) && P.slot >= 0 && r.token >= 0 && r.token < a.vocab) {
+    if (a.tokens_out) a.tokens_out[c.row] = r.token;
+    if ((a.flags & HS_SAMPLE_APPEND_TOKEN) && slot_ok && r.token >= 0 && r.token < a.vocab) {
       if (!slot_append_one(a.pool, P.slot, r.token)) out->status = r.status | 2;
     }
   }
   mark(8);
+  return false;
+}
+
+// Shared memory of the persistent kernel: the larger of the two paths' layouts.
+__host__ __device__ inline size_t bf16_kernel_smem() {
+  const size_t a = layout_v3().total, b = layout_cand().total;
+  return a > b ? a : b;
+}
+
+// One CTA per work item, two CTAs resident per SM; the hardware hands out the items in grid
+// order, long ones first: [0, batch) = row r on the counting path (a CTA whose row is not a
+// counting row leaves at once), then batch * split items = part p of row r on the candidate
+// path (likewise).  No CTA waits for another.
+__global__ void __launch_bounds__(kThreads, 2) row_kernel_bf16(const RowV3Args args) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int item = blockIdx.x;
+  int row = item;
+  bool count = item < args.batch;
+  if (!count) row = (item - args.batch) / args.split;
+  if (is_candidate_row(args.base.params[row], args.base.vocab) == count) return;  // the other path's row
+  if (!count) {
+    count = cand_part(args, smem_raw, row, (item - args.batch) % args.split);
+    __syncthreads();
+  }
+  if (count) count_row(args, smem_raw, row);
 }
 
 }  // namespace hs

@@ -40,6 +40,7 @@ struct RowKernelArgs {
   float* gstage;        // [batch, slice * cluster] global stage, or null = shared memory
   Pool pool;            // token-count histograms
   uint32_t flags;
+  int32_t* tokens_out;  // [batch] or null: the sampled ids once more, as the next step's input ids
 };
 
 struct RowCtx : ClusterCtx {
@@ -373,8 +374,9 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel(const RowKernelArgs a)
   c.sync_all();
 
   // ---- B. penalties from the row's resident (id, count) list -------------------------
-  const bool penalised = P.slot >= 0 && (P.repetition_penalty != 1.0f || P.presence_penalty != 0.0f ||
-                                          P.frequency_penalty != 0.0f);
+  const bool slot_ok = P.slot >= 0 && P.slot < a.pool.slots_total;
+  const bool penalised = slot_ok && (P.repetition_penalty != 1.0f || P.presence_penalty != 0.0f ||
+                                     P.frequency_penalty != 0.0f);
   if (penalised) {
     const int n_unique = min(a.pool.n[P.slot], a.pool.unique_cap);
     const int2* pairs = a.pool.pairs + (size_t)P.slot * a.pool.unique_cap;
@@ -418,7 +420,7 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel(const RowKernelArgs a)
 
   KeptSet kept{0u, 0x7fffffff};
   int token = argmax_id;
-  int status = 0;
+  int status = P.slot >= a.pool.slots_total ? 64 : 0;  // a slot this sampler does not have: no penalties
   u64 n_topk = (u64)a.vocab, n_minp = (u64)a.vocab, n_kept = (u64)a.vocab;
   u64 q_kept = 0;
   bool have_totals = false;
@@ -551,7 +553,8 @@ __global__ void __launch_bounds__(kThreads, 1) row_kernel(const RowKernelArgs a)
     out->n_cut_ties = (int32_t)cut_ties;
     out->row_max = m;
     out->log_z = log_z;
-    if ((a.flags & HS_SAMPLE_APPEND_TOKEN) && P.slot >= 0 && token >= 0 && token < a.vocab) {
+    if (a.tokens_out) a.tokens_out[c.row] = token;
+    if ((a.flags & HS_SAMPLE_APPEND_TOKEN) && slot_ok && token >= 0 && token < a.vocab) {
       if (!slot_append_one(a.pool, P.slot, token)) out->status = status | 2;
     }
   }

@@ -24,9 +24,11 @@
 // or one the probes keep missing, is found by scanning the row once more for its bit
 // pattern.  Lowest-id tie-breaks walk the row hierarchically.
 //
-// The kernel keeps the count table, the row's class list, its side list and the selection
-// histograms in shared memory (about 224 KB, one CTA per SM); what is left of L1 is too
-// small for its streaming loads, which therefore go past it.
+// A row's CTA keeps the count table, a short side list and (once the table has served, in its
+// place) the selection histograms in shared memory, about 88 KB, so that two CTAs share an
+// SM and one row's barrier-bound selection phases overlap another row's counting.  The list
+// of the row's non-empty classes (16 bytes each) lives in per-CTA global scratch and is
+// streamed from L2.  What is left of L1 is small, so the streaming loads go past it.
 #pragma once
 
 #include "hs_common.cuh"
@@ -44,7 +46,7 @@ constexpr uint32_t kV3Base = 113u << 7;       // smallest binned magnitude: 2^-1
 constexpr int kV3ListCap = 128;               // members resolved by sorting
 constexpr int kV3ScanCap = 1024;              // ids one class scan can hold (in the gather and list buffers)
 constexpr int kV3RareCap = 512;               // out-of-window tokens remembered before a sweep
-constexpr int kV3SideShared = 4096;           // side-list entries kept in shared memory (else global scratch)
+constexpr int kV3SideShared = 1024;           // side-list entries kept in shared memory (else global scratch)
 constexpr int kV3PhaseSlots = 16;
 constexpr int kSplitCap = 4096;               // candidate entries one CTA of a split row can hand over
 
@@ -66,8 +68,7 @@ struct LocalHist {
 };
 
 // A non-empty class with its score key and mass, computed once per row.  Stored in 16 bytes
-// (the first kV3SharedClasses of a row in shared memory, the rest in global scratch) and
-// handed to the visitors of for_each_class unpacked.
+// in the CTA's global scratch and handed to the visitors of for_each_class unpacked.
 struct __align__(16) ClassPacked {
   uint32_t key;  // 32-bit key of the class score
   uint32_t cnt;  // tokens in the class
@@ -90,25 +91,26 @@ __device__ __forceinline__ ClassEntry unpack_class(const uint4& v) {
 __device__ __forceinline__ uint4 pack_class(uint32_t key, uint32_t cnt, uint32_t cell, u64 q) {
   return make_uint4(key, cnt, (uint32_t)q, (uint32_t)(q >> 32) | (cell << 16));
 }
-constexpr int kV3SharedClasses = 6144;  // 96 KB of class entries next to the count table
 
 struct RowV3Args {
   RowKernelArgs base;
-  ClassPacked* clist;  // [batch, kCells - kV3SharedClasses] scratch: classes beyond those held in shared memory
-  int2* s_pair;   // [batch, s_cap] side lists: (token id or -1, fp32 bits of the score)
+  ClassPacked* clist;  // [n_scratch, kCells] scratch: the class list of the row a CTA is working on
+  int2* s_pair;   // [n_scratch, s_cap] side lists too long for shared memory: (token id or -1, fp32 bits of the score)
   int s_cap;
+  int n_scratch;       // scratch sets: as many as CTAs of the kernel can be resident at once
+  int* scratch_busy;   // [n_scratch] 1 while a CTA holds the set
   unsigned long long* phase_clocks;  // [batch, kV3PhaseSlots] or null
-  unsigned char* needs_count;        // [batch] set by row_kernel_topk when a row must be counted after all
-  int split;                         // CTAs per row in row_kernel_topk
+  int split;                         // CTAs per row on the candidate path
   unsigned long long* split_lists;   // [batch, split, kSplitCap] candidate lists of the row's CTAs
   int* split_n;                      // [batch, split] their lengths
   int* split_ticket;                 // [batch] arrival counter (returns to 0)
-  int pass;                          // row_kernel_v3: 0 = rows without a small top_k, 1 = rows the candidate kernel handed back
   int batch;                         // rows in the launch
 };
 
+// Shared memory of a counting row.  The selection histograms and the two member buffers are
+// only needed after the count table has been turned into the class list, and take its place.
 struct LayoutV3 {
-  size_t x, tab, hist, gbuf, list, rare, small, scl, total;
+  size_t x, tab, hist, gbuf, list, side, rare, small, total;
 };
 __host__ __device__ inline LayoutV3 layout_v3() {
   LayoutV3 l{};
@@ -120,15 +122,25 @@ __host__ __device__ inline LayoutV3 layout_v3() {
   };
   l.x = take(sizeof(Exchange));
   l.tab = take(sizeof(uint32_t) * kCells);
-  l.hist = take(sizeof(LocalHist));
-  l.gbuf = take(sizeof(V3Entry) * kV3ListCap);
-  l.list = take(sizeof(V3Entry) * kV3ListCap);
+  {
+    size_t in_tab = l.tab;
+    auto sub = [&](size_t bytes) {
+      const size_t at = in_tab;
+      in_tab = (in_tab + bytes + 15) & ~size_t(15);
+      return at;
+    };
+    l.hist = sub(sizeof(LocalHist));
+    l.gbuf = sub(sizeof(V3Entry) * kV3ListCap);
+    l.list = sub(sizeof(V3Entry) * kV3ListCap);
+  }
+  l.side = take(sizeof(int2) * kV3SideShared);
   l.rare = take(sizeof(int2) * kV3RareCap);
   l.small = take(sizeof(int) * 16);
-  l.scl = take(sizeof(ClassPacked) * kV3SharedClasses);
   l.total = off;
   return l;
 }
+static_assert(sizeof(LocalHist) + 2 * sizeof(V3Entry) * kV3ListCap + 32 <= sizeof(uint32_t) * kCells,
+              "the selection buffers fit in the count table's place");
 
 __device__ __forceinline__ int v3_bin_of_raw(uint32_t raw) {
   const uint32_t idx = (raw & 0x7fffu) - kV3Base;
@@ -157,12 +169,10 @@ struct Ctx3 {
   int slot;
   int2* s_pair;
   int n_s, s_cap;
-  ClassPacked* scl;  // this row's non-empty classes: entries [0, kV3SharedClasses) in shared memory,
-  ClassPacked* cl;   // the rest in global scratch
+  ClassPacked* cl;   // this row's non-empty classes (global scratch of this CTA)
   // entry i of the row's class list
   __device__ __forceinline__ ClassEntry class_at(int i) const {
-    const ClassPacked* p = i < kV3SharedClasses ? scl + i : cl + (i - kV3SharedClasses);
-    return unpack_class(*reinterpret_cast<const uint4*>(p));
+    return unpack_class(__ldcg(reinterpret_cast<const uint4*>(cl) + i));
   }
   int n_cl;
   float T, rp, pp, fp;
@@ -215,24 +225,21 @@ __device__ __forceinline__ void for_each_side3(const Ctx3& c, F&& f) {
   }
 }
 // Calls f(entry) for the row's non-empty classes, thread t taking entries t, t + kThreads, ...
+// (four 16-byte loads in flight per thread; the list sits in L2).
 template <class F>
 __device__ __forceinline__ void for_each_class(const Ctx3& c, F&& f) {
-  const int n_shared = min(c.n_cl, kV3SharedClasses);
-#pragma unroll 4
-  for (int i = threadIdx.x; i < n_shared; i += kThreads) f(unpack_class(reinterpret_cast<const uint4*>(c.scl)[i]));
-  // the overflow in global scratch, four entries in flight per thread
-  const int n_global = c.n_cl - n_shared;
-  for (int i0 = threadIdx.x; i0 < n_global; i0 += 4 * kThreads) {
+  const uint4* src = reinterpret_cast<const uint4*>(c.cl);
+  for (int i0 = threadIdx.x; i0 < c.n_cl; i0 += 4 * kThreads) {
     uint4 v[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int i = i0 + u * kThreads;
-      if (i < n_global) v[u] = reinterpret_cast<const uint4*>(c.cl)[i];
+      if (i < c.n_cl) v[u] = __ldcg(src + i);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int i = i0 + u * kThreads;
-      if (i >= n_global) break;
+      if (i >= c.n_cl) break;
       f(unpack_class(v[u]));
     }
   }

@@ -56,17 +56,20 @@ __global__ void __launch_bounds__(kThreads, 2) shard_partial_kernel(const ShardA
   c.T = P.temperature; c.rp = P.repetition_penalty; c.pp = P.presence_penalty; c.fp = P.frequency_penalty;
   c.pool = a.pool;
   c.slot = P.slot;
-  const bool penalised = P.slot >= 0 && (c.rp != 1.0f || c.pp != 0.0f || c.fp != 0.0f);
+  const bool slot_ok = P.slot >= 0 && P.slot < a.pool.slots_total;
+  const bool penalised = slot_ok && (c.rp != 1.0f || c.pp != 0.0f || c.fp != 0.0f);
   c.cls = penalised ? a.pool.cls + (size_t)P.slot * a.pool.cls_stride : nullptr;
-  c.s_pair = nullptr; c.n_s = 0; c.s_cap = 0; c.scl = nullptr; c.cl = nullptr; c.n_cl = 0; c.m = 0.f;
+  c.s_pair = nullptr; c.n_s = 0; c.s_cap = 0; c.cl = nullptr; c.n_cl = 0; c.m = 0.f;
   c.tab = nullptr; c.hist = nullptr; c.gbuf = nullptr; c.list = nullptr; c.gbuf_n = nullptr;
   hs_shard_rec* rec = args.recs + c.row;
   if (tid < 16) small[tid] = 0;
   __syncthreads();
   const int k = min(max(P.top_k, 1), c.vocab);
   int n = topk_candidates(c, L, k);
-  int status = 0;
-  if (n < 0) { status = 16; n = min(*L.n, kCandCap); }  // list overflow: the record is truncated
+  int status = P.slot >= a.pool.slots_total ? 64 : 0;  // a slot this sampler does not have: no penalties
+  // list overflow: what is in the list is partly unscored, so the record carries no candidates
+  // and the merge reports the row as failed
+  if (n < 0) { status |= 16; n = 0; }
   if (n > k) {
     const uint32_t cut = cand_kth_key(*c.x, L, n, k);
     n = cand_compact(L, n, cut);
@@ -75,6 +78,7 @@ __global__ void __launch_bounds__(kThreads, 2) shard_partial_kernel(const ShardA
   }
   cand_sort(L, n);
   if (n > HS_SHARD_CAND) { status |= 32; n = HS_SHARD_CAND; }  // more ties than the record holds
+  __syncthreads();
   const float m = n > 0 ? score_of(cand_key(L.cand[0])) : 0.f;
   // soft-max denominator of the whole slice, relative to the slice maximum (exact integer mass)
   u64 z = 0, unused = 0;

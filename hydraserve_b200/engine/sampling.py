@@ -7,11 +7,17 @@ C-ABI library (``include/hs_sampler.h``) on the caller's current CUDA stream and
 one result record per row.  There is no CPU code path: a tensor that lives on the host
 is copied to the GPU and sampled there, and a missing library or GPU raises.
 
-Extension over the reference (keyword-only, optional): ``request_ids``.  When given, the
-token-count histogram of each request stays resident on the device between calls and
-only the tokens appended since the previous call are uploaded, instead of rebuilding the
-histogram from the full history every step (the reference's behaviour,
-sampling.py:106-110, which remains the default here).
+Extensions over the reference, all optional:
+
+* ``request_ids`` (keyword-only).  When given, the token-count histogram of each request
+  stays resident on the device between calls and only the tokens appended since the
+  previous call are uploaded, instead of rebuilding the histogram from the full history
+  every step (the reference's behaviour, sampling.py:106-110, which remains the default
+  here).  ``release_request(request_id)`` frees a finished request's histogram, where the
+  reference's backends release a request (serving_loop.py:1481-1488).
+* ``sample_logits_packed``: the same call returning one array of fixed-size records
+  instead of a tuple of per-row objects, for the worker-to-coordinator reply
+  (pd_service.py:1097-1104) and the API layer (api/server.py:491-530).
 """
 from __future__ import annotations
 
@@ -19,7 +25,7 @@ import os
 from dataclasses import dataclass, replace
 from typing import Iterable, Sequence
 
-__all__ = ["SamplingParams", "TokenSample", "sample_logits"]
+__all__ = ["SamplingParams", "TokenSample", "sample_logits", "sample_logits_packed", "release_request"]
 
 _RANGES = (
     # field, low, high, low-inclusive, message (the reference's wording)
@@ -96,6 +102,19 @@ def _module():
     return sys.modules[__name__]
 
 
+def _checked(logits, histories, params, steps, request_ids):
+    if logits.ndim != 2:
+        raise ValueError("sampling logits must have shape [batch, vocabulary]")
+    histories = tuple(histories)
+    params = tuple(params)
+    steps = tuple(int(step) for step in steps)
+    if not (len(histories) == len(params) == len(steps) == logits.shape[0]):
+        raise ValueError("sampling metadata must match the logits batch")
+    if request_ids is not None and len(request_ids) != len(params):
+        raise ValueError("sampling metadata must match the logits batch")
+    return histories, params, steps
+
+
 def sample_logits(
     logits,
     histories: Iterable[Iterable[int]],
@@ -111,15 +130,7 @@ def sample_logits(
     ``steps``: number of tokens generated so far per row; it advances the seeded stream.
     Raises ``ValueError`` for the same shape and length mismatches as the reference.
     """
-    if logits.ndim != 2:
-        raise ValueError("sampling logits must have shape [batch, vocabulary]")
-    histories = tuple(histories)
-    params = tuple(params)
-    steps = tuple(int(step) for step in steps)
-    if not (len(histories) == len(params) == len(steps) == logits.shape[0]):
-        raise ValueError("sampling metadata must match the logits batch")
-    if request_ids is not None and len(request_ids) != len(params):
-        raise ValueError("sampling metadata must match the logits batch")
+    histories, params, steps = _checked(logits, histories, params, steps, request_ids)
     this = _module()
     from . import _device
 
@@ -135,6 +146,33 @@ def sample_logits(
             for i in range(len(params))
         )
     return _device.sample_batch(logits, histories, params, steps, request_ids)
+
+
+def sample_logits_packed(
+    logits,
+    histories: Iterable[Iterable[int]],
+    params: Iterable[SamplingParams],
+    *,
+    steps: Iterable[int],
+    request_ids: Sequence | None = None,
+):
+    """``sample_logits`` with the result as one ``PackedSamples`` (an array of fixed-size
+    records that indexes and iterates like the reference's tuple and pickles as bytes)."""
+    histories, params, steps = _checked(logits, histories, params, steps, request_ids)
+    from . import _device
+
+    greedy = all(_is_plain_greedy(config) for config in params)
+    return _device.sample_batch(logits, None if greedy else histories, params, steps,
+                                None if greedy else request_ids, all_plain_greedy=greedy, packed=True)
+
+
+def release_request(request_id, device=None) -> None:
+    """Free the device-resident histogram of a finished request (one that was sampled with
+    ``request_ids``); the place of the reference backends' ``release``
+    (serving_loop.py:1481-1488).  Unknown ids are ignored."""
+    from . import _device
+
+    _device.release_request(request_id, device)
 
 
 def _sample_row(logits, history, params: SamplingParams, step: int) -> TokenSample:

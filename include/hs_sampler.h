@@ -8,6 +8,15 @@
  * "host", pointers are DEVICE pointers valid on the sampler's device, and work is
  * enqueued on the given CUDA stream (a cudaStream_t passed as void*) without
  * synchronising it.
+ *
+ * Threads and streams.  Every function may be called from any thread, on any stream: the
+ * reference's callers are the serving loop, each worker's command loop and, concurrently,
+ * the threads that replay a first token on a side stream (hydraserve/engine/pd_service.py:
+ * 916-967, pd_worker.py:305-308, 475-480).  Calls on ONE sampler do not run concurrently:
+ * they take a lock for the time of their launches, and a call enqueued on another stream
+ * than the previous call first waits (on the GPU, through an event) for that call's work,
+ * because all calls share the sampler's scratch memory and histograms.  Two samplers never
+ * wait for each other.  hs_last_error returns the calling thread's last message.
  */
 #ifndef HS_SAMPLER_H
 #define HS_SAMPLER_H
@@ -33,8 +42,14 @@ typedef enum { HS_DTYPE_F32 = 0, HS_DTYPE_BF16 = 1 } hs_dtype;
 /* Bits of hs_row_params.flags. */
 #define HS_ROW_PLAIN_GREEDY 1u /* temperature 0, no penalties, no logprobs: argmax only */
 
-/* Bits of the `flags` argument of hs_sample. */
-#define HS_SAMPLE_APPEND_TOKEN 1u /* after sampling, count the sampled token in the row's slot */
+/* Bits of the `flags` argument of hs_sample / hs_sample_ex. */
+#define HS_SAMPLE_APPEND_TOKEN 1u   /* after sampling, count the sampled token in the row's slot */
+#define HS_SAMPLE_GENERAL_KERNEL 2u /* bf16 rows too take the general kernel (rows reported with status bit 4) */
+
+/* Bits of the `flags` argument of hs_create_ex (tests and tuning; a serving process passes 0). */
+#define HS_CREATE_FORCE_GENERAL 1u /* every row, bf16 included, takes the general (fp32-resident) kernel */
+#define HS_CREATE_PHASE_CLOCKS 2u  /* the bf16 kernel records phase time stamps, see hs_debug_phase_clocks */
+#define HS_CREATE_CLUSTER(n) (((uint32_t)(n) & 0xfu) << 8) /* general kernel: n = 1, 2, 4 or 8 CTAs per row */
 
 /* One row's sampling parameters: the numeric fields of SamplingParams
  * (reference sampling.py:8-19) in the fp32 precision the reference computes in. */
@@ -58,7 +73,12 @@ typedef struct hs_row_out {
   int32_t token;         /* sampled / argmax token id */
   float logprob;         /* log-probability of `token` (valid when n_logprobs >= 0) */
   int32_t n_top;         /* number of valid entries in top_ids / top_logprobs */
-  int32_t status;        /* 0 ok; bit 0: selection fell back (non-finite input) */
+  int32_t status;        /* 0 ok.  bit 0 (1): selection fell back (non-finite input); 2: the sampled token
+                            could not be counted (histogram full); 4: more individually scored tokens than
+                            the bf16 kernel keeps (values outside 2^-14 <= |x| < 2^10, history counts >= 3):
+                            sample the row again with HS_SAMPLE_GENERAL_KERNEL; 8: fewer top log-probabilities
+                            found than expected; 16 / 32: a vocabulary shard's record was cut short;
+                            64: params.slot is not a slot of this sampler (the row got no penalties) */
   int32_t n_kept;        /* size of the final candidate set */
   int32_t n_after_topk;  /* candidates left by top-k (ties at the k-th value kept) */
   int32_t n_after_minp;  /* ... and by min-p */
@@ -74,11 +94,18 @@ typedef struct hs_row_out {
 typedef struct hs_sampler hs_sampler;
 
 /* Create a sampler on `device`.  vocab_max: largest vocabulary any call will pass.
- * slots_max: number of resident token-count histograms (one per request in flight).
- * unique_cap: most distinct token ids one histogram can hold (<= vocab_max; 0 = vocab_max).
- * batch_max: most rows per call.  Allocates all device memory the sampler will ever use. */
-int hs_create(int device, int vocab_max, int slots_max, int unique_cap, int batch_max,
+ * slots_max: number of resident token-count histograms (one per request in flight); the
+ *   sampler adds batch_max more, [slots_max, slots_max + batch_max), for histories that live
+ *   for one call only.
+ * hist_cap: most distinct token ids one histogram can hold (<= vocab_max; 0 = vocab_max); a
+ *   request's history cannot hold more distinct ids than its context length.  Device memory
+ *   per slot: 12 * hist_cap + 4.25 * vocab_max bytes (hs_query what = 6).
+ * batch_max: most rows per call.  Allocates all device memory the sampler will ever use
+ *   (hs_query what = 5).  The environment is not consulted. */
+int hs_create(int device, int vocab_max, int slots_max, int hist_cap, int batch_max,
               hs_sampler** out);
+int hs_create_ex(int device, int vocab_max, int slots_max, int hist_cap, int batch_max,
+                 uint32_t flags /* HS_CREATE_* */, hs_sampler** out);
 int hs_destroy(hs_sampler* h);
 
 /* Token-count histograms: the device-resident form of the `counts` dict the reference
@@ -103,6 +130,14 @@ int hs_slot_unique_count(hs_sampler* h, int slot, void* stream, int* out);
 int hs_sample(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch,
               int vocab, const hs_row_params* params, hs_row_out* out, const float* noise,
               float* scores_out, uint32_t flags, void* stream);
+/* hs_sample that also leaves the sampled ids in tokens_out[batch] (device, int32; NULL = as
+ * hs_sample): the next decode step's input ids.  The reference copies them in from the host
+ * every step (hydraserve/model/runtime.py:682); with this buffer and HS_SAMPLE_APPEND_TOKEN a
+ * decode loop can run step after step on one stream without reading anything back, and fetch
+ * the records of several steps later (or never). */
+int hs_sample_ex(hs_sampler* h, const void* logits, int dtype, int64_t row_stride, int batch,
+                 int vocab, const hs_row_params* params, hs_row_out* out, const float* noise,
+                 float* scores_out, int32_t* tokens_out, uint32_t flags, void* stream);
 
 /* The all-rows-plain-greedy fast path (reference sampling.py:69-73): argmax per row,
  * lowest id on ties, int32 token ids to tokens_out[batch]. */
@@ -176,12 +211,16 @@ int hs_abi_version(void);
  *       1 = 1 if the general kernel would hold that row in shared memory, 0 if in global scratch
  *           (the bf16 kernels do not hold the row at all),
  *       2 = number of SMs, 3 = kernels launched by this sampler so far (low 31 bits),
- *       4 = 1 if (vocab, dtype) takes the bf16 kernels (candidate / counting), 0 if the general one */
+ *       4 = 1 if (vocab, dtype) takes the bf16 kernel (candidate / counting paths), 0 if the general one,
+ *       5 = device memory held by the sampler, in KiB, 6 = device bytes per histogram slot,
+ *       7 = CTAs of the bf16 kernel that can be resident at once (CTAs per SM x SMs) */
 int hs_query(hs_sampler* h, int what, int vocab, int dtype);
-/* Tuning aid: when the sampler was created with the environment variable HS_PHASE_CLOCKS=1,
- * the bf16 kernels record the SM clock at 16 phase slots per row of the last launch;
- * this copies batch x 16 counters to out_host (synchronises the device). */
+/* Tuning aid: a sampler created with HS_CREATE_PHASE_CLOCKS records the SM clock at 16 phase
+ * slots per row of the last launch; this copies batch x 16 counters to out_host
+ * (synchronises the device). */
 int hs_debug_phase_clocks(hs_sampler* h, int batch, unsigned long long* out_host);
+/* Tests and tuning.  what = 0: CTAs per candidate row, value 1, 2 or 4 (0 = chosen per call). */
+int hs_debug_set(hs_sampler* h, int what, int value);
 
 #ifdef __cplusplus
 }

@@ -20,7 +20,7 @@ from dataclasses import dataclass, field
 
 import numpy as np
 
-REL = 1e-5  # tolerance north-star states for penalised logits and log-probabilities
+REL = 1e-5  # relative tolerance for penalised logits and log-probabilities
 
 
 def close(a: float, b: float, rel: float = REL, abs_: float = 2e-6) -> bool:
@@ -29,17 +29,24 @@ def close(a: float, b: float, rel: float = REL, abs_: float = 2e-6) -> bool:
     return abs(a - b) <= max(abs_, rel * max(abs(a), abs(b)))
 
 
+# (case name, rows compared, rounding-sensitive rows, rows whose top-p cut split a tie group),
+# one entry per finished comparison; tests/conftest.py prints them after the run
+COUNTS: list = []
+
+
 @dataclass
 class Report:
     rows: int = 0
     sensitive: int = 0
     tie_split: int = 0
     failures: list = field(default_factory=list)
+    name: str = ""
 
     def fail(self, row, message):
         self.failures.append(f"row {row}: {message}")
 
-    def assert_ok(self, max_sensitive_fraction: float = 1.0):
+    def assert_ok(self, max_sensitive_fraction: float = 1.0, name: str = ""):
+        COUNTS.append((name or self.name or "?", self.rows, self.sensitive, self.tie_split))
         assert not self.failures, "\n".join(self.failures[:20])
         assert self.sensitive <= max_sensitive_fraction * max(self.rows, 1), (
             f"{self.sensitive} of {self.rows} rows were rounding-sensitive")

@@ -122,3 +122,100 @@ def test_missing_gpu_fails_loudly():
         pytest.skip("a GPU is present")
     with pytest.raises(RuntimeError, match="no CPU sampling path"):
         sampling.sample_logits(torch.zeros(1, 3), ((),), (SamplingParams(temperature=1.0, seed=1),), steps=(0,))
+
+
+def test_slot_book_evicts_least_recently_used_and_never_a_row_of_the_batch():
+    """More live requests than resident slots: the least recently used request outside the
+    current batch loses its slot; when every slot belongs to the batch, the caller is told to
+    use a per-call slot (no two rows of a call may share one)."""
+    from hydraserve_b200.engine._device import SlotBook
+
+    book = SlotBook(3)
+    batch = {"a", "b", "c"}
+    slots = {}
+    for rid in ("a", "b", "c"):
+        entry, new = book.lookup(rid, batch)
+        assert new and entry[1] == 0
+        entry[1] = 10
+        slots[rid] = entry[0]
+    assert sorted(slots.values()) == [0, 1, 2]
+    # a fourth request in the same batch finds every slot held by the batch: no eviction
+    entry, new = book.lookup("d", batch | {"d"})
+    assert entry is None and not new
+    assert {rid: book.entries[rid][0] for rid in "abc"} == slots
+    # touching "a" makes "b" the least recently used; a later batch without "b" evicts it
+    assert book.lookup("a", {"a"})[0][0] == slots["a"]
+    entry, new = book.lookup("d", {"a", "d"})
+    assert new and entry[0] == slots["b"] and entry[1] == 0 and "b" not in book.entries
+    # the evicted request comes back as new (its histogram is rebuilt), evicting "c"
+    entry, new = book.lookup("b", {"b"})
+    assert new and entry[0] == slots["c"] and "c" not in book.entries
+    assert book.release("a") and not book.release("a")
+    assert book.lookup("e", {"e"})[0][0] == slots["a"]
+    # slots held never repeat
+    held = [e[0] for e in book.entries.values()]
+    assert len(held) == len(set(held)) == 3
+
+
+def test_unseeded_rows_take_the_keys_they_are_given():
+    from hydraserve_b200.engine import _device
+
+    ps = [SamplingParams(temperature=1.0), SamplingParams(temperature=1.0, seed=7), SamplingParams()]
+    rec = _device.pack_params(ps, [0, 1, 2], None, [11, None, None])
+    assert int(rec["seed"][0]) == _device.mixed_seed(11, 0)
+    assert int(rec["seed"][1]) == _device.mixed_seed(7, 1)
+    assert int(rec["seed"][2]) == _device.mixed_seed(0, 2)
+    again = _device.pack_params(ps, [0, 1, 2], None, [11, None, None])
+    assert rec.tobytes() == again.tobytes()
+
+
+def test_packed_samples_behave_like_the_tuple_and_pickle_small():
+    """The array-form result: same TokenSample objects on demand, and what crosses a process
+    boundary is the raw records (the reference pickles tuple[TokenSample] per step,
+    pd_service.py:1097-1104).  64 rows x 20 logprobs."""
+    import pickle
+    import time
+
+    from hydraserve_b200 import _lib
+    from hydraserve_b200.engine import TokenSample, _device
+
+    rng = np.random.default_rng(5)
+    n = 64
+    records = np.zeros(n, dtype=_lib.ROW_OUT)
+    records["token"] = rng.integers(0, 151_936, n)
+    records["logprob"] = -rng.random(n).astype(np.float32)
+    records["n_top"] = 20
+    records["top_ids"] = rng.integers(0, 151_936, (n, 20))
+    records["top_logprobs"] = -np.sort(rng.random((n, 20)).astype(np.float32), axis=1)
+    records["n_top"][3] = 2  # fewer candidates than requested: -inf filler, as in the reference
+    params = [SamplingParams(temperature=1.0, seed=i, logprobs=20) for i in range(n)]
+    params[5] = SamplingParams(temperature=1.0, seed=5)
+    packed = _device.PackedSamples(records, [-1 if p.logprobs is None else p.logprobs for p in params], 151_936)
+    as_tuple = _device.records_to_samples(records, params, 151_936)
+    assert len(packed) == n and packed.to_samples() == as_tuple and packed == as_tuple
+    assert packed[5] == TokenSample(int(records["token"][5]))
+    assert len(packed[3].top_logprobs) == 20 and packed[3].top_logprobs[-1][1] == float("-inf")
+    assert packed.token_ids.tolist() == [s.token_id for s in as_tuple]
+    t0 = time.perf_counter()
+    wire_packed = pickle.dumps(packed, protocol=pickle.HIGHEST_PROTOCOL)
+    back = pickle.loads(wire_packed)
+    t_packed = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    wire_tuple = pickle.dumps(as_tuple, protocol=pickle.HIGHEST_PROTOCOL)
+    pickle.loads(wire_tuple)
+    t_tuple = time.perf_counter() - t0
+    assert back == as_tuple and back.records.tobytes() == records.tobytes()
+    assert len(wire_packed) < 64 * 208 + 512
+    assert len(wire_packed) < len(wire_tuple)
+    print(f"packed: {len(wire_packed)} bytes, {t_packed * 1e6:.0f} us; tuple[TokenSample]: "
+          f"{len(wire_tuple)} bytes, {t_tuple * 1e6:.0f} us")
+
+
+def test_slot_bytes_arithmetic():
+    """Device memory per histogram slot: 8 B (id, count) + 4 B (heavy list) per distinct id the
+    slot can hold, a 4-byte position and 2 bits of class per vocabulary entry."""
+    from hydraserve_b200.engine import _device
+
+    assert _device.slot_bytes(248_320, 32_768) == 12 * 32_768 + 4 * 248_320 + 4 * ((248_320 + 15) // 16 + 4) + 8
+    assert _device.slot_bytes(248_320, 32_768) <= 1.5 * 2**20
+    assert _device.slot_bytes(151_936, 0) == _device.slot_bytes(151_936, 151_936)

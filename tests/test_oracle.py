@@ -35,7 +35,7 @@ def test_checker_matches_reference_outputs(name):
             top=top, kept_n=kept_n, kept_ids=kept_ids, kept_sum=int(g["kept_sum"][r]),
             cut_value=None if kept_n < 0 else g["kept_min"][r],
             eps=REFERENCE_EPS, exact_ties=False)
-    report.assert_ok()
+    report.assert_ok(name=f"checker vs reference fixture {name}")
 
 
 def test_reference_unit_case_greedy_penalties_logprobs():

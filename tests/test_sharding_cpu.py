@@ -97,3 +97,47 @@ def test_shard_bounds_and_history_mapping():
         sharded.check_params([SamplingParams(temperature=1.0)])
     with pytest.raises(ValueError, match="top_k"):
         sharded.check_params([SamplingParams(temperature=1.0, top_k=57)])
+
+
+def _seed_worker(rank, world, port, queue):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from hydraserve_b200.engine import SamplingParams, _device
+
+        torch.manual_seed(1000 + 17 * rank)  # the ranks' global generators differ
+        for _ in range(rank * 3):
+            torch.rand(())
+        params = [SamplingParams(temperature=1.0, top_k=5), SamplingParams(temperature=0.8, top_k=9, seed=4),
+                  SamplingParams(temperature=1.2, top_k=2)]
+        keys = sharded.agree_on_unseeded_keys(params)
+        rec = _device.pack_params(params, [3, 4, 5], None, keys)
+        mine = [int(v) for v in rec["seed"]]
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine)
+        assert all(e == everyone[0] for e in everyone), everyone
+        assert keys[1] is None and keys[0] is not None and keys[0] != keys[2]
+        # every row seeded: nothing to agree on, no collective is issued
+        assert sharded.agree_on_unseeded_keys([SamplingParams(temperature=1.0, top_k=5, seed=1)]) is None
+        queue.put((rank, "ok"))
+    except Exception as exc:  # pragma: no cover - reported to the parent
+        queue.put((rank, repr(exc)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_unseeded_rows_get_the_same_stream_key_on_every_rank():
+    """Rows with seed=None take their stream key from torch's global generator, whose state
+    differs between ranks: rank 0's keys are broadcast so that tensor-parallel replicas draw
+    the same token."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_seed_worker, args=(r, world, port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [queue.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results
