@@ -102,10 +102,20 @@ __device__ __forceinline__ u64 shfl_xor_u64(u64 v, int lane_mask) {
 __device__ __forceinline__ u64 shfl_u64(u64 v, int src) {
   return __shfl_sync(0xffffffffu, v, src);
 }
+// Sum over the warp of values below 2^62: three 22-bit limbs, one REDUX each (a chain of
+// five dependent 64-bit shuffle steps costs several times as much).
 __device__ __forceinline__ u64 warp_sum_u64(u64 v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
+  const uint32_t l0 = __reduce_add_sync(0xffffffffu, (uint32_t)v & 0x3fffffu);
+  const uint32_t l1 = __reduce_add_sync(0xffffffffu, (uint32_t)(v >> 22) & 0x3fffffu);
+  const uint32_t l2 = __reduce_add_sync(0xffffffffu, (uint32_t)(v >> 44));
+  return (u64)l0 + ((u64)l1 << 22) + ((u64)l2 << 44);
+}
+// Maximum over the warp: the high words first, then the low words of the lanes that hold it.
+__device__ __forceinline__ u64 warp_max_u64(u64 v) {
+  const uint32_t hi = (uint32_t)(v >> 32);
+  const uint32_t top = __reduce_max_sync(0xffffffffu, hi);
+  const uint32_t lo = __reduce_max_sync(0xffffffffu, hi == top ? (uint32_t)v : 0u);
+  return ((u64)top << 32) | lo;
 }
 __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
   return __reduce_max_sync(0xffffffffu, v);
@@ -155,21 +165,11 @@ __device__ __forceinline__ uint32_t block_max_u32(Exchange& x, uint32_t v) {
 }
 __device__ __forceinline__ u64 block_max_u64(Exchange& x, u64 v) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    u64 t = __shfl_xor_sync(0xffffffffu, v, o);
-    v = t > v ? t : v;
-  }
+  v = warp_max_u64(v);
   __syncthreads();
   if (lane == 0) x.warp_a[warp] = v;
   __syncthreads();
-  v = lane < kWarps ? x.warp_a[lane] : 0ull;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    u64 t = __shfl_xor_sync(0xffffffffu, v, o);
-    v = t > v ? t : v;
-  }
-  return v;
+  return warp_max_u64(lane < kWarps ? x.warp_a[lane] : 0ull);
 }
 // Exclusive prefix of (a, b) over the warps of the CTA, given per-warp totals held by
 // every lane of each warp; also returns the CTA totals.  Two barriers.

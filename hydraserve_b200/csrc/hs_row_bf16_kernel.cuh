@@ -137,7 +137,9 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
                          (uint32_t)min((size_t)kPiece, cls_bytes - at));
     }
   }
-  if (tid < 16) small[tid] = 0;
+  // small[16..18] / [19..21]: highest (+ 1) / lowest non-empty cell per count class; [22]: lowest side key
+  if (tid < 32) small[tid] = (tid >= 19 && tid <= 22) ? -1 : 0;
+  if (tid == 0) c.x->bcast[5] = 0;  // highest side element, (key, ~id)
   __syncthreads();
   // Global scratch (class list, long side lists) is held per RESIDENT CTA: a CTA claims one of
   // the n_scratch sets (as many as CTAs can be resident, so one is always free), starting its
@@ -174,102 +176,100 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
 
   // ---- A. the one read of the row from HBM: count tokens per (count class, value) --------
   {
-      auto count_one = [&](uint32_t raw, int cc, int id) {
-        if (cc == 3) return;  // listed per request; handled below with its exact count
-        const int b = v3_bin_of_raw(raw);
-        if (b >= 0) {
-          atomicAdd(&c.tab[cc * kV3Bins + b], 1u);
-        } else {
-          const int slot = atomicAdd(rare_n, 1);
-          if (slot < kV3RareCap) rare[slot] = make_int2(id, (int)(raw | ((uint32_t)cc << 16)));
-        }
-      };
-      const int n8 = c.vec ? c.vocab / 8 : 0;
-      const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
-      const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
-      // Eight tokens at a time without a branch per token.  Per 32-bit word (two tokens):
-      // |x| + (0x8000 - base) sets bit 15 of a half iff |x| >= base and leaves |x| - base
-      // in its low bits; |x| + (0x8000 - top) sets it iff |x| >= top.  A chunk with a value
-      // outside the window or a token of count class 3 (rare) takes the per-token path.
-      constexpr uint32_t kLoAdd = (0x8000u - kV3Base) * 0x00010001u;
-      constexpr uint32_t kHiAdd = (0x8000u - (kV3Base + (uint32_t)kV3Half)) * 0x00010001u;
-      // 32-bit shared-memory addresses: one LOP3, one multiply-add, one shift-add and the
-      // reduction per token
-      const uint32_t tab_mid = (uint32_t)__cvta_generic_to_shared(c.tab + kV3Half);
-      // J-th token of the chunk (J even: low half of its word, odd: high half); its 2-bit
-      // class sits at bit 2J of cl.  Written as PTX so that each step is one instruction:
-      // sign mask (byte permute with sign replication), (lo & 0x7fff) ^ mask (one LOP3),
-      // class offset and table address (two multiply-adds on the FMA pipe), the reduction.
-      auto bump = [&](uint32_t lo_word, uint32_t word, uint32_t cl, auto J) {
-        constexpr int kJ = decltype(J)::value;
-        constexpr int kShift = 2 * kJ;
-        constexpr uint32_t kClassBytes = (uint32_t)(kV3Bins * 4);  // 3 << 13
-        uint32_t sign_mask, idx, rel, base, addr;
-        if (kJ & 1) {
-          asm("prmt.b32 %0, %1, 0, 0xBBBB;" : "=r"(sign_mask) : "r"(word));   // sign of byte 3
-          asm("prmt.b32 %0, %1, 0, 0x4432;" : "=r"(idx) : "r"(lo_word));      // high half
-        } else {
-          asm("prmt.b32 %0, %1, 0, 0x9999;" : "=r"(sign_mask) : "r"(word));   // sign of byte 1
-          idx = lo_word;
-        }
-        // bin = kV3Half + idx for x >= 0, kV3Half - 1 - idx = kV3Half + ~idx for x < 0
-        asm("lop3.b32 %0, %1, 0x7fff, %2, 0x6a;" : "=r"(rel) : "r"(idx), "r"(sign_mask));  // (a & b) ^ c
-        if (kShift < 14) {
-          const uint32_t field = cl & (3u << kShift);
-          asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(base) : "r"(field), "n"(kClassBytes >> kShift), "r"(tab_mid));
-        } else {
-          const uint32_t field = cl >> 14;
-          asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(base) : "r"(field), "n"(kClassBytes), "r"(tab_mid));
-        }
-        asm("mad.lo.u32 %0, %1, 4, %2;" : "=r"(addr) : "r"(rel), "r"(base));
-        asm volatile("red.shared.add.u32 [%0], 1;" ::"r"(addr) : "memory");
-      };
-      auto take_chunk = [&](const uint4& w4, uint32_t cl4, int i) {
-        const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
-        uint32_t lo[4], bad = cl4 & (cl4 >> 1) & 0x5555u;  // a token of class 3
-  #pragma unroll
+    auto count_one = [&](uint32_t raw, int cc, int id) {
+      if (cc == 3) return;  // listed per request; handled below with its exact count
+      const int b = v3_bin_of_raw(raw);
+      if (b >= 0) {
+        atomicAdd(&c.tab[cc * kV3Bins + b], 1u);
+      } else {
+        const int slot = atomicAdd(rare_n, 1);
+        if (slot < kV3RareCap) rare[slot] = make_int2(id, (int)(raw | ((uint32_t)cc << 16)));
+      }
+    };
+    const int n8 = c.vec ? c.vocab / 8 : 0;
+    const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
+    const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
+    // Eight tokens at a time without a branch per token.  Per 32-bit word (two tokens):
+    // |x| + (0x8000 - base) sets bit 15 of a half iff |x| >= base and leaves |x| - base in its
+    // low bits; |x| + (0x8000 - top) sets it iff |x| >= top; a byte permute with sign
+    // replication turns the two sign bits into two 16-bit masks, and one LOP3 leaves, per half,
+    // the bin relative to the middle of a class table as a signed 16-bit number (idx for
+    // x >= 0, -1 - idx for x < 0).  Per token: sign-extending extraction (one permute), class
+    // offset and table address (two multiply-adds on the FMA pipe), the reduction.  A chunk
+    // with a value outside the window or a token of count class 3 (rare) takes the per-token
+    // path.  Written as PTX where one instruction is meant.
+    constexpr uint32_t kLoAdd = (0x8000u - kV3Base) * 0x00010001u;
+    constexpr uint32_t kHiAdd = (0x8000u - (kV3Base + (uint32_t)kV3Half)) * 0x00010001u;
+    constexpr uint32_t kClassBytes = (uint32_t)(kV3Bins * 4);
+    const uint32_t tab_mid = (uint32_t)__cvta_generic_to_shared(c.tab + kV3Half);
+    auto take_chunk = [&](const uint4& w4, uint32_t cl4, int i) {
+      const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+      uint32_t rel2[4];
+      uint32_t wnd = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        uint32_t mag, mask;
+        asm("and.b32 %0, %1, 0x7fff7fff;" : "=r"(mag) : "r"(words[k]));
+        const uint32_t lo = mag + kLoAdd, ht = mag + kHiAdd;
+        asm("lop3.b32 %0, %1, %2, %3, 0xef;" : "=r"(wnd) : "r"(lo), "r"(ht), "r"(wnd));     // wnd | ~lo | ht
+        asm("prmt.b32 %0, %1, 0, 0xBB99;" : "=r"(mask) : "r"(words[k]));                     // 0xffff per negative half
+        asm("lop3.b32 %0, %1, 0x7fff7fff, %2, 0x6a;" : "=r"(rel2[k]) : "r"(lo), "r"(mask));  // (lo & 0x7fff7fff) ^ mask
+      }
+      // bits 15 / 31 of wnd: a value outside the window; bit 2J of cl & (cl >> 1): token J is of class 3
+      if (((wnd & 0x80008000u) | (cl4 & (cl4 >> 1) & 0x5555u)) == 0) {
+#pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint32_t mag = words[k] & 0x7fff7fffu;
-          lo[k] = mag + kLoAdd;
-          bad |= (~lo[k] | (mag + kHiAdd)) & 0x80008000u;
-        }
-        if (bad == 0) {
-#define HS_BUMP_WORD(K)                                                           \
-  bump(lo[K], words[K], cl4, std::integral_constant<int, 2 * K>{});               \
-  bump(lo[K], words[K], cl4, std::integral_constant<int, 2 * K + 1>{});
-          HS_BUMP_WORD(0) HS_BUMP_WORD(1) HS_BUMP_WORD(2) HS_BUMP_WORD(3)
-#undef HS_BUMP_WORD
-        } else {
-          count_chunk_slow(c.tab, rare_n, rare, w4, cl4, i);
-        }
-      };
-      // two batches of loads: the next one is on its way while this one is counted
-      constexpr int kInFlight = 4;  // 128-bit loads per batch (4, 6 and 8 measured the same)
-      uint4 w[kInFlight], wn[kInFlight];
-      uint32_t cl[kInFlight], cn[kInFlight];
-      auto fetch = [&](uint4 (&dw)[kInFlight], uint32_t (&dc)[kInFlight], int i0) {
-  #pragma unroll
-        for (int u = 0; u < kInFlight; ++u) {
-          const int i = i0 + u * kThreads;
-          if (i < n8) {
-            dw[u] = __ldcg(src4 + i);  // past L1: almost all of it is shared memory here
-            dc[u] = cls16p ? __ldcg(cls16p + i) : 0u;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int kShift = 2 * (2 * k + h);
+            uint32_t r;
+            if (h == 0) asm("prmt.b32 %0, %1, 0, 0x9910;" : "=r"(r) : "r"(rel2[k]));  // low half, sign extended
+            else asm("prmt.b32 %0, %1, 0, 0xBB32;" : "=r"(r) : "r"(rel2[k]));          // high half, sign extended
+            uint32_t base;
+            if (kShift < 14) base = (cl4 & (3u << kShift)) * (kClassBytes >> kShift) + tab_mid;
+            else base = (cl4 >> 14) * kClassBytes + tab_mid;
+            const uint32_t addr = r * 4u + base;
+            asm volatile("red.shared.add.u32 [%0], 1;" ::"r"(addr) : "memory");
           }
         }
-      };
-      fetch(w, cl, tid);
-      if (hv_pair.x >= 0 && hv_pair.x < c.vocab) hv_raw = load_now_u16(c.logits + hv_pair.x);
-      for (int i0 = tid; i0 < n8; i0 += kInFlight * kThreads) {
-        fetch(wn, cn, i0 + kInFlight * kThreads);
-  #pragma unroll
-        for (int u = 0; u < kInFlight; ++u) {
-          const int i = i0 + u * kThreads;
-          if (i < n8) take_chunk(w[u], cl[u], i);
-        }
-  #pragma unroll
-        for (int u = 0; u < kInFlight; ++u) { w[u] = wn[u]; cl[u] = cn[u]; }
+      } else {
+        count_chunk_slow(c.tab, rare_n, rare, w4, cl4, i);
       }
-      for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) count_one(c.logits[id], c.class_of(id), id);
+    };
+    // Two batches of loads: the next one is on its way while this one is counted.  The main
+    // loop runs without bounds checks; what is left over is taken chunk by chunk.
+    constexpr int kInFlight = 2;  // 128-bit loads per thread and batch
+    constexpr int kStride = kInFlight * kThreads;
+    const int n_full = n8 / kStride;
+    int i0 = tid;
+    if (hv_pair.x >= 0 && hv_pair.x < c.vocab) hv_raw = load_now_u16(c.logits + hv_pair.x);
+    if (n_full > 0) {
+      uint4 w[kInFlight], wn[kInFlight];
+      uint32_t cl[kInFlight], cn[kInFlight];
+#pragma unroll
+      for (int u = 0; u < kInFlight; ++u) {
+        w[u] = __ldcg(src4 + i0 + u * kThreads);  // past L1: almost all of it is shared memory here
+        cl[u] = cls16p ? (uint32_t)__ldcg(cls16p + i0 + u * kThreads) : 0u;
+        wn[u] = w[u];
+        cn[u] = cl[u];
+      }
+      for (int it = 0; it < n_full; ++it) {
+        if (it + 1 < n_full) {
+#pragma unroll
+          for (int u = 0; u < kInFlight; ++u) {
+            wn[u] = __ldcg(src4 + i0 + kStride + u * kThreads);
+            cn[u] = cls16p ? (uint32_t)__ldcg(cls16p + i0 + kStride + u * kThreads) : 0u;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) take_chunk(w[u], cl[u], i0 + u * kThreads);
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) { w[u] = wn[u]; cl[u] = cn[u]; }
+        i0 += kStride;
+      }
+    }
+    for (int i = i0; i < n8; i += kThreads) take_chunk(__ldcg(src4 + i), cls16p ? (uint32_t)__ldcg(cls16p + i) : 0u, i);
+    for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) count_one(c.logits[id], c.class_of(id), id);
   }
   __syncthreads();
   mark(1);
@@ -277,6 +277,7 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
   // ---- B. the side list: tokens with history count >= 3, and values outside the bin window
   // It is walked by every selection, so it lives in shared memory when it fits.
   u64 side_best = 0;
+  uint32_t side_worst = 0xffffffffu;  // this thread's lowest side key
   const int n_rare = *rare_n;
   if (n_rare <= kV3RareCap && n_heavy + kV3RareCap <= kV3SideShared) {
     c.s_pair = side_shared;
@@ -288,6 +289,7 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
       c.s_pair[slot] = make_int2(id, __float_as_int(s));
       const u64 packed = ((u64)key_of(s) << 32) | (uint32_t)(~(uint32_t)id);
       side_best = packed > side_best ? packed : side_best;
+      side_worst = min(side_worst, key_of(s));
     };
     if (penalised) {
       if (tid < n_heavy) {  // the entry whose reads were started early
@@ -323,56 +325,56 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
     }
   }
   if (clocks && tid == 0) clocks[11] = clock64();
-  side_best = block_max_u64(*c.x, side_best);  // (its barriers also publish the side list)
-  mark(2);
-
-  // ---- C. row maximum ------------------------------------------------------------------------
-  // scores grow with the bin inside a count class: the top non-empty bin of each class decides
-  uint32_t cells_key = 0;
+  // ---- C. row maximum and minimum --------------------------------------------------------------
+  // Scores grow with the bin inside a count class, so the highest and lowest non-empty bin of
+  // each class decide (with the side list).  One pass over the table; warps combine with
+  // REDUX and meet in shared memory, one barrier (which also publishes the side list).
   {
-    uint32_t top[3];
+    uint32_t top[3] = {0u, 0u, 0u}, bot[3] = {0xffffffffu, 0xffffffffu, 0xffffffffu};
+    constexpr int kPerClass = kV3Bins / kThreads;  // a thread's cells tid + u * kThreads: count class u / kPerClass
+    static_assert(kV3Bins % kThreads == 0, "a thread's u-th cell has the same count class for all threads");
 #pragma unroll
     for (int k = 0; k < 3; ++k) {
-      uint32_t mine = 0;
-      for (int cell = k * kV3Bins + tid; cell < (k + 1) * kV3Bins; cell += kThreads)
-        if (c.tab[cell]) mine = (uint32_t)cell + 1;
-      top[k] = block_max_u32(*c.x, mine);
+#pragma unroll 4
+      for (int u = 0; u < kPerClass; ++u) {
+        const uint32_t cell = (uint32_t)(tid + (k * kPerClass + u) * kThreads);
+        if (c.tab[cell]) { top[k] = cell + 1u; bot[k] = min(bot[k], cell); }
+      }
     }
+    const int lane = tid & 31;
 #pragma unroll
-    for (int k = 0; k < 3; ++k)
-      if (top[k]) cells_key = max(cells_key, key_of(c.cell_score((int)top[k] - 1)));
+    for (int k = 0; k < 3; ++k) {
+      const uint32_t t = __reduce_max_sync(0xffffffffu, top[k]);
+      const uint32_t l = __reduce_min_sync(0xffffffffu, bot[k]);
+      if (lane == 0) {
+        if (t) atomicMax(reinterpret_cast<unsigned*>(small) + 16 + k, t);
+        if (l != 0xffffffffu) atomicMin(reinterpret_cast<unsigned*>(small) + 19 + k, l);
+      }
+    }
+    const u64 sb = warp_max_u64(side_best);
+    const uint32_t sl = __reduce_min_sync(0xffffffffu, side_worst);
+    if (lane == 0) {
+      if (sb) atomicMax(&c.x->bcast[5], sb);
+      if (sl != 0xffffffffu) atomicMin(reinterpret_cast<unsigned*>(small) + 22, sl);
+    }
   }
+  __syncthreads();
+  side_best = c.x->bcast[5];
+  mark(2);
+  uint32_t cells_key = 0, min_key = reinterpret_cast<unsigned*>(small)[22];
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    const uint32_t t = reinterpret_cast<unsigned*>(small)[16 + k], l = reinterpret_cast<unsigned*>(small)[19 + k];
+    if (t) cells_key = max(cells_key, key_of(c.cell_score((int)t - 1)));
+    if (l != 0xffffffffu) min_key = min(min_key, key_of(c.cell_score((int)l)));
+  }
+  if (clocks && tid == 0) clocks[25] = clock64();
   const uint32_t side_key = (uint32_t)(side_best >> 32);
   const int side_arg = (int)(~(uint32_t)(side_best & 0xffffffffu));
   const bool any_side = side_best != 0;
   const uint32_t max_key = max(cells_key, side_key);
   c.m = score_of(max_key);
   const float m = c.m;
-  // ---- the row's non-empty classes, each with its key and mass computed once ---------------
-  // Thread t owns classes t, t + kThreads, ... (the populated value range spreads evenly over
-  // the threads) and writes its entries back to back; the order is fixed by the counts alone.
-  {
-    constexpr int kPerCells = kCells / kThreads;
-    int mine = 0;
-#pragma unroll 4
-    for (int u = 0; u < kPerCells; ++u) mine += c.tab[tid + u * kThreads] != 0;
-    const u64 incl = warp_scan_u64((u64)mine);
-    u64 pre, pre_unused, tot, tot_unused;
-    block_warp_prefix2(*c.x, shfl_u64(incl, 31), 0, pre, pre_unused, tot, tot_unused);
-    int at = (int)(pre + incl) - mine;
-    for (int u = 0; u < kPerCells; ++u) {
-      const int cell = tid + u * kThreads;
-      const uint32_t n = c.tab[cell];
-      if (!n) continue;
-      const float s = c.cell_score(cell);
-      const u64 q = mass_of(s, m);
-      reinterpret_cast<uint4*>(c.cl)[at] = pack_class(key_of(s), n, (uint32_t)cell, q);
-      ++at;
-    }
-    c.n_cl = (int)tot;
-    __syncthreads();
-  }
-  mark(3);  // (the count table has served: the selection histograms take its place)
 
   KeptSet kept{0u, 0x7fffffff};
   int token = -1;
@@ -393,11 +395,43 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
       kept.tie_limit = nth_in_group(c, cut_group, (u64)cut_ties);
     }
   };
-
   // per-class raw thresholds of a score bound (see cand_thresholds), for the walks that only
   // need the few tokens at or above a key
   CandCtx bound_ctx{nullptr, nullptr, nullptr, nullptr, small + 8, nullptr};
   int* low_id = small + 3;
+  // what the draw found: a member of one class (cell, its size, the n-th by ascending id)
+  int draw_cell = -1;
+  u64 draw_members = 0, draw_nth = 0;
+  bool token_known = false;
+
+  {
+  // ---- the row's non-empty classes, each with its key and mass computed once ---------------
+  // Thread t owns classes t, t + kThreads, ... (the populated value range spreads evenly over
+  // the threads) and writes its entries back to back; the order is fixed by the counts alone.
+  {
+    constexpr int kPerCells = kCells / kThreads;
+    int mine = 0;
+#pragma unroll 4
+    for (int u = 0; u < kPerCells; ++u) mine += c.tab[tid + u * kThreads] != 0;
+    const u64 incl = warp_scan_u64((u64)mine);
+    u64 pre, pre_unused, tot, tot_unused;
+    block_warp_prefix2(*c.x, shfl_u64(incl, 31), 0, pre, pre_unused, tot, tot_unused);
+    int at = (int)(pre + incl) - mine;
+    if (clocks && tid == 0) clocks[26] = clock64();
+    for (int u = 0; u < kPerCells; ++u) {
+      const int cell = tid + u * kThreads;
+      const uint32_t n = c.tab[cell];
+      if (!n) continue;
+      const float s = c.cell_score(cell);
+      const u64 q = mass_of(s, m);
+      reinterpret_cast<uint4*>(c.cl)[at] = pack_class(key_of(s), n, (uint32_t)cell, q);
+      ++at;
+    }
+    c.n_cl = (int)tot;
+    __syncthreads();
+  }
+  mark(3);  // (the count table has served: the selection histograms take its place)
+
   if (c.greedy) {
     // arg max with penalties: the lowest id among the tokens whose score key is the maximum
     if (tid == 0) *low_id = side_key == max_key ? side_arg : 0x7fffffff;
@@ -477,7 +511,11 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
     q_kept = mass;
     mark(6);
 
-    // ---- draw --------------------------------------------------------------------------
+  }
+  }
+
+  // ---- draw ------------------------------------------------------------------------------
+  if (!c.greedy) {
     if (q_kept == 0) {
       status |= 1;
       token = any_side ? side_arg : 0;
@@ -498,62 +536,82 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
       best = block_max_u64(*c.x, best);
       token = (int)(~(uint32_t)(best & 0xffffffffu));
     } else {
-      // Inverse CDF over exact integer masses in the order: classes above the cut (by class
-      // index), the tie group at the cut (its lowest ids), side elements above the cut (by id).
-      const Philox4 r = philox4x32_10(0u, 0u, 0u, 0u, (uint32_t)P.seed, (uint32_t)(P.seed >> 32));
-      const u64 r64 = ((u64)r.v[0] << 32) | r.v[1];
-      const u64 target = __umul64hi(r64, q_kept);
-      // classes above the cut in the order (thread, step): thread t owns entries t, t + kThreads, ...
-      u64 chunk = 0;
-      for_each_class(c, [&](const ClassEntry& e) { if (e.key > kept.cut_key) chunk += e.w; });
-      const u64 incl = warp_scan_u64(chunk);
-      u64 pre, pre_unused, q_cells, tot_unused;
-      block_warp_prefix2(*c.x, shfl_u64(incl, 31), 0, pre, pre_unused, q_cells, tot_unused);
-      mark(12);
-      // the group at the cut key: cut_ties members when top-p split it, else all of them
-      u64 group_kept = cut_ties >= 0 ? (u64)cut_ties : 0;
-      u64 q_cut = 0;
-      if (cut_ties < 0) {
-        // cut by top-k / min-p / nothing: everything at the cut key is kept; count it
-        u64 gc = 0, gm = 0;
-        for_each_class(c, [&](const ClassEntry& e) { if (e.key == kept.cut_key) gc += e.cnt; });
-        for_each_side3(c, [&](int, float s) { if (key_of(s) == kept.cut_key) gc += 1; });
-        block_sum2(*c.x, gc, gm);
-        group_kept = gc;
-      }
-      q_cut = mass_of(score_of(kept.cut_key), m);
-      const u64 q_group = group_kept * q_cut;
-      mark(13);
-      if (target < q_cells) {
-        if (tid == 0) c.x->bcast[5] = 0;
-        __syncthreads();
-        u64 run = pre + incl - chunk;
-        if (run <= target && target < run + chunk) {
-          bool done = false;
-          for (int i = tid; i < c.n_cl && !done; i += kThreads) {
-            const ClassEntry e = c.class_at(i);
-            if (e.key <= kept.cut_key) continue;
-            if (e.w && target < run + e.w) {
-              c.x->bcast[3] = e.cnt;
-              c.x->bcast[4] = (target - run) / e.q + 1;
-              c.x->bcast[5] = (u64)e.cell + 1;
-              done = true;
-            }
-            run += e.w;
-          }
+      {
+        // Inverse CDF over exact integer masses in the order: classes above the cut (by class
+        // index), the tie group at the cut (its lowest ids), side elements above the cut (by id).
+        const Philox4 r = philox4x32_10(0u, 0u, 0u, 0u, (uint32_t)P.seed, (uint32_t)(P.seed >> 32));
+        const u64 r64 = ((u64)r.v[0] << 32) | r.v[1];
+        const u64 target = __umul64hi(r64, q_kept);
+        // classes above the cut in the order (thread, step): thread t owns entries t, t + kThreads, ...
+        u64 chunk = 0;
+        for_each_class(c, [&](const ClassEntry& e) { if (e.key > kept.cut_key) chunk += e.w; });
+        const u64 incl = warp_scan_u64(chunk);
+        u64 pre, pre_unused, q_cells, tot_unused;
+        block_warp_prefix2(*c.x, shfl_u64(incl, 31), 0, pre, pre_unused, q_cells, tot_unused);
+        mark(12);
+        // the group at the cut key: cut_ties members when top-p split it, else all of them
+        u64 group_kept = cut_ties >= 0 ? (u64)cut_ties : 0;
+        u64 q_cut = 0;
+        if (cut_ties < 0) {
+          // cut by top-k / min-p / nothing: everything at the cut key is kept; count it
+          u64 gc = 0, gm = 0;
+          for_each_class(c, [&](const ClassEntry& e) { if (e.key == kept.cut_key) gc += e.cnt; });
+          for_each_side3(c, [&](int, float s) { if (key_of(s) == kept.cut_key) gc += 1; });
+          block_sum2(*c.x, gc, gm);
+          group_kept = gc;
         }
-        __syncthreads();
-        const int cell = (int)c.x->bcast[5] - 1;
-        const u64 members = c.x->bcast[3], nth = c.x->bcast[4];
-        __syncthreads();
-        mark(14);
+        q_cut = mass_of(score_of(kept.cut_key), m);
+        const u64 q_group = group_kept * q_cut;
+        mark(13);
+        if (target < q_cells) {
+          if (tid == 0) c.x->bcast[5] = 0;
+          __syncthreads();
+          u64 run = pre + incl - chunk;
+          if (run <= target && target < run + chunk) {
+            bool done = false;
+            for (int i = tid; i < c.n_cl && !done; i += kThreads) {
+              const ClassEntry e = c.class_at(i);
+              if (e.key <= kept.cut_key) continue;
+              if (e.w && target < run + e.w) {
+                c.x->bcast[3] = e.cnt;
+                c.x->bcast[4] = (target - run) / e.q + 1;
+                c.x->bcast[5] = (u64)e.cell + 1;
+                done = true;
+              }
+              run += e.w;
+            }
+          }
+          __syncthreads();
+          draw_cell = (int)c.x->bcast[5] - 1;
+          draw_members = c.x->bcast[3];
+          draw_nth = c.x->bcast[4];
+          __syncthreads();
+          if (draw_cell < 0) { token = any_side ? side_arg : 0; status |= 1; token_known = true; }
+        } else if (target < q_cells + q_group) {
+          need_cut_group();
+          const u64 nth = q_cut ? (target - q_cells) / q_cut + 1 : 1;
+          token = nth_in_group(c, cut_group, nth);  // the kept members are the lowest ids
+          if (token == 0x7fffffff) { token = any_side ? side_arg : 0; status |= 1; }
+          token_known = true;
+        } else {
+          SideDrawFill3 fill{&c, kept.cut_key};
+          Selection sd = descend_local<true>(c, fill, 0u, target - q_cells - q_group + 1, -1.0f, 0, 1, 0x7FFu);
+          if (sd.ok) token = (int)(~sd.key);
+          else { token = any_side ? side_arg : 0; status |= 1; }
+          token_known = true;
+        }
+      }
+      mark(14);
+      if (!token_known) {
+        // a uniformly chosen member of ONE class (not of other classes that share its key):
+        // large classes by rejection (about vocab / members scattered probes, which a lone CTA
+        // issues slowly), classes of up to kV3ListCap tokens by one scan of the row
+        const int cell = draw_cell;
+        const u64 members = draw_members, nth = draw_nth;
         if (clocks && tid == 0) clocks[15] = members;
         if (cell >= 0) {
           Group g{key_of(c.cell_score(cell)), -1, -1, -1};
           if (cell < kV3Bins) g.cell0 = cell; else if (cell < 2 * kV3Bins) g.cell1 = cell; else g.cell2 = cell;
-          // only this class, not other members that share its key: large classes by rejection
-          // (about vocab / members scattered probes, which a lone CTA issues slowly), classes
-          // of up to kV3ListCap tokens by one scan of the row
           if (members > (u64)kV3ListCap) {
             const u64 per_round = ((u64)c.vocab + members - 1) / members;  // probes for ~63 % success
             const int trials = (int)min((u64)kRandomTrials, max(1ull, (per_round + kThreads - 1) / kThreads));
@@ -570,16 +628,6 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
           }
         }
         if (token < 0 || token == 0x7fffffff) { token = any_side ? side_arg : 0; status |= 1; }
-      } else if (target < q_cells + q_group) {
-        need_cut_group();
-        const u64 nth = q_cut ? (target - q_cells) / q_cut + 1 : 1;
-        token = nth_in_group(c, cut_group, nth);  // the kept members are the lowest ids
-        if (token == 0x7fffffff) { token = any_side ? side_arg : 0; status |= 1; }
-      } else {
-        SideDrawFill3 fill{&c, kept.cut_key};
-        Selection sd = descend_local<true>(c, fill, 0u, target - q_cells - q_group + 1, -1.0f, 0, 1, 0x7FFu);
-        if (sd.ok) token = (int)(~sd.key);
-        else { token = any_side ? side_arg : 0; status |= 1; }
       }
     }
   }
@@ -588,7 +636,10 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
   // ---- D. log-probabilities -------------------------------------------------------------
   float log_z = 0.f;
   if (P.n_logprobs >= 0) {
-    log_z = (float)(log((double)q_kept) - (double)kMassShift * 0.6931471805599453);
+    if (tid == 0) c.x->bcast[6] = (u64)__float_as_uint((float)(log((double)q_kept) - (double)kMassShift * 0.6931471805599453));
+    __syncthreads();
+    log_z = __uint_as_float((uint32_t)c.x->bcast[6]);
+    __syncthreads();
     if (tid == 0 && token >= 0 && token < a.vocab)
       out->logprob = (c.element_score(token, c.logits[token], c.class_of(token)) - m) - log_z;
     int n_want = min(P.n_logprobs, a.vocab);

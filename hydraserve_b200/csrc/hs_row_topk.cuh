@@ -631,15 +631,7 @@ __device__ FinishOut finish_impl(Exchange& x, const u64* cand, u64* mass, int n,
       const u64 packed = ((u64)__float_as_uint(ratio) << 32) | (uint32_t)(~(uint32_t)id);
       best = packed > best ? packed : best;
     }
-    if (WARP) {
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) {
-        const u64 o = shfl_xor_u64(best, d);
-        best = o > best ? o : best;
-      }
-    } else {
-      best = block_max_u64(x, best);
-    }
+    best = WARP ? warp_max_u64(best) : block_max_u64(x, best);
     r.token = (int)(~(uint32_t)(best & 0xffffffffu));
   } else {
     const Philox4 ph = philox4x32_10(0u, 0u, 0u, 0u, (uint32_t)P.seed, (uint32_t)(P.seed >> 32));

@@ -47,7 +47,7 @@ constexpr int kV3ListCap = 128;               // members resolved by sorting
 constexpr int kV3ScanCap = 1024;              // ids one class scan can hold (in the gather and list buffers)
 constexpr int kV3RareCap = 512;               // out-of-window tokens remembered before a sweep
 constexpr int kV3SideShared = 1024;           // side-list entries kept in shared memory (else global scratch)
-constexpr int kV3PhaseSlots = 16;
+constexpr int kV3PhaseSlots = 32;
 constexpr int kSplitCap = 4096;               // candidate entries one CTA of a split row can hand over
 
 struct V3Entry {
@@ -135,7 +135,7 @@ __host__ __device__ inline LayoutV3 layout_v3() {
   }
   l.side = take(sizeof(int2) * kV3SideShared);
   l.rare = take(sizeof(int2) * kV3RareCap);
-  l.small = take(sizeof(int) * 16);
+  l.small = take(sizeof(int) * 32);
   l.total = off;
   return l;
 }
@@ -281,8 +281,10 @@ __device__ Selection descend_local(Ctx3& c, Fill& fill, uint32_t lo_key, u64 tar
     for (int b = tid; b < kBins; b += kThreads) { h.ent[b] = 0; h.cnt[b] = 0; h.l0[b] = 0; h.l1[b] = 0; h.l2[b] = 0; }
     if (tid == 0) c.x->bcast[7] = 0;
     __syncthreads();
+    if (c.dbg && tid == 0 && BY_MASS && level == first_level) c.dbg[16] = clock64();
     fill(level, shift, bits, prefix, lo_key, add);
     __syncthreads();
+    if (c.dbg && tid == 0 && BY_MASS && level == first_level) c.dbg[17] = clock64();
     constexpr int kPer = kBins / kThreads;
     const int hi = kBins - 1 - kPer * tid;
     u64 c_sum = 0, m_sum = 0;
@@ -297,7 +299,12 @@ __device__ Selection descend_local(Ctx3& c, Fill& fill, uint32_t lo_key, u64 tar
     if (level == first_level) {
       sel.total_cnt = ta;
       sel.total_mass = tb;
-      if (BY_MASS && top_p >= 0.0f) sel.target = top_p_target(tb, top_p);
+      if (BY_MASS && top_p >= 0.0f) {
+        // (double precision: one thread works it out for all)
+        if (tid == 0) c.x->bcast[6] = top_p_target(tb, top_p);
+        __syncthreads();
+        sel.target = c.x->bcast[6];
+      }
     }
     const u64 want = sel.target - (BY_MASS ? sel.above_mass : sel.above_cnt);
     {
@@ -341,6 +348,7 @@ __device__ Selection descend_local(Ctx3& c, Fill& fill, uint32_t lo_key, u64 tar
     prefix = (prefix << bits) | bin;
     sel.levels = level + 1;
     __syncthreads();
+    if (c.dbg && tid == 0 && BY_MASS && level == first_level) c.dbg[18] = clock64();
     if (stop_pop && level < 2 && entries <= stop_pop) break;  // few enough members to sort
   }
   sel.prefix = prefix;
@@ -407,6 +415,7 @@ __device__ int gather_members3(Ctx3& c, uint32_t lo_key, int levels, uint32_t pr
     if (slot < kV3ListCap) c.gbuf[slot] = V3Entry{e.key, -1, e.cnt, e.cell, e.q};
   });
   __syncthreads();
+  if (c.dbg && tid == 0) c.dbg[20] = clock64();
   const int n = min(*c.gbuf_n, kV3ListCap);
   if (tid < n) {
     const V3Entry mine = c.gbuf[tid];
@@ -429,8 +438,10 @@ __device__ int gather_members3(Ctx3& c, uint32_t lo_key, int levels, uint32_t pr
 template <bool BY_MASS>
 __device__ Selection resolve3(Ctx3& c, Selection sel, uint32_t lo_key) {
   if (!sel.ok || sel.levels == 3) return sel;
+  if (c.dbg && threadIdx.x == 0 && BY_MASS) { c.dbg[19] = clock64(); c.dbg[23] = (unsigned long long)sel.levels; }
   const int n = gather_members3(c, lo_key, sel.levels, sel.prefix);
   const int tid = threadIdx.x;
+  if (c.dbg && tid == 0 && BY_MASS) { c.dbg[21] = clock64(); c.dbg[24] = (unsigned long long)n; }
   u64 a = 0, b = 0;
   if (tid < n) { a = c.list[tid].cnt; b = a * c.list[tid].q; }
   const u64 ia = warp_scan_u64(a), ib = warp_scan_u64(b);
