@@ -311,7 +311,7 @@ def run_ours(args, world, rank, local_rank):
     batch, vocab = w.batch, w.vocab
     history_len = max((int(h.size) for h in w.histories), default=0)
     sampler = _device.DeviceSampler(device, vocab_max=vocab, batch_max=batch, resident_slots=batch,
-                                    hist_cap=min(vocab, max(history_len, 4096)))
+                                    hist_cap=min(vocab, max(history_len, 4096) + args.steps + args.warmup + 64))
     lib, handle = sampler.lib, sampler.handle
 
     # device-resident histograms, one slot per row (request); built once, outside the timed region

@@ -67,6 +67,12 @@ struct hs_sampler {
   int force_cluster = 0;
   int force_general = 0;  // route bf16 rows through the general (fp32-stage) kernel too
   int force_split = 0;    // CTAs per candidate row (0 = chosen per call)
+  int force_csplit = 0;   // CTAs per counting row (0 = chosen per call)
+  int ctab_tables = 0;    // count tables the hand-over scratch holds
+  uint32_t* ctab = nullptr;   // [ctab_tables, kCells]
+  int2* crare = nullptr;      // [ctab_tables, kV3RareCap]
+  int* crare_n = nullptr;     // [ctab_tables]
+  int* count_ticket = nullptr;  // [batch_max]
   int resident_bf16 = 0;  // CTAs of the bf16 kernel that can be resident at once: CTAs per SM x SMs
   int2* side_pair = nullptr;  // [resident_bf16, side_cap] side lists too long for shared memory
   hs::ClassPacked* clist = nullptr;  // [resident_bf16, kCells] class list of the row a CTA works on
@@ -191,9 +197,18 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
     int split = h->force_split ? h->force_split : (h->resident_bf16 + batch - 1) / batch;
     split = std::max(1, std::min(split, kMaxSplit));
     if (vocab < split * 2 * hs::kSample) split = 1;
+    // counting rows: as many CTAs per row as the hand-over scratch allows (the whole batch may
+    // be counting rows), so that a small batch still spreads over the SMs
+    int csplit = 1;
+    if (vocab >= 65536) {
+      if ((long long)batch * 4 <= h->ctab_tables) csplit = 4;
+      else if ((long long)batch * 2 <= h->ctab_tables) csplit = 2;
+    }
+    if (h->force_csplit && (long long)batch * h->force_csplit <= h->ctab_tables) csplit = h->force_csplit;
     hs::RowV3Args a3{a, h->clist, h->side_pair, h->side_cap, h->resident_bf16, h->scratch_busy, h->phase_clocks,
+                     csplit, h->ctab, h->crare, h->crare_n, h->count_ticket,
                      split, h->split_lists, h->split_n, h->split_ticket, batch};
-    const unsigned grid = (unsigned)batch * (unsigned)(1 + split);
+    const unsigned grid = (unsigned)batch * (unsigned)(csplit + split);
     hs::row_kernel_bf16<<<grid, hs::kThreads, hs::bf16_kernel_smem(), stream>>>(a3);
     HS_CUDA(h, cudaGetLastError());
     h->launches += 1;
@@ -258,6 +273,7 @@ int launch_append(hs_sampler* h, const int32_t* tokens, const int32_t* offsets, 
 void release(hs_sampler* h) {
   cudaFree(h->pool.pairs); cudaFree(h->pool.cls); cudaFree(h->pool.heavy); cudaFree(h->pool.n_heavy); cudaFree(h->pool.n); cudaFree(h->pool.pos);
   cudaFree(h->side_pair); cudaFree(h->clist); cudaFree(h->scratch_busy);
+  cudaFree(h->ctab); cudaFree(h->crare); cudaFree(h->crare_n); cudaFree(h->count_ticket);
   cudaFree(h->split_lists); cudaFree(h->split_n); cudaFree(h->split_ticket);
   if (h->ev_done) cudaEventDestroy(h->ev_done);
   cudaFree(h->phase_clocks);
@@ -428,6 +444,12 @@ int hs_create_ex(int device, int vocab_max, int slots_max, int hist_cap, int bat
   ok = ok && dmalloc(h, &h->side_pair, (size_t)h->resident_bf16 * h->side_cap * sizeof(int2));
   ok = ok && dmalloc(h, &h->clist, (size_t)h->resident_bf16 * hs::kCells * sizeof(hs::ClassPacked));
   ok = ok && dmalloc(h, &h->scratch_busy, (size_t)h->resident_bf16 * sizeof(int));
+  // hand-over scratch of counting rows split over several CTAs: two tables per resident CTA
+  h->ctab_tables = 2 * h->resident_bf16;
+  ok = ok && dmalloc(h, &h->ctab, (size_t)h->ctab_tables * hs::kCells * sizeof(uint32_t));
+  ok = ok && dmalloc(h, &h->crare, (size_t)h->ctab_tables * hs::kV3RareCap * sizeof(int2));
+  ok = ok && dmalloc(h, &h->crare_n, (size_t)h->ctab_tables * sizeof(int));
+  ok = ok && dmalloc(h, &h->count_ticket, (size_t)batch_max * sizeof(int));
   ok = ok && cudaEventCreateWithFlags(&h->ev_done, cudaEventDisableTiming) == cudaSuccess;
   ok = ok && dmalloc(h, &h->split_lists, (size_t)batch_max * kMaxSplit * hs::kSplitCap * sizeof(unsigned long long));
   ok = ok && dmalloc(h, &h->split_n, (size_t)batch_max * kMaxSplit * sizeof(int));
@@ -442,6 +464,7 @@ int hs_create_ex(int device, int vocab_max, int slots_max, int hist_cap, int bat
   if (!ok) return bail(HS_ERR_CUDA);
   ok = ok && cudaMemset(h->split_ticket, 0, (size_t)batch_max * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMemset(h->scratch_busy, 0, (size_t)h->resident_bf16 * sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMemset(h->count_ticket, 0, (size_t)batch_max * sizeof(int)) == cudaSuccess;
   ok = ok && cudaMemset(h->pool.n, 0, st * sizeof(int32_t)) == cudaSuccess;
   ok = ok && cudaMemset(h->pool.n_heavy, 0, st * sizeof(int32_t)) == cudaSuccess;
   ok = ok && cudaMemset(h->pool.cls, 0, st * (size_t)h->pool.cls_stride * sizeof(uint32_t)) == cudaSuccess;
@@ -699,6 +722,11 @@ int hs_debug_set(hs_sampler* h, int what, int value) {
   if (what == 0) {
     if (value != 0 && value != 1 && value != 2 && value != 4) return fail(h, HS_ERR_INVALID, "split must be 0, 1, 2 or 4");
     h->force_split = value;
+    return HS_OK;
+  }
+  if (what == 1) {
+    if (value != 0 && value != 1 && value != 2 && value != 4) return fail(h, HS_ERR_INVALID, "counting split must be 0, 1, 2 or 4");
+    h->force_csplit = value;
     return HS_OK;
   }
   return fail(h, HS_ERR_INVALID, "unknown setting");

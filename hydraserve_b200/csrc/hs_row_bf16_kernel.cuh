@@ -33,8 +33,11 @@ __device__ __noinline__ void count_chunk_slow(uint32_t* tab, int* rare_n, int2* 
   }
 }
 
-// The counting path for one row (also: plain arg max of a row in a mixed batch).
-__device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* smem_raw, int row_index) {
+// The counting path for one row (also: plain arg max of a row in a mixed batch).  part < 0:
+// this CTA counts the whole row.  part >= 0: the row's tokens are counted by args.csplit CTAs,
+// each a contiguous range; every part leaves its count table and rare list in global scratch,
+// and the part that arrives last (a ticket) adds the others' to its own and goes on alone.
+__device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* smem_raw, int row_index, int part) {
   const RowKernelArgs& a = args.base;
   const LayoutV3 lay = layout_v3();
   Ctx3 c;
@@ -83,6 +86,7 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
 
   // ---- plain greedy rows of a mixed batch: arg max only -----------------------------------
   if (c.greedy && !penalised && P.n_logprobs < 0) {
+    if (part > 0) return;  // (one CTA walks the whole row)
     u64 best = 0;
     auto consider = [&](uint32_t raw, int id) {
       const u64 packed = ((u64)key_of(canonical(__uint_as_float(raw << 16))) << 32) | (uint32_t)(~(uint32_t)id);
@@ -122,52 +126,33 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
     n_heavy = a.pool.n_heavy[P.slot];
     if (tid < a.pool.unique_cap) hv_q = load_now_s32(a.pool.heavy + (size_t)P.slot * a.pool.unique_cap + tid);
   }
-  // ask L2 for the whole row (and its class map) now: the counting loop then waits for L2,
-  // not for HBM, and the later walks over the row find it there
+  // this CTA's range of 8-token chunks [chunk_lo, chunk_hi); the last part also takes the
+  // tokens after the last whole chunk
+  const int n8_row = c.vec ? c.vocab / 8 : 0;
+  const int parts = part < 0 ? 1 : args.csplit;
+  const int my_part = part < 0 ? 0 : part;
+  const int per_part = (n8_row + parts - 1) / parts;
+  const int chunk_lo = min(my_part * per_part, n8_row), chunk_hi = min(chunk_lo + per_part, n8_row);
+  const bool last_part = my_part == parts - 1;
+  // ask L2 for the range (and its class map) now: the counting loop then waits for L2, not for
+  // HBM, and the later walks over the row find it there
   if (c.vec) {
     constexpr uint32_t kPiece = 16384;
-    const size_t row_bytes = ((size_t)c.vocab * 2) & ~(size_t)15;
-    for (size_t at = (size_t)tid * kPiece; at < row_bytes; at += (size_t)kThreads * kPiece)
-      prefetch_l2_bulk(reinterpret_cast<const unsigned char*>(c.logits) + at,
-                       (uint32_t)min((size_t)kPiece, row_bytes - at));
-    if (c.cls && (reinterpret_cast<uintptr_t>(c.cls) & 15u) == 0) {
-      const size_t cls_bytes = ((size_t)c.vocab / 4) & ~(size_t)15;
+    const unsigned char* base = reinterpret_cast<const unsigned char*>(c.logits) + (size_t)chunk_lo * 16;
+    const size_t bytes = (size_t)(chunk_hi - chunk_lo) * 16;
+    for (size_t at = (size_t)tid * kPiece; at < bytes; at += (size_t)kThreads * kPiece)
+      prefetch_l2_bulk(base + at, (uint32_t)min((size_t)kPiece, bytes - at));
+    if (c.cls && (reinterpret_cast<uintptr_t>(c.cls) & 15u) == 0 && (chunk_lo & 7) == 0) {
+      const unsigned char* cbase = reinterpret_cast<const unsigned char*>(c.cls) + (size_t)chunk_lo * 2;
+      const size_t cls_bytes = ((size_t)(chunk_hi - chunk_lo) * 2) & ~(size_t)15;
       for (size_t at = (size_t)tid * kPiece; at < cls_bytes; at += (size_t)kThreads * kPiece)
-        prefetch_l2_bulk(reinterpret_cast<const unsigned char*>(c.cls) + at,
-                         (uint32_t)min((size_t)kPiece, cls_bytes - at));
+        prefetch_l2_bulk(cbase + at, (uint32_t)min((size_t)kPiece, cls_bytes - at));
     }
   }
   // small[16..18] / [19..21]: highest (+ 1) / lowest non-empty cell per count class; [22]: lowest side key
   if (tid < 32) small[tid] = (tid >= 19 && tid <= 22) ? -1 : 0;
   if (tid == 0) c.x->bcast[5] = 0;  // highest side element, (key, ~id)
   __syncthreads();
-  // Global scratch (class list, long side lists) is held per RESIDENT CTA: a CTA claims one of
-  // the n_scratch sets (as many as CTAs can be resident, so one is always free), starting its
-  // search at the pair of its SM, and gives it back at the end.
-  if (tid == 0) {
-    unsigned smid;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    int got = -1;
-    for (int k = 0; k < 2 * args.n_scratch && got < 0; ++k) {
-      const int at = (int)((2u * smid + (unsigned)k) % (unsigned)args.n_scratch);
-      if (atomicCAS(&args.scratch_busy[at], 0, 1) == 0) got = at;
-    }
-    small[15] = got;
-  }
-  __syncthreads();
-  const int scratch = small[15];
-  if (scratch < 0) {  // cannot happen while n_scratch covers the resident CTAs; fail the row, do not wait
-    if (tid == 0) { out->token = 0; out->status = 128; out->n_top = 0; out->n_kept = 0; }
-    return;
-  }
-  auto release_scratch = [&]() {
-    __syncthreads();
-    if (tid == 0) { __threadfence(); atomicExch(&args.scratch_busy[scratch], 0); }
-  };
-  c.s_pair = args.s_pair + (size_t)scratch * args.s_cap;
-  c.s_cap = args.s_cap;
-  c.cl = args.clist + (size_t)scratch * kCells;
-
   for (int i = tid; i < kCells; i += kThreads) c.tab[i] = 0;
   __syncthreads();
   n_heavy = min(n_heavy, min(a.pool.unique_cap, args.s_cap));
@@ -186,7 +171,6 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
         if (slot < kV3RareCap) rare[slot] = make_int2(id, (int)(raw | ((uint32_t)cc << 16)));
       }
     };
-    const int n8 = c.vec ? c.vocab / 8 : 0;
     const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
     const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
     // Eight tokens at a time without a branch per token.  Per 32-bit word (two tokens):
@@ -240,8 +224,8 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
     // loop runs without bounds checks; what is left over is taken chunk by chunk.
     constexpr int kInFlight = 2;  // 128-bit loads per thread and batch
     constexpr int kStride = kInFlight * kThreads;
-    const int n_full = n8 / kStride;
-    int i0 = tid;
+    const int n_full = (chunk_hi - chunk_lo) / kStride;
+    int i0 = chunk_lo + tid;
     if (hv_pair.x >= 0 && hv_pair.x < c.vocab) hv_raw = load_now_u16(c.logits + hv_pair.x);
     if (n_full > 0) {
       uint4 w[kInFlight], wn[kInFlight];
@@ -268,11 +252,80 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
         i0 += kStride;
       }
     }
-    for (int i = i0; i < n8; i += kThreads) take_chunk(__ldcg(src4 + i), cls16p ? (uint32_t)__ldcg(cls16p + i) : 0u, i);
-    for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) count_one(c.logits[id], c.class_of(id), id);
+    for (int i = i0; i < chunk_hi; i += kThreads) take_chunk(__ldcg(src4 + i), cls16p ? (uint32_t)__ldcg(cls16p + i) : 0u, i);
+    if (last_part)
+      for (int id = n8_row * 8 + tid; id < c.vocab; id += kThreads) count_one(c.logits[id], c.class_of(id), id);
   }
   __syncthreads();
+  if (parts > 1) {
+    // Hand this part's counts over: table and rare list to global scratch, then a ticket.  The
+    // part that draws the last ticket adds the other parts' to its own and goes on; the
+    // others are done.  Nobody waits for anybody.
+    const size_t mine = (size_t)c.row * parts + my_part;
+    uint32_t* gtab = args.ctab + mine * kCells;
+    for (int i = tid; i < kCells / 4; i += kThreads)
+      reinterpret_cast<uint4*>(gtab)[i] = reinterpret_cast<const uint4*>(c.tab)[i];
+    const int nr = *rare_n;
+    for (int t = tid; t < min(nr, kV3RareCap); t += kThreads) args.crare[mine * kV3RareCap + t] = rare[t];
+    if (tid == 0) args.crare_n[mine] = nr;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) small[14] = atomicAdd(&args.count_ticket[c.row], 1);
+    __syncthreads();
+    if (small[14] != parts - 1) return;
+    __threadfence();
+    if (tid == 0) args.count_ticket[c.row] = 0;
+    for (int g = 0; g < parts; ++g) {
+      if (g == my_part) continue;
+      const size_t theirs = (size_t)c.row * parts + g;
+      const uint4* src = reinterpret_cast<const uint4*>(args.ctab + theirs * kCells);
+      for (int i = tid; i < kCells / 4; i += kThreads) {
+        const uint4 v = __ldcg(src + i);
+        uint4 t = reinterpret_cast<uint4*>(c.tab)[i];
+        t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+        reinterpret_cast<uint4*>(c.tab)[i] = t;
+      }
+      // their rare list goes behind this CTA's (a total beyond the capacity is swept up below)
+      const int ng = ((volatile int*)args.crare_n)[theirs];
+      __syncthreads();
+      const int have = *rare_n;
+      __syncthreads();
+      if (have <= kV3RareCap && ng <= kV3RareCap) {
+        for (int t = tid; t < ng; t += kThreads)
+          if (have + t < kV3RareCap) rare[have + t] = __ldcg(args.crare + theirs * kV3RareCap + t);
+      }
+      if (tid == 0) *rare_n = have + ng;
+      __syncthreads();
+    }
+  }
   mark(1);
+  // Global scratch (class list, long side lists) is held per RESIDENT CTA: a CTA claims one of
+  // the n_scratch sets (as many as CTAs can be resident, so one is always free), starting its
+  // search at the pair of its SM, and gives it back at the end.
+  if (tid == 0) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    int got = -1;
+    for (int k = 0; k < 2 * args.n_scratch && got < 0; ++k) {
+      const int at = (int)((2u * smid + (unsigned)k) % (unsigned)args.n_scratch);
+      if (atomicCAS(&args.scratch_busy[at], 0, 1) == 0) got = at;
+    }
+    small[15] = got;
+  }
+  __syncthreads();
+  const int scratch = small[15];
+  if (scratch < 0) {  // cannot happen while n_scratch covers the resident CTAs; fail the row, do not wait
+    if (tid == 0) { out->token = 0; out->status = 128; out->n_top = 0; out->n_kept = 0; }
+    return;
+  }
+  auto release_scratch = [&]() {
+    __syncthreads();
+    if (tid == 0) { __threadfence(); atomicExch(&args.scratch_busy[scratch], 0); }
+  };
+  c.s_pair = args.s_pair + (size_t)scratch * args.s_cap;
+  c.s_cap = args.s_cap;
+  c.cl = args.clist + (size_t)scratch * kCells;
+
 
   // ---- B. the side list: tokens with history count >= 3, and values outside the bin window
   // It is walked by every selection, so it lives in shared memory when it fits.
@@ -605,14 +658,14 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
       if (!token_known) {
         // a uniformly chosen member of ONE class (not of other classes that share its key):
         // large classes by rejection (about vocab / members scattered probes, which a lone CTA
-        // issues slowly), classes of up to kV3ListCap tokens by one scan of the row
+        // issues slowly), classes of up to kV3RejectMin tokens by one scan of the row
         const int cell = draw_cell;
         const u64 members = draw_members, nth = draw_nth;
         if (clocks && tid == 0) clocks[15] = members;
         if (cell >= 0) {
           Group g{key_of(c.cell_score(cell)), -1, -1, -1};
           if (cell < kV3Bins) g.cell0 = cell; else if (cell < 2 * kV3Bins) g.cell1 = cell; else g.cell2 = cell;
-          if (members > (u64)kV3ListCap) {
+          if (members > (u64)kV3RejectMin) {
             const u64 per_round = ((u64)c.vocab + members - 1) / members;  // probes for ~63 % success
             const int trials = (int)min((u64)kRandomTrials, max(1ull, (per_round + kThreads - 1) / kThreads));
             // a class the scan can hold gets a few rounds, then the scan; a larger one many
@@ -886,21 +939,26 @@ __host__ __device__ inline size_t bf16_kernel_smem() {
 }
 
 // One CTA per work item, two CTAs resident per SM; the hardware hands out the items in grid
-// order, long ones first: [0, batch) = row r on the counting path (a CTA whose row is not a
-// counting row leaves at once), then batch * split items = part p of row r on the candidate
-// path (likewise).  No CTA waits for another.
+// order, long ones first: batch * csplit items = part p of row r on the counting path (a CTA
+// whose row is not a counting row leaves at once), then batch * split items = part p of row r
+// on the candidate path (likewise).  No CTA waits for another.
 __global__ void __launch_bounds__(kThreads, 2) row_kernel_bf16(const RowV3Args args) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int item = blockIdx.x;
-  int row = item;
-  bool count = item < args.batch;
-  if (!count) row = (item - args.batch) / args.split;
+  const int n_count = args.batch * args.csplit;
+  bool count = item < n_count;
+  // counting items are laid out part-major, so that the parts of one row start on different SMs
+  int row = count ? item % args.batch : (item - n_count) / args.split;
+  int part = count ? item / args.batch : (item - n_count) % args.split;
   if (is_candidate_row(args.base.params[row], args.base.vocab) == count) return;  // the other path's row
   if (!count) {
-    count = cand_part(args, smem_raw, row, (item - args.batch) % args.split);
+    if (!cand_part(args, smem_raw, row, part)) return;
     __syncthreads();
+    part = -1;  // more ties than a candidate list holds: this CTA counts the whole row
+  } else if (args.csplit == 1) {
+    part = -1;
   }
-  if (count) count_row(args, smem_raw, row);
+  count_row(args, smem_raw, row, part);
 }
 
 }  // namespace hs

@@ -43,11 +43,12 @@ constexpr int kV3Half = 3072;                 // 24 binades x 128 mantissas
 constexpr int kV3Bins = 2 * kV3Half;          // per count class
 constexpr int kCells = 3 * kV3Bins;           // count classes 0, 1, 2
 constexpr uint32_t kV3Base = 113u << 7;       // smallest binned magnitude: 2^-14
-constexpr int kV3ListCap = 128;               // members resolved by sorting
+constexpr int kV3ListCap = 256;               // members resolved by sorting
+constexpr int kV3RejectMin = 128;             // classes of up to this many tokens are found by scanning the row, larger ones by rejection
 constexpr int kV3ScanCap = 1024;              // ids one class scan can hold (in the gather and list buffers)
 constexpr int kV3RareCap = 512;               // out-of-window tokens remembered before a sweep
 constexpr int kV3SideShared = 1024;           // side-list entries kept in shared memory (else global scratch)
-constexpr int kV3PhaseSlots = 32;
+constexpr int kV3PhaseSlots = 64;
 constexpr int kSplitCap = 4096;               // candidate entries one CTA of a split row can hand over
 
 struct V3Entry {
@@ -100,6 +101,11 @@ struct RowV3Args {
   int n_scratch;       // scratch sets: as many as CTAs of the kernel can be resident at once
   int* scratch_busy;   // [n_scratch] 1 while a CTA holds the set
   unsigned long long* phase_clocks;  // [batch, kV3PhaseSlots] or null
+  int csplit;                        // CTAs per row on the counting path (1, 2 or 4)
+  uint32_t* ctab;                    // [batch, csplit, kCells] count tables handed over by the parts of a row
+  int2* crare;                       // [batch, csplit, kV3RareCap] their rare lists
+  int* crare_n;                      // [batch, csplit]
+  int* count_ticket;                 // [batch] arrival counter (returns to 0)
   int split;                         // CTAs per row on the candidate path
   unsigned long long* split_lists;   // [batch, split, kSplitCap] candidate lists of the row's CTAs
   int* split_n;                      // [batch, split] their lengths
@@ -292,8 +298,10 @@ __device__ Selection descend_local(Ctx3& c, Fill& fill, uint32_t lo_key, u64 tar
     for (int u = 0; u < kPer; ++u) { c_sum += h.cnt[hi - u]; m_sum += h.mass(hi - u); }
     const u64 ia = warp_scan_u64(c_sum);
     const u64 ib = warp_scan_u64(m_sum);
+    if (c.dbg && tid == 0 && BY_MASS && level == first_level) c.dbg[30] = clock64();
     u64 pa, pb, ta, tb;
     block_warp_prefix2(*c.x, shfl_u64(ia, 31), shfl_u64(ib, 31), pa, pb, ta, tb);
+    if (c.dbg && tid == 0 && BY_MASS && level == first_level) c.dbg[31] = clock64();
     u64 ex_cnt = pa + ia - c_sum;
     u64 ex_mass = pb + ib - m_sum;
     if (level == first_level) {
@@ -306,6 +314,7 @@ __device__ Selection descend_local(Ctx3& c, Fill& fill, uint32_t lo_key, u64 tar
         sel.target = c.x->bcast[6];
       }
     }
+    if (c.dbg && tid == 0 && BY_MASS && level == first_level) c.dbg[32] = clock64();
     const u64 want = sel.target - (BY_MASS ? sel.above_mass : sel.above_cnt);
     {
       const u64 ex = BY_MASS ? ex_mass : ex_cnt;
@@ -447,6 +456,7 @@ __device__ Selection resolve3(Ctx3& c, Selection sel, uint32_t lo_key) {
   const u64 ia = warp_scan_u64(a), ib = warp_scan_u64(b);
   u64 pa, pb, tc, tm;
   block_warp_prefix2(*c.x, shfl_u64(ia, 31), shfl_u64(ib, 31), pa, pb, tc, tm);
+  if (c.dbg && tid == 0 && BY_MASS) c.dbg[34] = clock64();
   const u64 want = sel.target - (BY_MASS ? sel.above_mass : sel.above_cnt);
   if (tid == 0) c.x->bcast[7] = 0;
   __syncthreads();
@@ -462,6 +472,7 @@ __device__ Selection resolve3(Ctx3& c, Selection sel, uint32_t lo_key) {
     return sel;
   }
   const uint32_t key = (uint32_t)c.x->bcast[0];
+  if (c.dbg && tid == 0 && BY_MASS) c.dbg[35] = clock64();
   u64 ac = 0, am = 0, bc = 0, bm = 0;
   if (tid < n) {
     if (c.list[tid].key > key) { ac = a; am = b; }
@@ -477,6 +488,7 @@ __device__ Selection resolve3(Ctx3& c, Selection sel, uint32_t lo_key) {
   sel.bin_cnt = bc;
   sel.bin_mass = bm;
   __syncthreads();
+  if (c.dbg && tid == 0 && BY_MASS) c.dbg[36] = clock64();
   return sel;
 }
 
@@ -653,10 +665,10 @@ __device__ int nth_in_group(Ctx3& c, const Group& g, u64 n) {
 
 // Token id of the n-th (1-based, ascending id) token of ONE class (count class and
 // one-value bin `cell`), for classes of at most kV3ScanCap tokens, or -1 when the row has
-// no 16-byte aligned view or the class turns out larger.  One pass over the row: a class
-// is one bf16 bit pattern, so eight tokens are screened with four XORs and a zero-half
-// test, and only words with a matching half look at the class map.  The ids found (kept in
-// the gather and list buffers, which are contiguous) are ranked among themselves.
+// no 16-byte aligned view or too many tokens hold the class's value.  One pass over the row: a
+// class is one bf16 bit pattern, so eight tokens are screened with four XORs and a zero-half
+// test; the ids of all tokens with that value are kept (in the gather and list buffers, which
+// are contiguous), those of other count classes dropped, and the rest ranked among themselves.
 static_assert(kV3ScanCap * sizeof(int) <= 2 * kV3ListCap * sizeof(V3Entry), "scan ids fit the two buffers");
 __device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
   if (!c.vec) return -1;
@@ -678,54 +690,56 @@ __device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
   const int n8 = c.vocab / 8;
   const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
   auto zero_half = [](uint32_t x) { return (x - 0x00010001u) & ~x & 0x80008000u; };
-  auto probe = [&](int id, uint32_t r, uint32_t klass) {
-    if (r == raw && (int)klass == cc) {
+  // Every token that holds the value is noted, whatever its count class (the value alone is
+  // held by tokens of every class); the classes of the few that were noted are looked up
+  // afterwards, one thread per token, instead of along with every chunk of the row.
+  auto probe = [&](int id, uint32_t r, uint32_t) {
+    if (r == raw) {
       const int slot = atomicAdd(c.gbuf_n, 1);
       if (slot < kV3ScanCap) ids[slot] = id;
     }
   };
-  // The class map is read along with the logits: the value alone is held by tokens of every
-  // count class, and looking a class up only on a hit costs a dependent scattered read per
-  // hit, serialised inside each warp.
-  const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
-  // two batches of loads: the next is on its way while this one is screened
+  // two batches of loads: the next is on its way while this one is screened (past L1: with this
+  // kernel's shared memory there is too little of it for the loads in flight)
   constexpr int kBatch = 4;
   uint4 w[kBatch], wn[kBatch];
-  uint32_t cl[kBatch], cn[kBatch];
-  auto fetch = [&](uint4 (&dw)[kBatch], uint32_t (&dc)[kBatch], int i0) {
+  auto fetch = [&](uint4 (&dw)[kBatch], int i0) {
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
       const int i = i0 + u * kThreads;
-      // past L1: with this kernel's shared memory there is too little of it for the loads in flight
       dw[u] = i < n8 ? __ldcg(src4 + i) : make_uint4(~vv, ~vv, ~vv, ~vv);
-      dc[u] = (cls16p && i < n8) ? (uint32_t)__ldcg(cls16p + i) : 0u;
     }
   };
-  fetch(w, cl, tid);
+  fetch(w, tid);
   for (int i0 = tid; i0 < n8; i0 += kBatch * kThreads) {
-    fetch(wn, cn, i0 + kBatch * kThreads);
+    fetch(wn, i0 + kBatch * kThreads);
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
       const uint32_t z = zero_half(w[u].x ^ vv) | zero_half(w[u].y ^ vv) | zero_half(w[u].z ^ vv) |
                          zero_half(w[u].w ^ vv);
       if (z) {
         const int id = 8 * (i0 + u * kThreads);
-        probe(id, w[u].x & 0xffffu, cl[u] & 3u); probe(id + 1, w[u].x >> 16, (cl[u] >> 2) & 3u);
-        probe(id + 2, w[u].y & 0xffffu, (cl[u] >> 4) & 3u); probe(id + 3, w[u].y >> 16, (cl[u] >> 6) & 3u);
-        probe(id + 4, w[u].z & 0xffffu, (cl[u] >> 8) & 3u); probe(id + 5, w[u].z >> 16, (cl[u] >> 10) & 3u);
-        probe(id + 6, w[u].w & 0xffffu, (cl[u] >> 12) & 3u); probe(id + 7, w[u].w >> 16, (cl[u] >> 14) & 3u);
+        probe(id, w[u].x & 0xffffu, 0u); probe(id + 1, w[u].x >> 16, 0u);
+        probe(id + 2, w[u].y & 0xffffu, 0u); probe(id + 3, w[u].y >> 16, 0u);
+        probe(id + 4, w[u].z & 0xffffu, 0u); probe(id + 5, w[u].z >> 16, 0u);
+        probe(id + 6, w[u].w & 0xffffu, 0u); probe(id + 7, w[u].w >> 16, 0u);
       }
     }
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u) { w[u] = wn[u]; cl[u] = cn[u]; }
+    for (int u = 0; u < kBatch; ++u) w[u] = wn[u];
   }
-  for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) probe(id, c.logits[id], (uint32_t)c.class_of(id));
+  for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) probe(id, c.logits[id], 0u);
   if (tid == 0) c.x->bcast[6] = 0;
   __syncthreads();
   const int found = *c.gbuf_n;
   if (found <= kV3ScanCap) {
+    // tokens of other count classes drop out (an id beyond every real one ranks last)
+    for (int t = tid; t < found; t += kThreads)
+      if (c.class_of(ids[t]) != cc) ids[t] = 0x7fffffff;
+    __syncthreads();
     for (int t = tid; t < found; t += kThreads) {
       const int mine = ids[t];
+      if (mine == 0x7fffffff) continue;
       u64 rank = 1;
       for (int j = 0; j < found; ++j) rank += ids[j] < mine ? 1 : 0;
       if (rank == n) c.x->bcast[6] = (u64)mine + 1;

@@ -239,6 +239,10 @@ class DeviceSampler:
         """CTAs per candidate row (tests and tuning); 0 = chosen per call."""
         _lib.check(self.lib, self.handle, self.lib.hs_debug_set(self.handle, 0, int(split)), "hs_debug_set")
 
+    def set_count_split(self, split: int) -> None:
+        """CTAs per counting row (tests and tuning); 0 = chosen per call."""
+        _lib.check(self.lib, self.handle, self.lib.hs_debug_set(self.handle, 1, int(split)), "hs_debug_set")
+
     def prepare_logits(self, logits):
         torch = self.torch
         if logits.device != self.device:

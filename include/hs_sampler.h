@@ -219,7 +219,8 @@ int hs_query(hs_sampler* h, int what, int vocab, int dtype);
  * slots per row of the last launch; this copies batch x 16 counters to out_host
  * (synchronises the device). */
 int hs_debug_phase_clocks(hs_sampler* h, int batch, unsigned long long* out_host);
-/* Tests and tuning.  what = 0: CTAs per candidate row, value 1, 2 or 4 (0 = chosen per call). */
+/* Tests and tuning.  what = 0: CTAs per candidate row, what = 1: CTAs per counting row; value 1, 2
+ * or 4 (0 = chosen per call). */
 int hs_debug_set(hs_sampler* h, int what, int value);
 
 #ifdef __cplusplus

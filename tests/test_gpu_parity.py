@@ -108,6 +108,19 @@ def test_rows_match_checker(sampler, name):
     report.assert_ok(max_sensitive_fraction=0.5, name=name)
 
 
+@pytest.mark.parametrize("parts", [2, 4])
+@pytest.mark.parametrize("name", ["small_bf16", "small_odd_bf16", "config2_8rows", "config3_4rows", "config4_8rows"])
+def test_counting_rows_split_over_several_ctas(sampler, name, parts):
+    """A counting row whose tokens are counted by 2 or 4 CTAs (each a range; the last to
+    arrive adds the others' count tables to its own) gives the same results as one CTA."""
+    sampler.set_count_split(parts)
+    try:
+        compare_case(sampler, cases.build(name)).assert_ok(max_sensitive_fraction=0.5,
+                                                           name=f"{name} (counted by {parts} CTAs per row)")
+    finally:
+        sampler.set_count_split(0)
+
+
 @pytest.fixture(scope="module")
 def general_sampler(built_library):
     """A sampler that sends bf16 rows through the general (fp32-resident) kernel as well."""
