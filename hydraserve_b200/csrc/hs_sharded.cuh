@@ -81,9 +81,27 @@ __global__ void __launch_bounds__(kThreads, 2) shard_partial_kernel(const ShardA
   __syncthreads();
   const float m = n > 0 ? score_of(cand_key(L.cand[0])) : 0.f;
   // soft-max denominator of the whole slice, relative to the slice maximum (exact integer mass)
+  // (the slice was streamed a moment ago and sits in L2: eight tokens per 128-bit load, their
+  // count classes from one 16-bit load)
   u64 z = 0, unused = 0;
-  for (int id = tid; id < c.vocab; id += kThreads)
-    z += mass_of(c.element_score(id, c.logits[id], c.class_of(id)), m);
+  {
+    const int n8 = c.vec ? c.vocab / 8 : 0;
+    const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
+    const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
+    for (int i = tid; i < n8; i += kThreads) {
+      const uint4 w = __ldcg(src4 + i);
+      const uint32_t cl = cls16p ? (uint32_t)cls16p[i] : 0u;
+      const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const uint32_t raw = (words[q >> 1] >> (16 * (q & 1))) & 0xffffu;
+        const int cc = (int)((cl >> (2 * q)) & 3u);
+        z += mass_of(c.element_score(8 * i + q, raw, cc), m);
+      }
+    }
+    for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads)
+      z += mass_of(c.element_score(id, c.logits[id], c.class_of(id)), m);
+  }
   block_sum2(*c.x, z, unused);
   for (int i = tid; i < HS_SHARD_CAND; i += kThreads) {
     rec->ids[i] = i < n ? cand_id(L.cand[i]) + args.vocab_offset : -1;

@@ -14,6 +14,7 @@ and the process-wide sampler of a GPU is never destroyed while a call is inside 
 from __future__ import annotations
 
 import ctypes as C
+import itertools
 import os
 import threading
 from collections import OrderedDict
@@ -264,20 +265,29 @@ class DeviceSampler:
         _lib.check(self.lib, self.handle, st, "hs_slots_reset")
 
     def append_tokens(self, slots, token_arrays, vocab: int) -> None:
-        """Count token_arrays[i] into slot slots[i]."""
+        """Count token_arrays[i] (a numpy array or any sequence of ints) into slot slots[i].
+        Ids outside [0, vocab) are ignored, as in the reference (sampling.py:108)."""
         if len(slots) == 0:
             return
-        lens = [int(a.size) for a in token_arrays]
-        if max(lens) == 0:
+        lens = [len(a) for a in token_arrays]
+        total = sum(lens)
+        if total == 0:
             return
+        if all(not isinstance(a, np.ndarray) for a in token_arrays):
+            # short Python sequences (the one token a request gained since its last step): one pass
+            flat = np.fromiter(itertools.chain.from_iterable(token_arrays), dtype=np.int64, count=total)
+        else:
+            flat = np.concatenate([np.asarray(a, dtype=np.int64).reshape(-1) for a in token_arrays])
+        # the device ignores ids outside [0, vocab); -1 stands for everything that is
+        flat = np.where((flat < 0) | (flat >= vocab), -1, flat).astype(np.int32)
         offsets = np.zeros(len(slots) + 1, dtype=np.int32)
         np.cumsum(lens, out=offsets[1:])
-        flat = np.concatenate(token_arrays).astype(np.int32, copy=False)
-        d_tok = self._to_device(flat)
-        d_off = self._to_device(offsets)
-        d_slots = self._to_device(np.asarray(slots, dtype=np.int32))
-        st = self.lib.hs_slots_append(self.handle, d_tok.data_ptr(), d_off.data_ptr(),
-                                      d_slots.data_ptr(), len(slots), vocab, max(lens),
+        # one staged copy for tokens, offsets and slot numbers
+        packed = np.concatenate([flat, offsets, np.asarray(slots, dtype=np.int32)])
+        d = self._to_device(packed)
+        base = d.data_ptr()
+        st = self.lib.hs_slots_append(self.handle, base, base + 4 * flat.size,
+                                      base + 4 * (flat.size + offsets.size), len(slots), vocab, max(lens),
                                       self._stream())
         _lib.check(self.lib, self.handle, st, "hs_slots_append")
 
@@ -306,7 +316,7 @@ class DeviceSampler:
             entry[1] = 0
         if n > entry[1]:
             tail = history[entry[1]:] if hasattr(history, "__getitem__") else tuple(history)[entry[1]:]
-            appends.append((entry[0], history_array(tail, vocab)))
+            appends.append((entry[0], tail))
             entry[1] = n
         return entry[0]
 
@@ -395,12 +405,11 @@ class DeviceSampler:
                     in_batch = {r for r in request_ids if r is not None}
                 slot = self._slot_for_request(request_ids[i], history, vocab, resets, appends, in_batch)
             if slot < 0:
-                tokens = history_array(history, vocab)
-                if tokens.size == 0:
+                if len(history) == 0:
                     continue
                 slot = self.scratch_base + i
                 resets.append(slot)
-                appends.append((slot, tokens))
+                appends.append((slot, history if isinstance(history, (np.ndarray, list, tuple)) else tuple(history)))
             slots[i] = slot
         self.reset_slots(resets)
         self.append_tokens([s for s, _ in appends], [t for _, t in appends], vocab)
