@@ -54,8 +54,8 @@ METRIC = "sampled rows/sec"
 UNIT = "rows/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one step's kernel on config 3, from the ncu
-# capture summarised in profiles/bf16_row_kernel_config3.md (None until one is taken)
-NCU_DRAM_BYTES_PER_STEP = {3: None}
+# capture summarised in profiles/bf16_row_kernel_config3.md
+NCU_DRAM_BYTES_PER_STEP = {3: 189_446_912}
 
 WORKLOADS = {
     2: dict(batch=64, vocab=151_936, history=4096, sets=8, scaling="weak",

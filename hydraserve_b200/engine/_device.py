@@ -32,6 +32,7 @@ _MASK63 = np.uint64(2**63 - 1)
 STATUS_FELL_BACK, STATUS_APPEND_FAILED, STATUS_NEEDS_GENERAL = 1, 2, 4
 STATUS_SHARD_CUT = 16 | 32
 STATUS_BAD_SLOT = 64
+STATUS_NO_SCRATCH = 128
 
 
 def mixed_seed(seed: int, step: int) -> int:
@@ -589,7 +590,7 @@ def sample_batch(logits, histories, params, steps, request_ids, all_plain_greedy
                 return PackedSamples(records, [-1] * batch, vocab)
             return tuple(TokenSample(int(t)) for t in tokens.tolist())
         records, _ = sampler.sample(logits, histories, params, steps, request_ids)
-    bad = records["status"] & (STATUS_APPEND_FAILED | STATUS_NEEDS_GENERAL | STATUS_BAD_SLOT)
+    bad = records["status"] & (STATUS_APPEND_FAILED | STATUS_NEEDS_GENERAL | STATUS_BAD_SLOT | STATUS_NO_SCRATCH)
     if bad.any():
         raise _lib.SamplerError(f"sampler reported status {int(bad.max())} for row {int(np.argmax(bad != 0))}")
     if packed:

@@ -78,7 +78,9 @@ typedef struct hs_row_out {
                             the bf16 kernel keeps (values outside 2^-14 <= |x| < 2^10, history counts >= 3):
                             sample the row again with HS_SAMPLE_GENERAL_KERNEL; 8: fewer top log-probabilities
                             found than expected; 16 / 32: a vocabulary shard's record was cut short;
-                            64: params.slot is not a slot of this sampler (the row got no penalties) */
+                            64: params.slot is not a slot of this sampler (the row got no penalties);
+                            128: the row found no free scratch block (more CTAs resident than the
+                            sampler was sized for: an internal error, the row is not sampled) */
   int32_t n_kept;        /* size of the final candidate set */
   int32_t n_after_topk;  /* candidates left by top-k (ties at the k-th value kept) */
   int32_t n_after_minp;  /* ... and by min-p */
