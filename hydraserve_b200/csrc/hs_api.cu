@@ -68,6 +68,8 @@ struct hs_sampler {
   int force_general = 0;  // route bf16 rows through the general (fp32-stage) kernel too
   int force_split = 0;    // CTAs per candidate row (0 = chosen per call)
   int force_csplit = 0;   // CTAs per counting row (0 = chosen per call)
+  int token_draw = 1;     // near-flat counting rows draw by rejection on tokens
+  int prefetch_row = 1;   // counting rows prefetch their row into L2 before the selections
   int ctab_tables = 0;    // count tables the hand-over scratch holds
   uint32_t* ctab = nullptr;   // [ctab_tables, kCells]
   int2* crare = nullptr;      // [ctab_tables, kV3RareCap]
@@ -191,6 +193,8 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
   a.logits = logits; a.dtype = dtype; a.row_stride = row_stride; a.vocab = vocab; a.slice = 0;
   a.params = params; a.out = out; a.noise = noise; a.scores_out = scores_out; a.gstage = nullptr;
   a.pool = h->pool; a.flags = flags & HS_SAMPLE_APPEND_TOKEN; a.tokens_out = tokens_out;
+  a.prefetch_row = h->prefetch_row;
+  a.token_draw = h->token_draw;
   if (dtype == HS_DTYPE_BF16 && !h->force_general && !(flags & HS_SAMPLE_GENERAL_KERNEL)) {
     // One launch: a CTA per counting row and per part of a candidate row, two resident per
     // SM.  Small batches: several CTAs stream each candidate row so that every SM has work.
@@ -727,6 +731,14 @@ int hs_debug_set(hs_sampler* h, int what, int value) {
   if (what == 1) {
     if (value != 0 && value != 1 && value != 2 && value != 4) return fail(h, HS_ERR_INVALID, "counting split must be 0, 1, 2 or 4");
     h->force_csplit = value;
+    return HS_OK;
+  }
+  if (what == 3) {
+    h->token_draw = value ? 1 : 0;
+    return HS_OK;
+  }
+  if (what == 2) {
+    h->prefetch_row = value;
     return HS_OK;
   }
   return fail(h, HS_ERR_INVALID, "unknown setting");

@@ -50,6 +50,7 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
   int2* rare = reinterpret_cast<int2*>(smem_raw + lay.rare);  // (id, raw bits | count class << 16)
   int* small = reinterpret_cast<int*>(smem_raw + lay.small);
   c.gbuf_n = small;
+  c.step_n = small + 24;
   int* rare_n = small + 1;
   int* side_n = small + 2;
   const int tid = threadIdx.x;
@@ -136,7 +137,7 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
   const bool last_part = my_part == parts - 1;
   // ask L2 for the range (and its class map) now: the counting loop then waits for L2, not for
   // HBM, and the later walks over the row find it there
-  if (c.vec) {
+  if (c.vec && a.prefetch_row != 3) {
     constexpr uint32_t kPiece = 16384;
     const unsigned char* base = reinterpret_cast<const unsigned char*>(c.logits) + (size_t)chunk_lo * 16;
     const size_t bytes = (size_t)(chunk_hi - chunk_lo) * 16;
@@ -231,6 +232,8 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
       uint4 w[kInFlight], wn[kInFlight];
       uint32_t cl[kInFlight], cn[kInFlight];
 #pragma unroll
+      const bool keep = a.prefetch_row == 2;
+      const u64 keep_policy = l2_keep_policy();
       for (int u = 0; u < kInFlight; ++u) {
         w[u] = __ldcg(src4 + i0 + u * kThreads);  // past L1: almost all of it is shared memory here
         cl[u] = cls16p ? (uint32_t)__ldcg(cls16p + i0 + u * kThreads) : 0u;
@@ -241,7 +244,7 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
         if (it + 1 < n_full) {
 #pragma unroll
           for (int u = 0; u < kInFlight; ++u) {
-            wn[u] = __ldcg(src4 + i0 + kStride + u * kThreads);
+            wn[u] = keep ? load_keep(src4 + i0 + kStride + u * kThreads, keep_policy) : __ldcg(src4 + i0 + kStride + u * kThreads);
             cn[u] = cls16p ? (uint32_t)__ldcg(cls16p + i0 + kStride + u * kThreads) : 0u;
           }
         }
@@ -414,13 +417,14 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
   __syncthreads();
   side_best = c.x->bcast[5];
   mark(2);
-  uint32_t cells_key = 0, min_key = reinterpret_cast<unsigned*>(small)[22];
+  uint32_t cells_key = 0, min_key = reinterpret_cast<unsigned*>(small)[22], cells_min_key = 0xffffffffu;
 #pragma unroll
   for (int k = 0; k < 3; ++k) {
     const uint32_t t = reinterpret_cast<unsigned*>(small)[16 + k], l = reinterpret_cast<unsigned*>(small)[19 + k];
     if (t) cells_key = max(cells_key, key_of(c.cell_score((int)t - 1)));
-    if (l != 0xffffffffu) min_key = min(min_key, key_of(c.cell_score((int)l)));
+    if (l != 0xffffffffu) cells_min_key = min(cells_min_key, key_of(c.cell_score((int)l)));
   }
+  min_key = min(min_key, cells_min_key);
   if (clocks && tid == 0) clocks[25] = clock64();
   const uint32_t side_key = (uint32_t)(side_best >> 32);
   const int side_arg = (int)(~(uint32_t)(side_best & 0xffffffffu));
@@ -484,6 +488,16 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
     __syncthreads();
   }
   mark(3);  // (the count table has served: the selection histograms take its place)
+  // Whatever comes last -- a member of the drawn class, the lowest ids of a tie group, the top
+  // log-probabilities' ids, a penalised arg max -- walks or probes the row again, and by then
+  // other rows have pushed it out of L2: ask for it now, while the selections run.
+  if (c.vec && a.prefetch_row == 1) {
+    constexpr uint32_t kPiece = 16384;
+    const size_t row_bytes = ((size_t)c.vocab * 2) & ~(size_t)15;
+    for (size_t at = (size_t)tid * kPiece; at < row_bytes; at += (size_t)kThreads * kPiece)
+      prefetch_l2_bulk(reinterpret_cast<const unsigned char*>(c.logits) + at,
+                       (uint32_t)min((size_t)kPiece, row_bytes - at));
+  }
 
   if (c.greedy) {
     // arg max with penalties: the lowest id among the tokens whose score key is the maximum
@@ -532,7 +546,17 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
     }
     mark(5);
     if (P.top_p < 1.0f) {
+      {
+        // first level over the scores' own range (from the lowest class that can be kept to the
+        // row maximum) instead of the key's top bits: one level separates a near-flat row
+        const float lo = score_of(max(kept.cut_key, cells_min_key == 0xffffffffu ? min_key : cells_min_key));
+        const float range = m - lo;
+        c.lin = range > 0.f && range < 3.0e38f;
+        c.lin_lo = lo;
+        c.lin_scale = c.lin ? __fdiv_rn(2047.5f, range) : 0.f;
+      }
       Selection sp = select_union3<true, true>(c, kept.cut_key, 0, P.top_p);
+      c.lin = false;
       n_minp = sp.total_cnt;
       if (sp.ok && sp.bin_cnt > 0) {
         const u64 qv = sp.bin_mass / sp.bin_cnt;  // every token at the cut key has the same mass
@@ -589,7 +613,27 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
       best = block_max_u64(*c.x, best);
       token = (int)(~(uint32_t)(best & 0xffffffffu));
     } else {
-      {
+      // Near-flat rows: rejection on tokens, when one round is all but sure to accept.
+      bool by_tokens = false;
+      if (a.token_draw && mass_to_float(q_kept) * (float)(kTokenTrials * kThreads) >= 4.0f * (float)c.vocab) {
+        bool group_hit;
+        const int t = draw_by_token_rejection(c, kept, tie_split, cut_ties > 0 ? (u64)cut_ties : 0ull, cut_group_cnt, P.seed, 4,
+                                              group_hit);
+        if (t >= 0) {
+          token = t;
+          if (group_hit) {
+            // one of the kept members of the group the cut splits: its lowest ids
+            need_cut_group();
+            const Philox4 r = philox4x32_10(0u, 0u, 0u, 4u, (uint32_t)P.seed, (uint32_t)(P.seed >> 32));
+            const u64 nth = 1 + __umul64hi(((u64)r.v[0] << 32) | r.v[1], (u64)cut_ties);
+            token = nth_in_group(c, cut_group, nth);
+            if (token == 0x7fffffff) { token = any_side ? side_arg : 0; status |= 1; }
+          }
+          token_known = true;
+          by_tokens = true;
+        }
+      }
+      if (!by_tokens) {
         // Inverse CDF over exact integer masses in the order: classes above the cut (by class
         // index), the tie group at the cut (its lowest ids), side elements above the cut (by id).
         const Philox4 r = philox4x32_10(0u, 0u, 0u, 0u, (uint32_t)P.seed, (uint32_t)(P.seed >> 32));
@@ -670,9 +714,9 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
             const int trials = (int)min((u64)kRandomTrials, max(1ull, (per_round + kThreads - 1) / kThreads));
             // a class the scan can hold gets a few rounds, then the scan; a larger one many
             token = random_in_class(c, cell, trials, P.seed, members <= (u64)kV3ScanCap ? 4 : 32);
-            if (token < 0 && members <= (u64)kV3ScanCap) token = nth_in_small_class(c, cell, nth);
+            if (token < 0 && members <= (u64)kV3ScanCap) token = nth_in_small_class(c, cell, nth, members);
           } else {
-            token = nth_in_small_class(c, cell, nth);
+            token = nth_in_small_class(c, cell, nth, members);
           }
           if (token < 0) {
             Group only = g;

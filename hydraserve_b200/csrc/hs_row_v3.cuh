@@ -165,6 +165,7 @@ struct Ctx3 {
   V3Entry* gbuf;     // gather buffer
   V3Entry* list;     // sorted members
   int* gbuf_n;
+  int* step_n = nullptr;  // two counters the early-exit scan alternates between
   int row, vocab;
   unsigned long long* dbg = nullptr;
   int lo, hi;                    // token range this CTA streams in the candidate path (lo a multiple of 8)
@@ -184,6 +185,15 @@ struct Ctx3 {
   float T, rp, pp, fp;
   bool greedy;
   float m;
+  // Linear bucketing of the first level of a mass descent (see descend_local): bucket =
+  // (score - lin_lo) * lin_scale, which grows with the key like the key's own top bits do,
+  // but spreads a row whose scores lie close together over all buckets.
+  bool lin = false;
+  float lin_lo = 0.f, lin_scale = 0.f;
+  __device__ __forceinline__ uint32_t lin_bucket(uint32_t key) const {
+    const float t = (hs::score_of(key) - lin_lo) * lin_scale;
+    return (uint32_t)min(max(__float2int_rz(t), 0), kBins - 1);
+  }
 
   __device__ __forceinline__ float score_of_value(float v) const {
     return greedy ? canonical(v) : canonical(__fdiv_rn(v, T));
@@ -308,8 +318,11 @@ __device__ Selection descend_local(Ctx3& c, Fill& fill, uint32_t lo_key, u64 tar
       sel.total_cnt = ta;
       sel.total_mass = tb;
       if (BY_MASS && top_p >= 0.0f) {
-        // (double precision: one thread works it out for all)
-        if (tid == 0) c.x->bcast[6] = top_p_target(tb, top_p);
+        // (double precision, slow: the lanes of one warp try neighbouring candidates at once)
+        if (tid < 32) {
+          const u64 t = top_p_target_warp(tb, top_p);
+          if (tid == 0) c.x->bcast[6] = t;
+        }
         __syncthreads();
         sel.target = c.x->bcast[6];
       }
@@ -359,6 +372,13 @@ __device__ Selection descend_local(Ctx3& c, Fill& fill, uint32_t lo_key, u64 tar
     __syncthreads();
     if (c.dbg && tid == 0 && BY_MASS && level == first_level) c.dbg[18] = clock64();
     if (stop_pop && level < 2 && entries <= stop_pop) break;  // few enough members to sort
+    if (c.lin && level == 0) {
+      // the linear buckets did not separate the row: once more, by the key's own bits
+      c.lin = false;
+      sel.above_cnt = sel.above_mass = 0;
+      prefix = prefix0;
+      level = first_level - 1;
+    }
   }
   sel.prefix = prefix;
   sel.key = sel.levels == 3 ? prefix : (prefix << (sel.levels == 1 ? 21 : 10));
@@ -374,13 +394,14 @@ struct UnionFill3 {
                                              uint32_t lo_key, const Add& add) const {
     const uint32_t mask = (1u << bits) - 1u;
     auto ok = [&](uint32_t k) { return k >= lo_key && (level == 0 || (k >> (shift + bits)) == prefix); };
+    const bool lin = c->lin && level == 0;
     for_each_side3(*c, [&](int, float s) {
       const uint32_t k = key_of(s);
       const bool valid = ok(k);
-      add(valid, (k >> shift) & mask, 1u, (WITH_MASS && valid) ? mass_of(s, c->m) : 0ull);
+      add(valid, lin ? c->lin_bucket(k) : (k >> shift) & mask, 1u, (WITH_MASS && valid) ? mass_of(s, c->m) : 0ull);
     });
     for_each_class(*c, [&](const ClassEntry& e) {
-      add(ok(e.key), (e.key >> shift) & mask, e.cnt, WITH_MASS ? e.w : 0ull);
+      add(ok(e.key), lin ? c->lin_bucket(e.key) : (e.key >> shift) & mask, e.cnt, WITH_MASS ? e.w : 0ull);
     });
   }
 };
@@ -408,8 +429,10 @@ __device__ int gather_members3(Ctx3& c, uint32_t lo_key, int levels, uint32_t pr
   if (tid == 0) *c.gbuf_n = 0;
   __syncthreads();
   const int drop = levels == 1 ? 21 : (levels == 2 ? 10 : 0);
+  const bool lin = c.lin && levels == 1;
   auto matches = [&](uint32_t k) {
     if (k < lo_key) return false;
+    if (lin) return c.lin_bucket(k) == prefix;
     return levels == 0 || (levels == 3 ? k == prefix : (k >> drop) == prefix);
   };
   for_each_side3(c, [&](int id, float s) {
@@ -473,13 +496,15 @@ __device__ Selection resolve3(Ctx3& c, Selection sel, uint32_t lo_key) {
   }
   const uint32_t key = (uint32_t)c.x->bcast[0];
   if (c.dbg && tid == 0 && BY_MASS) c.dbg[35] = clock64();
-  u64 ac = 0, am = 0, bc = 0, bm = 0;
-  if (tid < n) {
-    if (c.list[tid].key > key) { ac = a; am = b; }
-    if (c.list[tid].key == key) { bc = a; bm = b; }
+  // the list is sorted by key: what lies above the key's group and the group itself are read
+  // off the running sums at the group's two ends
+  if (tid < n && c.list[tid].key == key) {
+    if (tid == 0 || c.list[tid - 1].key != key) { c.x->bcast[1] = pa + ia - a; c.x->bcast[2] = pb + ib - b; }
+    if (tid == n - 1 || c.list[tid + 1].key != key) { c.x->bcast[3] = pa + ia; c.x->bcast[4] = pb + ib; }
   }
-  block_sum2(*c.x, ac, am);
-  block_sum2(*c.x, bc, bm);
+  __syncthreads();
+  const u64 ac = c.x->bcast[1], am = c.x->bcast[2];
+  const u64 bc = c.x->bcast[3] - ac, bm = c.x->bcast[4] - am;
   sel.key = key;
   sel.prefix = key;
   sel.levels = 3;
@@ -663,92 +688,127 @@ __device__ int nth_in_group(Ctx3& c, const Group& g, u64 n) {
   return result;
 }
 
-// Token id of the n-th (1-based, ascending id) token of ONE class (count class and
-// one-value bin `cell`), for classes of at most kV3ScanCap tokens, or -1 when the row has
-// no 16-byte aligned view or too many tokens hold the class's value.  One pass over the row: a
-// class is one bf16 bit pattern, so eight tokens are screened with four XORs and a zero-half
-// test; the ids of all tokens with that value are kept (in the gather and list buffers, which
-// are contiguous), those of other count classes dropped, and the rest ranked among themselves.
+// Token id of the n-th (1-based, ascending id) of the `members` tokens of ONE class (count
+// class and one-value bin `cell`), for classes of at most kV3ScanCap tokens, or -1 when the row
+// has no 16-byte aligned view.  The row is walked from the end that is nearer to the n-th
+// member, 16,384 tokens per step, and the walk stops with the step that reaches it: members are
+// spread evenly over the row, so on average a quarter of it is read.  A class is one bf16 bit
+// pattern and a normal number (the bin window holds neither zeros nor NaNs), so two tokens are
+// compared with it by one native bf16x2 equality per 32-bit word; a hit looks its count class
+// up in the 16 class bits that travel with its chunk.  The ids found (in the gather and list
+// buffers, which are contiguous) are ranked among themselves.
 static_assert(kV3ScanCap * sizeof(int) <= 2 * kV3ListCap * sizeof(V3Entry), "scan ids fit the two buffers");
-__device__ int nth_in_small_class(Ctx3& c, int cell, u64 n) {
-  if (!c.vec) return -1;
+// (Not inlined, and handed plain values instead of the row's context: inside the kernel's main
+// body its eight 128-bit registers in flight were spilled to local memory, which this kernel's
+// small L1 turns into round trips to L2 inside the loop.)
+struct ScanArgs {
+  const unsigned short* logits;
+  const uint32_t* cls;
+  int vocab;
+  int* ids;       // [kV3ScanCap]
+  int* slot_n;    // ids used
+  int* step_n;    // [2]
+  u64* result;    // id + 1 of the answer, or 0
+  unsigned long long* dbg;
+};
+__device__ __noinline__ void scan_small_class(const ScanArgs c, uint32_t raw, int cc, int n, int members) {
   const int tid = threadIdx.x;
-  const int cc = cell / kV3Bins;
-  const uint32_t raw = v3_raw_of_bin(cell - cc * kV3Bins);
   const uint32_t vv = raw | (raw << 16);
-  int* ids = reinterpret_cast<int*>(c.gbuf);
-  if (tid == 0) *c.gbuf_n = 0;
-  {
-    // the row may have left L2 since it was counted
-    constexpr uint32_t kPiece = 16384;
-    const size_t row_bytes = ((size_t)c.vocab * 2) & ~(size_t)15;
-    for (size_t at = (size_t)tid * kPiece; at < row_bytes; at += (size_t)kThreads * kPiece)
-      prefetch_l2_bulk(reinterpret_cast<const unsigned char*>(c.logits) + at,
-                       (uint32_t)min((size_t)kPiece, row_bytes - at));
-  }
+  const __nv_bfloat162 vv2 = *reinterpret_cast<const __nv_bfloat162*>(&vv);
+  int* ids = c.ids;
+  const bool forward = 2 * n <= members + 1;
+  const int need = forward ? n : members - n + 1;  // counted from the end the walk starts at
+  if (tid == 0) { *c.slot_n = 0; c.step_n[0] = 0; c.step_n[1] = 0; *c.result = 0; }
   __syncthreads();
+  if (c.dbg && tid == 0) c.dbg[40] = clock64();
   const int n8 = c.vocab / 8;
   const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
-  auto zero_half = [](uint32_t x) { return (x - 0x00010001u) & ~x & 0x80008000u; };
-  // Every token that holds the value is noted, whatever its count class (the value alone is
-  // held by tokens of every class); the classes of the few that were noted are looked up
-  // afterwards, one thread per token, instead of along with every chunk of the row.
-  auto probe = [&](int id, uint32_t r, uint32_t) {
-    if (r == raw) {
-      const int slot = atomicAdd(c.gbuf_n, 1);
-      if (slot < kV3ScanCap) ids[slot] = id;
-    }
+  const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
+  // Members found are counted in two counters that take turns step by step: after a step's
+  // barrier every thread reads that step's counter, which nobody adds to before the barrier
+  // after next, so all threads see the same running total and leave the walk together.
+  auto note = [&](int id, int parity) {
+    const int slot = atomicAdd(c.slot_n, 1);
+    if (slot < kV3ScanCap) ids[slot] = id;
+    atomicAdd(c.step_n + parity, 1);
   };
-  // two batches of loads: the next is on its way while this one is screened (past L1: with this
-  // kernel's shared memory there is too little of it for the loads in flight)
+  // the few tokens after the last whole chunk: first when walking backwards, last otherwise
+  auto tail = [&](int parity) {
+    for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads)
+      if ((uint32_t)c.logits[id] == raw && (c.cls ? (int)((c.cls[id >> 4] >> ((id & 15) * 2)) & 3u) : 0) == cc) note(id, parity);
+  };
+  if (!forward) tail(0);
   constexpr int kBatch = 4;
+  constexpr int kStep = kBatch * kThreads;  // chunks per step
+  const int n_steps = (n8 + kStep - 1) / kStep;
   uint4 w[kBatch], wn[kBatch];
-  auto fetch = [&](uint4 (&dw)[kBatch], int i0) {
+  uint32_t cl[kBatch], cn[kBatch];
+  // chunk u of step s for this thread (steps are numbered in walking order)
+  auto chunk_of = [&](int s, int u) { return (forward ? s : n_steps - 1 - s) * kStep + u * kThreads + tid; };
+  auto fetch = [&](uint4 (&dw)[kBatch], uint32_t (&dc)[kBatch], int s) {
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
-      const int i = i0 + u * kThreads;
-      dw[u] = i < n8 ? __ldcg(src4 + i) : make_uint4(~vv, ~vv, ~vv, ~vv);
+      const int i = chunk_of(s, u);
+      const bool in = s < n_steps && i < n8;
+      dw[u] = in ? __ldcg(src4 + i) : make_uint4(~vv, ~vv, ~vv, ~vv);
+      dc[u] = (in && cls16p) ? (uint32_t)__ldcg(cls16p + i) : 0u;
     }
   };
-  fetch(w, tid);
-  for (int i0 = tid; i0 < n8; i0 += kBatch * kThreads) {
-    fetch(wn, i0 + kBatch * kThreads);
+  fetch(w, cl, 0);
+  bool reached = false;
+  int total = 0, seen[2] = {0, 0};
+  for (int s = 0; s < n_steps; ++s) {
+    fetch(wn, cn, s + 1);
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
-      const uint32_t z = zero_half(w[u].x ^ vv) | zero_half(w[u].y ^ vv) | zero_half(w[u].z ^ vv) |
-                         zero_half(w[u].w ^ vv);
-      if (z) {
-        const int id = 8 * (i0 + u * kThreads);
-        probe(id, w[u].x & 0xffffu, 0u); probe(id + 1, w[u].x >> 16, 0u);
-        probe(id + 2, w[u].y & 0xffffu, 0u); probe(id + 3, w[u].y >> 16, 0u);
-        probe(id + 4, w[u].z & 0xffffu, 0u); probe(id + 5, w[u].z >> 16, 0u);
-        probe(id + 6, w[u].w & 0xffffu, 0u); probe(id + 7, w[u].w >> 16, 0u);
+      const uint32_t m0 = __heq2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].x), vv2);
+      const uint32_t m1 = __heq2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].y), vv2);
+      const uint32_t m2 = __heq2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].z), vv2);
+      const uint32_t m3 = __heq2_mask(*reinterpret_cast<const __nv_bfloat162*>(&w[u].w), vv2);
+      if (m0 | m1 | m2 | m3) {
+        const int id = 8 * chunk_of(s, u);
+        uint32_t hits = ((m0 & 1u) | ((m0 >> 15) & 2u)) | (((m1 & 1u) | ((m1 >> 15) & 2u)) << 2) |
+                        (((m2 & 1u) | ((m2 >> 15) & 2u)) << 4) | (((m3 & 1u) | ((m3 >> 15) & 2u)) << 6);
+        while (hits) {
+          const int q = __ffs(hits) - 1;
+          hits &= hits - 1;
+          if ((int)((cl[u] >> (2 * q)) & 3u) == cc) note(id + q, s & 1);
+        }
       }
     }
-#pragma unroll
-    for (int u = 0; u < kBatch; ++u) w[u] = wn[u];
-  }
-  for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) probe(id, c.logits[id], 0u);
-  if (tid == 0) c.x->bcast[6] = 0;
-  __syncthreads();
-  const int found = *c.gbuf_n;
-  if (found <= kV3ScanCap) {
-    // tokens of other count classes drop out (an id beyond every real one ranks last)
-    for (int t = tid; t < found; t += kThreads)
-      if (c.class_of(ids[t]) != cc) ids[t] = 0x7fffffff;
     __syncthreads();
-    for (int t = tid; t < found; t += kThreads) {
-      const int mine = ids[t];
-      if (mine == 0x7fffffff) continue;
-      u64 rank = 1;
-      for (int j = 0; j < found; ++j) rank += ids[j] < mine ? 1 : 0;
-      if (rank == n) c.x->bcast[6] = (u64)mine + 1;
+    {
+      const int now = c.step_n[s & 1];
+      total += now - seen[s & 1];
+      seen[s & 1] = now;
     }
+    if (total >= need) { reached = true; break; }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) { w[u] = wn[u]; cl[u] = cn[u]; }
+  }
+  if (forward && !reached) tail(0);
+  if (c.dbg && tid == 0) c.dbg[43] = clock64();
+  __syncthreads();
+  if (c.dbg && tid == 0) c.dbg[41] = clock64();
+  const int found = min(*c.slot_n, kV3ScanCap);
+  // every member on the near side of the last step's far end was noted: the one that `need - 1`
+  // others precede (follow, when walking backwards) is the answer
+  for (int t = tid; t < found; t += kThreads) {
+    const int mine = ids[t];
+    int before = 0;
+    for (int j = 0; j < found; ++j) before += (forward ? ids[j] < mine : ids[j] > mine) ? 1 : 0;
+    if (before + 1 == need) *c.result = (u64)mine + 1;
   }
   __syncthreads();
+  if (c.dbg && tid == 0) { c.dbg[42] = clock64(); c.dbg[44] = (unsigned long long)found; }
+}
+__device__ __forceinline__ int nth_in_small_class(Ctx3& c, int cell, u64 n, u64 members) {
+  if (!c.vec || members > (u64)kV3ScanCap || n < 1 || n > members) return -1;
+  const int cc = cell / kV3Bins;
+  const ScanArgs sa{c.logits, c.cls, c.vocab, reinterpret_cast<int*>(c.gbuf), c.gbuf_n, c.step_n, &c.x->bcast[6], c.dbg};
+  scan_small_class(sa, v3_raw_of_bin(cell - cc * kV3Bins), cc, (int)n, (int)members);
   const u64 hit = c.x->bcast[6];
   __syncthreads();
-  if (found > kV3ScanCap) return -1;
   return hit ? (int)(hit - 1) : 0x7fffffff;
 }
 
@@ -816,6 +876,59 @@ __device__ int random_in_class(Ctx3& c, int cell, int trials, uint64_t seed, int
       const int token = (int)c.x->bcast[6];
       __syncthreads();
       return token;
+    }
+  }
+  return -1;
+}
+
+// A token of the kept set drawn with probability proportional to its mass, by rejection on
+// TOKENS: a Philox-drawn position is accepted when a second number, uniform on [0, 2^40), lies
+// below the token's integer mass (2^40 stands for the row maximum) and the token is kept.  The
+// first accepted trial wins (trial t = (round * kTokenTrials + j) * kThreads + thread), which
+// makes the draw exact and reproducible.  The chance per trial is the kept mass over
+// vocab * 2^40: high on near-flat rows -- exactly where the draw by classes is slow (many
+// small classes, whose members must be looked for) -- and hopeless on peaked ones, so the
+// caller asks for it only when a round is almost sure to succeed.  A top-p cut that splits a
+// tie group keeps the group's `cut_ties` lowest ids: a member of the group that is hit stands
+// for the group as a whole and is accepted with probability cut_ties / group_cnt; the caller
+// then picks one of the kept members (group_hit).  Returns -1 if max_rounds pass without a hit.
+constexpr int kTokenTrials = 2;
+__device__ int draw_by_token_rejection(Ctx3& c, const KeptSet& kept, bool tie_split, u64 cut_ties, u64 group_cnt,
+                                       uint64_t seed, int max_rounds, bool& group_hit) {
+  const int tid = threadIdx.x;
+  group_hit = false;
+  for (int round = 0; round < max_rounds; ++round) {
+    int id[kTokenTrials];
+    u64 u[kTokenTrials];
+    uint32_t raw[kTokenTrials];
+    int cc[kTokenTrials];
+#pragma unroll
+    for (int j = 0; j < kTokenTrials; ++j) {
+      const Philox4 r = philox4x32_10((uint32_t)round, (uint32_t)tid, (uint32_t)j, 2u, (uint32_t)seed, (uint32_t)(seed >> 32));
+      id[j] = (int)__umul64hi(((u64)r.v[0] << 32) | r.v[1], (u64)c.vocab);
+      u[j] = ((u64)r.v[2] << 8) | (r.v[3] >> 24);
+    }
+#pragma unroll
+    for (int j = 0; j < kTokenTrials; ++j) { raw[j] = (uint32_t)c.logits[id[j]]; cc[j] = c.class_of(id[j]); }
+    u64 best = 0;
+#pragma unroll
+    for (int j = 0; j < kTokenTrials; ++j) {
+      const float s = c.element_score(id[j], raw[j], cc[j]);
+      const uint32_t k = key_of(s);
+      if (k < kept.cut_key || !(u[j] < mass_of(s, c.m))) continue;
+      bool group = false;
+      if (k == kept.cut_key && tie_split) {
+        const Philox4 r = philox4x32_10((uint32_t)round, (uint32_t)tid, (uint32_t)j, 3u, (uint32_t)seed, (uint32_t)(seed >> 32));
+        if (!(__umul64hi(((u64)r.v[0] << 32) | r.v[1], group_cnt) < cut_ties)) continue;
+        group = true;
+      }
+      const u64 packed = ((u64)((kTokenTrials - j) * kThreads - tid) << 33) | ((u64)(group ? 1u : 0u) << 32) | (uint32_t)id[j];
+      best = packed > best ? packed : best;
+    }
+    best = block_max_u64(*c.x, best);
+    if (best) {
+      group_hit = ((best >> 32) & 1ull) != 0;
+      return (int)(uint32_t)best;
     }
   }
   return -1;

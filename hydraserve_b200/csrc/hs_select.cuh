@@ -80,6 +80,24 @@ __device__ __forceinline__ u64 top_p_target(u64 total, float top_p) {
   return a;
 }
 
+// The same value, worked out by the 32 lanes of one warp together (all must call): lane l tries
+// the l-th candidate above the first guess and the lowest that passes wins, so the slow
+// double-precision divisions run side by side instead of one after the other.
+__device__ __forceinline__ u64 top_p_target_warp(u64 total, float top_p) {
+  const double tot = (double)total;
+  const float up = __uint_as_float(__float_as_uint(top_p) + 1u);
+  const double mid = 0.5 * ((double)top_p + (double)up);
+  const double guess = floor(mid * tot) - 2.0;
+  const u64 a0 = guess < 1.0 ? 1ull : (u64)guess;
+  const u64 mine = a0 + (threadIdx.x & 31);
+  const bool pass = (threadIdx.x & 31) >= 8 || (float)((double)mine / tot) > top_p;  // (the scalar version stops after 8 steps too)
+  const uint32_t votes = __ballot_sync(0xffffffffu, pass);
+  u64 a = a0 + (u64)(__ffs(votes) - 1);
+  if (a > total) a = total;
+  if (a < 1) a = 1;
+  return a;
+}
+
 // Walks keys downwards from the top until the running count (BY_MASS = false) or mass
 // (BY_MASS = true) reaches the target.  fill(level, shift, bits, prefix, lo_key, add)
 // must call add(valid, bucket, count, mass), with all lanes of each warp together, where

@@ -245,6 +245,11 @@ class DeviceSampler:
         """CTAs per counting row (tests and tuning); 0 = chosen per call."""
         _lib.check(self.lib, self.handle, self.lib.hs_debug_set(self.handle, 1, int(split)), "hs_debug_set")
 
+    def set_token_draw(self, on: bool) -> None:
+        """Near-flat counting rows draw by rejection on tokens (default) or always class by
+        class (tests and tuning)."""
+        _lib.check(self.lib, self.handle, self.lib.hs_debug_set(self.handle, 3, 1 if on else 0), "hs_debug_set")
+
     def prepare_logits(self, logits):
         torch = self.torch
         if logits.device != self.device:

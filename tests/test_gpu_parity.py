@@ -284,13 +284,17 @@ def _bf16_round(x):
     return (bits.astype(np.uint32) << 16).view(np.float32), bits
 
 
+@pytest.mark.parametrize("draw", ["by_tokens", "by_classes"])
 @pytest.mark.parametrize("kind", ["fine", "coarse", "two_values"])
-def test_bf16_philox_draws_follow_the_distribution(sampler, kind):
-    """The counting kernel's seeded draw (class by inverse CDF, then a uniformly chosen
-    member: by scanning the row for small classes, by rejection for large ones) against the
-    checker's distribution.  fine: every class has a few members (scan); coarse: classes of
-    tens to hundreds of members (scan, and rejection with the scan as fall-back);
-    two_values: classes of about a thousand members (rejection)."""
+def test_bf16_philox_draws_follow_the_distribution(sampler, kind, draw):
+    """The counting kernel's seeded draw against the checker's distribution, both ways it is
+    made.  by_tokens (what these fairly flat rows take by default): rejection on tokens, with
+    a top-p cut that splits a tie group (coarse, two_values: only the group's lowest ids may
+    come out).  by_classes (what peaked rows take; forced here): class by inverse CDF, then a
+    uniformly chosen member, by scanning the row for small classes, by rejection for large
+    ones.  fine: every class has a few members (scan); coarse: classes of tens to hundreds of
+    members (scan, and rejection with the scan as fall-back); two_values: classes of about a
+    thousand members (rejection)."""
     from scipy import stats
 
     from hydraserve_b200.engine.sampling import SamplingParams
@@ -312,15 +316,19 @@ def test_bf16_philox_draws_follow_the_distribution(sampler, kind):
     assert sampler.query(4, vocab) == 1, "bf16 rows must take the counting / candidate kernels"
     counts = np.zeros(vocab, np.int64)
     total = 0
-    for rep in range(reps):
-        params = [base.with_seed(rep * rows + i) for i in range(rows)]
-        records, _ = sampler.sample(logits, [history] * rows, params, [rep] * rows, None)
-        assert int((records["status"] != 0).sum()) == 0
-        if rep == 0:
-            again, _ = sampler.sample(logits, [history] * rows, params, [rep] * rows, None)
-            np.testing.assert_array_equal(records["token"], again["token"])
-        np.add.at(counts, records["token"], 1)
-        total += rows
+    sampler.set_token_draw(draw == "by_tokens")
+    try:
+        for rep in range(reps):
+            params = [base.with_seed(rep * rows + i) for i in range(rows)]
+            records, _ = sampler.sample(logits, [history] * rows, params, [rep] * rows, None)
+            assert int((records["status"] != 0).sum()) == 0
+            if rep == 0:
+                again, _ = sampler.sample(logits, [history] * rows, params, [rep] * rows, None)
+                np.testing.assert_array_equal(records["token"], again["token"])
+            np.add.at(counts, records["token"], 1)
+            total += rows
+    finally:
+        sampler.set_token_draw(True)
     assert counts.sum() == counts[o.kept].sum(), "a token outside the candidate set was drawn"
     expected = probs * total
     big = expected >= 5
@@ -329,7 +337,7 @@ def test_bf16_philox_draws_follow_the_distribution(sampler, kind):
     if exp[-1] == 0:
         obs, exp = obs[:-1], exp[:-1]
     chi2, pvalue = stats.chisquare(obs, exp * obs.sum() / exp.sum())
-    assert pvalue > 1e-4, f"{kind}: chi-square p={pvalue:.3g} over {total} draws ({obs.size} cells)"
+    assert pvalue > 1e-4, f"{kind}/{draw}: chi-square p={pvalue:.3g} over {total} draws ({obs.size} cells)"
 
 
 def test_candidate_path_ties_and_long_lists(sampler):
