@@ -69,7 +69,6 @@ struct hs_sampler {
   int force_split = 0;    // CTAs per candidate row (0 = chosen per call)
   int force_csplit = 0;   // CTAs per counting row (0 = chosen per call)
   int token_draw = 1;     // near-flat counting rows draw by rejection on tokens
-  int prefetch_row = 1;   // counting rows prefetch their row into L2 before the selections
   int ctab_tables = 0;    // count tables the hand-over scratch holds
   uint32_t* ctab = nullptr;   // [ctab_tables, kCells]
   int2* crare = nullptr;      // [ctab_tables, kV3RareCap]
@@ -193,12 +192,13 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
   a.logits = logits; a.dtype = dtype; a.row_stride = row_stride; a.vocab = vocab; a.slice = 0;
   a.params = params; a.out = out; a.noise = noise; a.scores_out = scores_out; a.gstage = nullptr;
   a.pool = h->pool; a.flags = flags & HS_SAMPLE_APPEND_TOKEN; a.tokens_out = tokens_out;
-  a.prefetch_row = h->prefetch_row;
   a.token_draw = h->token_draw;
   if (dtype == HS_DTYPE_BF16 && !h->force_general && !(flags & HS_SAMPLE_GENERAL_KERNEL)) {
     // One launch: a CTA per counting row and per part of a candidate row, two resident per
     // SM.  Small batches: several CTAs stream each candidate row so that every SM has work.
-    int split = h->force_split ? h->force_split : (h->resident_bf16 + batch - 1) / batch;
+    // (as many CTAs per row as fit in one wave, rounded down: a second, partial wave costs more
+    // than idle SMs in the first)
+    int split = h->force_split ? h->force_split : h->resident_bf16 / batch;
     split = std::max(1, std::min(split, kMaxSplit));
     if (vocab < split * 2 * hs::kSample) split = 1;
     // counting rows: as many CTAs per row as the hand-over scratch allows (the whole batch may
@@ -735,10 +735,6 @@ int hs_debug_set(hs_sampler* h, int what, int value) {
   }
   if (what == 3) {
     h->token_draw = value ? 1 : 0;
-    return HS_OK;
-  }
-  if (what == 2) {
-    h->prefetch_row = value;
     return HS_OK;
   }
   return fail(h, HS_ERR_INVALID, "unknown setting");

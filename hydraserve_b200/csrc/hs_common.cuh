@@ -61,18 +61,10 @@ __device__ __forceinline__ uint32_t load_now_u16(const unsigned short* p) {
   return v;
 }
 
-// A 128-bit load past L1 whose line L2 should keep in preference to others ("evict last"): for
-// data that is read again later in the same launch, after other rows have streamed through.
-__device__ __forceinline__ u64 l2_keep_policy() {
-  u64 p;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-__device__ __forceinline__ uint4 load_keep(const uint4* p, u64 policy) {
-  uint4 v;
-  asm volatile("ld.global.cg.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(policy));
-  return v;
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
 }
 
 // ---- probability mass as an exact integer -------------------------------------------

@@ -135,21 +135,6 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
   const int per_part = (n8_row + parts - 1) / parts;
   const int chunk_lo = min(my_part * per_part, n8_row), chunk_hi = min(chunk_lo + per_part, n8_row);
   const bool last_part = my_part == parts - 1;
-  // ask L2 for the range (and its class map) now: the counting loop then waits for L2, not for
-  // HBM, and the later walks over the row find it there
-  if (c.vec && a.prefetch_row != 3) {
-    constexpr uint32_t kPiece = 16384;
-    const unsigned char* base = reinterpret_cast<const unsigned char*>(c.logits) + (size_t)chunk_lo * 16;
-    const size_t bytes = (size_t)(chunk_hi - chunk_lo) * 16;
-    for (size_t at = (size_t)tid * kPiece; at < bytes; at += (size_t)kThreads * kPiece)
-      prefetch_l2_bulk(base + at, (uint32_t)min((size_t)kPiece, bytes - at));
-    if (c.cls && (reinterpret_cast<uintptr_t>(c.cls) & 15u) == 0 && (chunk_lo & 7) == 0) {
-      const unsigned char* cbase = reinterpret_cast<const unsigned char*>(c.cls) + (size_t)chunk_lo * 2;
-      const size_t cls_bytes = ((size_t)(chunk_hi - chunk_lo) * 2) & ~(size_t)15;
-      for (size_t at = (size_t)tid * kPiece; at < cls_bytes; at += (size_t)kThreads * kPiece)
-        prefetch_l2_bulk(cbase + at, (uint32_t)min((size_t)kPiece, cls_bytes - at));
-    }
-  }
   // small[16..18] / [19..21]: highest (+ 1) / lowest non-empty cell per count class; [22]: lowest side key
   if (tid < 32) small[tid] = (tid >= 19 && tid <= 22) ? -1 : 0;
   if (tid == 0) c.x->bcast[5] = 0;  // highest side element, (key, ~id)
@@ -232,8 +217,6 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
       uint4 w[kInFlight], wn[kInFlight];
       uint32_t cl[kInFlight], cn[kInFlight];
 #pragma unroll
-      const bool keep = a.prefetch_row == 2;
-      const u64 keep_policy = l2_keep_policy();
       for (int u = 0; u < kInFlight; ++u) {
         w[u] = __ldcg(src4 + i0 + u * kThreads);  // past L1: almost all of it is shared memory here
         cl[u] = cls16p ? (uint32_t)__ldcg(cls16p + i0 + u * kThreads) : 0u;
@@ -244,7 +227,7 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
         if (it + 1 < n_full) {
 #pragma unroll
           for (int u = 0; u < kInFlight; ++u) {
-            wn[u] = keep ? load_keep(src4 + i0 + kStride + u * kThreads, keep_policy) : __ldcg(src4 + i0 + kStride + u * kThreads);
+            wn[u] = __ldcg(src4 + i0 + kStride + u * kThreads);
             cn[u] = cls16p ? (uint32_t)__ldcg(cls16p + i0 + kStride + u * kThreads) : 0u;
           }
         }
@@ -488,16 +471,6 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
     __syncthreads();
   }
   mark(3);  // (the count table has served: the selection histograms take its place)
-  // Whatever comes last -- a member of the drawn class, the lowest ids of a tie group, the top
-  // log-probabilities' ids, a penalised arg max -- walks or probes the row again, and by then
-  // other rows have pushed it out of L2: ask for it now, while the selections run.
-  if (c.vec && a.prefetch_row == 1) {
-    constexpr uint32_t kPiece = 16384;
-    const size_t row_bytes = ((size_t)c.vocab * 2) & ~(size_t)15;
-    for (size_t at = (size_t)tid * kPiece; at < row_bytes; at += (size_t)kThreads * kPiece)
-      prefetch_l2_bulk(reinterpret_cast<const unsigned char*>(c.logits) + at,
-                       (uint32_t)min((size_t)kPiece, row_bytes - at));
-  }
 
   if (c.greedy) {
     // arg max with penalties: the lowest id among the tokens whose score key is the maximum
@@ -995,14 +968,24 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_bf16(const RowV3Args a
   int row = count ? item % args.batch : (item - n_count) / args.split;
   int part = count ? item / args.batch : (item - n_count) % args.split;
   if (is_candidate_row(args.base.params[row], args.base.vocab) == count) return;  // the other path's row
+  // (tuning aid: when each item started and ended, in ns of the global timer, slots 48.. of its row)
+  unsigned long long* when = nullptr;
+  if (args.phase_clocks && threadIdx.x == 0) {
+    when = args.phase_clocks + (size_t)row * kV3PhaseSlots + (count ? 48 : 56) + 2 * part;
+    when[0] = global_timer_ns();
+  }
   if (!count) {
-    if (!cand_part(args, smem_raw, row, part)) return;
+    if (!cand_part(args, smem_raw, row, part)) {
+      if (when) when[1] = global_timer_ns();
+      return;
+    }
     __syncthreads();
     part = -1;  // more ties than a candidate list holds: this CTA counts the whole row
   } else if (args.csplit == 1) {
     part = -1;
   }
   count_row(args, smem_raw, row, part);
+  if (when) when[1] = global_timer_ns();
 }
 
 }  // namespace hs

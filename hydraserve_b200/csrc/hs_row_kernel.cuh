@@ -42,7 +42,6 @@ struct RowKernelArgs {
   uint32_t flags;
   int32_t* tokens_out;  // [batch] or null: the sampled ids once more, as the next step's input ids
   int token_draw;       // bf16 counting rows draw near-flat rows by rejection on tokens (tuning / test switch)
-  int prefetch_row;     // bf16 counting rows ask L2 for their row again before the selections (tuning switch)
 };
 
 struct RowCtx : ClusterCtx {

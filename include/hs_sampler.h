@@ -222,9 +222,8 @@ int hs_query(hs_sampler* h, int what, int vocab, int dtype);
  * (synchronises the device). */
 int hs_debug_phase_clocks(hs_sampler* h, int batch, unsigned long long* out_host);
 /* Tests and tuning.  what = 0: CTAs per candidate row, what = 1: CTAs per counting row; value 1, 2
- * or 4 (0 = chosen per call).  what = 2: counting rows ask L2 for their row again before the
- * selections (value 1, the default) or not (0).  what = 3: near-flat counting rows draw by
- * rejection on tokens (1, the default) or always class by class (0). */
+ * or 4 (0 = chosen per call).  what = 3: near-flat counting rows draw by rejection on tokens
+ * (1, the default) or always class by class (0). */
 int hs_debug_set(hs_sampler* h, int what, int value);
 
 #ifdef __cplusplus
