@@ -24,6 +24,10 @@
 #include "hs_select.cuh"
 #include "hs_row_v3.cuh"
 
+#ifndef HS_CAND_BATCH
+#define HS_CAND_BATCH 4
+#endif
+
 namespace hs {
 
 constexpr int kTopKMax = 256;      // largest top_k served by the candidate path
@@ -431,7 +435,7 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
   const int first8 = c.lo / 8;  // lo is a multiple of 8
   const int n8 = c.vec ? c.hi / 8 : first8;
   const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
-  constexpr int kBatch = 4;  // two batches of loads: the next is on its way while this one is compared
+  constexpr int kBatch = HS_CAND_BATCH;  // two batches of loads: the next is on its way while this one is compared
   int n_scored = n;
   uint4 w[kBatch], wn[kBatch];
   auto fetch = [&](uint4 (&dst)[kBatch], int base) {

@@ -46,8 +46,14 @@ constexpr uint32_t kV3Base = 113u << 7;       // smallest binned magnitude: 2^-1
 constexpr int kV3ListCap = 256;               // members resolved by sorting
 constexpr int kV3RejectMin = 128;             // classes of up to this many tokens are found by scanning the row, larger ones by rejection
 constexpr int kV3ScanCap = 1024;              // ids one class scan can hold (in the gather and list buffers)
-constexpr int kV3RareCap = 512;               // out-of-window tokens remembered before a sweep
-constexpr int kV3SideShared = 1024;           // side-list entries kept in shared memory (else global scratch)
+#ifndef HS_RARE_CAP
+#define HS_RARE_CAP 512
+#endif
+#ifndef HS_SIDE_SHARED
+#define HS_SIDE_SHARED 1024
+#endif
+constexpr int kV3RareCap = HS_RARE_CAP;               // out-of-window tokens remembered before a sweep
+constexpr int kV3SideShared = HS_SIDE_SHARED;           // side-list entries kept in shared memory (else global scratch)
 constexpr int kV3PhaseSlots = 64;
 constexpr int kSplitCap = 4096;               // candidate entries one CTA of a split row can hand over
 
