@@ -58,6 +58,8 @@ def _static_row(p: SamplingParams) -> bytes:
 
 _static_rows: dict = {}  # id(params) -> (params, packed bytes); the object is kept so the id stays its own
 _STATIC_ROWS_MAX = 8192
+_static_batches: dict = {}  # ids of a batch's params -> (the params, packed static part, any unseeded, seeds)
+_STATIC_BATCHES_MAX = 64
 
 
 def _static_row_cached(p: SamplingParams) -> bytes:
@@ -80,20 +82,45 @@ def draw_unseeded_keys(params):
             if (p.seed is None and p.temperature != 0.0) else None for p in params]
 
 
+def batch_static(params):
+    """What depends on a batch's SamplingParams alone: (the params, packed static part, any
+    unseeded row, seeds, which rows have penalties).  A serving loop passes the same objects
+    step after step, so this is kept per batch (the entry holds the objects: their ids stay
+    theirs while it lives)."""
+    n = len(params)
+    key = tuple(map(id, params))
+    hit = _static_batches.get(key)
+    if hit is None:
+        static = np.frombuffer(b"".join(_static_row_cached(p) for p in params), dtype=_lib.ROW_PARAMS).copy() \
+            if n else np.zeros(0, dtype=_lib.ROW_PARAMS)
+        unseeded = any(p.seed is None and p.temperature != 0.0 for p in params)
+        fixed_seeds = None if unseeded else np.fromiter((p.seed if p.seed is not None else 0 for p in params),
+                                                        dtype=np.uint64, count=n)
+        if len(_static_batches) >= _STATIC_BATCHES_MAX:
+            _static_batches.clear()
+        hit = _static_batches[key] = (tuple(params), static, unseeded, fixed_seeds,
+                                      tuple(_has_penalties(p) for p in params))
+    return hit
+
+
 def pack_params(params, steps, slots=None, unseeded_keys=None) -> np.ndarray:
     """SamplingParams -> the C struct array ``hs_row_params[batch]`` (host, numpy).
 
     unseeded_keys: per row, the stream key of a row whose ``seed`` is None (or None); drawn
     from torch's global generator when not given."""
     n = len(params)
-    rec = np.frombuffer(b"".join(_static_row_cached(p) for p in params), dtype=_lib.ROW_PARAMS).copy() \
-        if n else np.zeros(0, dtype=_lib.ROW_PARAMS)
-    if unseeded_keys is None and any(p.seed is None and p.temperature != 0.0 for p in params):
-        unseeded_keys = draw_unseeded_keys(params)
-    seeds = np.fromiter(
-        ((p.seed if p.seed is not None else ((unseeded_keys[i] if unseeded_keys else None) or 0))
-         for i, p in enumerate(params)), dtype=np.uint64, count=n)
-    step_arr = np.fromiter((int(s) + 1 for s in steps), dtype=np.int64, count=n).astype(np.uint64)
+    hit = batch_static(params)
+    _, static, unseeded, fixed_seeds, _ = hit
+    rec = static.copy()
+    if unseeded:
+        if unseeded_keys is None:
+            unseeded_keys = draw_unseeded_keys(params)
+        seeds = np.fromiter(
+            ((p.seed if p.seed is not None else ((unseeded_keys[i] if unseeded_keys else None) or 0))
+             for i, p in enumerate(params)), dtype=np.uint64, count=n)
+    else:
+        seeds = fixed_seeds
+    step_arr = (np.asarray(steps, dtype=np.int64) + 1).astype(np.uint64)
     with np.errstate(over="ignore"):
         rec["seed"] = (seeds + step_arr * np.uint64(SEED_STRIDE)) & _MASK63  # == mixed_seed, vectorised
     if slots is not None:
@@ -401,12 +428,21 @@ class DeviceSampler:
         slots = [-1] * batch
         resets, appends = [], []
         in_batch = None
-        for i, p in enumerate(params):
-            if not _has_penalties(p):
+        entries = self.book.entries if request_ids is not None else None
+        for i, penalised in enumerate(batch_static(params)[4]):
+            if not penalised:
                 continue
             history = histories[i]
             slot = -1
-            if request_ids is not None and request_ids[i] is not None:
+            if entries is not None and request_ids[i] is not None:
+                # the common step in line: a known request whose history grew by one token
+                entry = entries.get(request_ids[i])
+                if entry is not None and len(history) == entry[1] + 1 and type(history) in (list, tuple):
+                    entries.move_to_end(request_ids[i])
+                    appends.append((entry[0], history[-1:]))
+                    entry[1] += 1
+                    slots[i] = entry[0]
+                    continue
                 if in_batch is None:
                     in_batch = {r for r in request_ids if r is not None}
                 slot = self._slot_for_request(request_ids[i], history, vocab, resets, appends, in_batch)
@@ -518,8 +554,11 @@ def record_to_sample(rec, logprobs, vocab: int) -> TokenSample:
 
 def records_to_samples(records, params, vocab: int):
     tokens = records["token"].tolist()
-    return tuple(TokenSample(tokens[i]) if p.logprobs is None else record_to_sample(records[i], p.logprobs, vocab)
-                 for i, p in enumerate(params))
+    out = list(map(TokenSample, tokens))
+    for i, p in enumerate(params):
+        if p.logprobs is not None:
+            out[i] = record_to_sample(records[i], p.logprobs, vocab)
+    return tuple(out)
 
 
 class PackedSamples:
