@@ -401,11 +401,17 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
   side_best = c.x->bcast[5];
   mark(2);
   uint32_t cells_key = 0, min_key = reinterpret_cast<unsigned*>(small)[22], cells_min_key = 0xffffffffu;
-#pragma unroll
-  for (int k = 0; k < 3; ++k) {
-    const uint32_t t = reinterpret_cast<unsigned*>(small)[16 + k], l = reinterpret_cast<unsigned*>(small)[19 + k];
-    if (t) cells_key = max(cells_key, key_of(c.cell_score((int)t - 1)));
-    if (l != 0xffffffffu) cells_min_key = min(cells_min_key, key_of(c.cell_score((int)l)));
+  {
+    // six scores (highest and lowest non-empty cell of three count classes): lanes 0..5 of every
+    // warp work one out each and the warp combines them
+    const int lane = tid & 31;
+    const bool top = lane < 3;
+    const uint32_t mark_at = reinterpret_cast<unsigned*>(small)[(top ? 16 : 19) + lane % 3];
+    const bool valid = lane < 6 && (top ? mark_at != 0u : mark_at != 0xffffffffu);
+    uint32_t key = 0;
+    if (valid) key = key_of(c.cell_score(top ? (int)mark_at - 1 : (int)mark_at));
+    cells_key = __reduce_max_sync(0xffffffffu, valid && top ? key : 0u);
+    cells_min_key = __reduce_min_sync(0xffffffffu, valid && !top ? key : 0xffffffffu);
   }
   min_key = min(min_key, cells_min_key);
   if (clocks && tid == 0) clocks[25] = clock64();

@@ -697,8 +697,9 @@ __device__ int nth_in_group(Ctx3& c, const Group& g, u64 n) {
 // Token id of the n-th (1-based, ascending id) of the `members` tokens of ONE class (count
 // class and one-value bin `cell`), for classes of at most kV3ScanCap tokens, or -1 when the row
 // has no 16-byte aligned view.  The row is walked from the end that is nearer to the n-th
-// member, 16,384 tokens per step, and the walk stops with the step that reaches it: members are
-// spread evenly over the row, so on average a quarter of it is read.  A class is one bf16 bit
+// member, 16,384 tokens per step, and the walk stops soon after the step that reaches it (it
+// looks every fourth step): members are spread evenly over the row, so on average a third of
+// it is read.  A class is one bf16 bit
 // pattern and a normal number (the bin window holds neither zeros nor NaNs), so two tokens are
 // compared with it by one native bf16x2 equality per 32-bit word; a hit looks its count class
 // up in the 16 class bits that travel with its chunk.  The ids found (in the gather and list
@@ -730,9 +731,9 @@ __device__ __noinline__ void scan_small_class(const ScanArgs c, uint32_t raw, in
   const int n8 = c.vocab / 8;
   const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
   const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
-  // Members found are counted in two counters that take turns step by step: after a step's
-  // barrier every thread reads that step's counter, which nobody adds to before the barrier
-  // after next, so all threads see the same running total and leave the walk together.
+  // Members found are counted in two counters that take turns from one look to the next:
+  // after a look's barrier every thread reads that turn's counter, which nobody adds to before
+  // the barrier after next, so all threads see the same running total and leave together.
   auto note = [&](int id, int parity) {
     const int slot = atomicAdd(c.slot_n, 1);
     if (slot < kV3ScanCap) ids[slot] = id;
@@ -746,6 +747,7 @@ __device__ __noinline__ void scan_small_class(const ScanArgs c, uint32_t raw, in
   if (!forward) tail(0);
   constexpr int kBatch = 4;
   constexpr int kStep = kBatch * kThreads;  // chunks per step
+  constexpr int kCheckShift = 2;            // the walk looks whether it may stop every 2^kCheckShift steps
   const int n_steps = (n8 + kStep - 1) / kStep;
   uint4 w[kBatch], wn[kBatch];
   uint32_t cl[kBatch], cn[kBatch];
@@ -778,17 +780,20 @@ __device__ __noinline__ void scan_small_class(const ScanArgs c, uint32_t raw, in
         while (hits) {
           const int q = __ffs(hits) - 1;
           hits &= hits - 1;
-          if ((int)((cl[u] >> (2 * q)) & 3u) == cc) note(id + q, s & 1);
+          if ((int)((cl[u] >> (2 * q)) & 3u) == cc) note(id + q, (s >> kCheckShift) & 1);
         }
       }
     }
-    __syncthreads();
-    {
-      const int now = c.step_n[s & 1];
-      total += now - seen[s & 1];
-      seen[s & 1] = now;
+    // (a look every few steps: a barrier after every step would make each one wait for its
+    // slowest load)
+    if ((s & ((1 << kCheckShift) - 1)) == (1 << kCheckShift) - 1) {
+      const int turn = (s >> kCheckShift) & 1;
+      __syncthreads();
+      const int now = c.step_n[turn];
+      total += now - seen[turn];
+      seen[turn] = now;
+      if (total >= need) { reached = true; break; }
     }
-    if (total >= need) { reached = true; break; }
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) { w[u] = wn[u]; cl[u] = cn[u]; }
   }
