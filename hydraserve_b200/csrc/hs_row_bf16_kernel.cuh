@@ -596,8 +596,10 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
       bool by_tokens = false;
       if (a.token_draw && mass_to_float(q_kept) * (float)(kTokenTrials * kThreads) >= 4.0f * (float)c.vocab) {
         bool group_hit;
+        // (a sixteenth of the trials accepted on average: one per thread is plenty)
+        const int trials = mass_to_float(q_kept) * 16.0f >= (float)c.vocab ? 1 : kTokenTrials;
         const int t = draw_by_token_rejection(c, kept, tie_split, cut_ties > 0 ? (u64)cut_ties : 0ull, cut_group_cnt, P.seed, 4,
-                                              group_hit);
+                                              trials, group_hit);
         if (t >= 0) {
           token = t;
           if (group_hit) {

@@ -899,13 +899,14 @@ __device__ int random_in_class(Ctx3& c, int cell, int trials, uint64_t seed, int
 // makes the draw exact and reproducible.  The chance per trial is the kept mass over
 // vocab * 2^40: high on near-flat rows -- exactly where the draw by classes is slow (many
 // small classes, whose members must be looked for) -- and hopeless on peaked ones, so the
-// caller asks for it only when a round is almost sure to succeed.  A top-p cut that splits a
+// caller asks for it only when a round is almost sure to succeed (with one trial per thread
+// on the flattest rows, else two).  A top-p cut that splits a
 // tie group keeps the group's `cut_ties` lowest ids: a member of the group that is hit stands
 // for the group as a whole and is accepted with probability cut_ties / group_cnt; the caller
 // then picks one of the kept members (group_hit).  Returns -1 if max_rounds pass without a hit.
 constexpr int kTokenTrials = 2;
 __device__ int draw_by_token_rejection(Ctx3& c, const KeptSet& kept, bool tie_split, u64 cut_ties, u64 group_cnt,
-                                       uint64_t seed, int max_rounds, bool& group_hit) {
+                                       uint64_t seed, int max_rounds, int trials, bool& group_hit) {
   const int tid = threadIdx.x;
   group_hit = false;
   for (int round = 0; round < max_rounds; ++round) {
@@ -915,15 +916,21 @@ __device__ int draw_by_token_rejection(Ctx3& c, const KeptSet& kept, bool tie_sp
     int cc[kTokenTrials];
 #pragma unroll
     for (int j = 0; j < kTokenTrials; ++j) {
+      if (j >= trials) break;
       const Philox4 r = philox4x32_10((uint32_t)round, (uint32_t)tid, (uint32_t)j, 2u, (uint32_t)seed, (uint32_t)(seed >> 32));
       id[j] = (int)__umul64hi(((u64)r.v[0] << 32) | r.v[1], (u64)c.vocab);
       u[j] = ((u64)r.v[2] << 8) | (r.v[3] >> 24);
     }
 #pragma unroll
-    for (int j = 0; j < kTokenTrials; ++j) { raw[j] = (uint32_t)c.logits[id[j]]; cc[j] = c.class_of(id[j]); }
+    for (int j = 0; j < kTokenTrials; ++j) {
+      if (j >= trials) break;
+      raw[j] = (uint32_t)c.logits[id[j]];
+      cc[j] = c.class_of(id[j]);
+    }
     u64 best = 0;
 #pragma unroll
     for (int j = 0; j < kTokenTrials; ++j) {
+      if (j >= trials) break;
       const float s = c.element_score(id[j], raw[j], cc[j]);
       const uint32_t k = key_of(s);
       if (k < kept.cut_key || !(u[j] < mass_of(s, c.m))) continue;
