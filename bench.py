@@ -55,7 +55,7 @@ UNIT = "rows/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one step's kernel on config 3, from the ncu
 # capture summarised in profiles/bf16_row_kernel_config3.md
-NCU_DRAM_BYTES_PER_STEP = {3: 170_448_384}
+NCU_DRAM_BYTES_PER_STEP = {3: 164_936_192}
 
 WORKLOADS = {
     2: dict(batch=64, vocab=151_936, history=4096, sets=8, scaling="weak",

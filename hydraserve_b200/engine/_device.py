@@ -624,7 +624,8 @@ def sample_batch(logits, histories, params, steps, request_ids, all_plain_greedy
         return PackedSamples(np.zeros(0, _lib.ROW_OUT), [], vocab) if packed else ()
     hist_need = 0
     if not all_plain_greedy:
-        hist_need = max((len(h) for h, p in zip(histories, params) if _has_penalties(p)), default=0)
+        pen = batch_static(params)[4]
+        hist_need = max((len(h) for h, on in zip(histories, pen) if on), default=0)
     with lease_sampler(device, vocab, batch, hist_need) as sampler:
         if all_plain_greedy:
             tokens = sampler.greedy(logits).cpu().numpy()
