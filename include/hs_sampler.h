@@ -217,9 +217,10 @@ int hs_abi_version(void);
  *       5 = device memory held by the sampler, in KiB, 6 = device bytes per histogram slot,
  *       7 = CTAs of the bf16 kernel that can be resident at once (CTAs per SM x SMs) */
 int hs_query(hs_sampler* h, int what, int vocab, int dtype);
-/* Tuning aid: a sampler created with HS_CREATE_PHASE_CLOCKS records the SM clock at 64 phase
- * slots per row of the last launch; this copies batch x 64 counters to out_host
- * (synchronises the device). */
+/* Tuning aid: a sampler created with HS_CREATE_PHASE_CLOCKS records, per row of the last launch,
+ * 64 counters: the SM clock at the phases of the row's CTA (slots 0..47), and when each of the
+ * row's work items started and ended, in ns of the global timer (slots 48..55: up to four
+ * counting parts, 56..63: up to four candidate parts).  Copies batch x 64 counters to out_host (synchronises the device). */
 int hs_debug_phase_clocks(hs_sampler* h, int batch, unsigned long long* out_host);
 /* Tests and tuning.  what = 0: CTAs per candidate row, what = 1: CTAs per counting row; value 1, 2
  * or 4 (0 = chosen per call).  what = 3: near-flat counting rows draw by rejection on tokens
