@@ -80,33 +80,50 @@ __global__ void __launch_bounds__(kThreads, 2) shard_partial_kernel(const ShardA
   if (n > HS_SHARD_CAND) { status |= 32; n = HS_SHARD_CAND; }  // more ties than the record holds
   __syncthreads();
   const float m = n > 0 ? score_of(cand_key(L.cand[0])) : 0.f;
-  // soft-max denominator of the whole slice, relative to the slice maximum (exact integer mass)
-  // (the slice was streamed a moment ago and sits in L2: eight tokens per 128-bit load, their
-  // count classes from one 16-bit load)
+  // The record's candidates leave shared memory now: the list's place is needed below.
+  for (int i = tid; i < HS_SHARD_CAND; i += kThreads) {
+    rec->ids[i] = i < n ? cand_id(L.cand[i]) + args.vocab_offset : -1;
+    rec->scores[i] = i < n ? score_of(cand_key(L.cand[i])) : 0.f;
+  }
+  __syncthreads();
+  // Soft-max denominator of the whole slice, relative to the slice maximum (exact integer
+  // mass).  A token's mass follows from its value and count class, so the slice (streamed a
+  // moment ago, it sits in L2) is COUNTED per class into three tables of one-value bins, in the
+  // candidate list's place, and every non-empty class contributes count x mass: one exponential
+  // per class instead of one per token.  Tokens held three times or more, and values outside
+  // the bin window, are rare and add their mass directly.
   u64 z = 0, unused = 0;
   {
+    uint32_t* tab = reinterpret_cast<uint32_t*>(smem_raw + lay.cand);
+    static_assert(sizeof(uint32_t) * kCells <= sizeof(u64) * kCandCap * 2 + sizeof(uint32_t) * kBins,
+                  "the count tables fit in the place of the candidate list, its masses and the counters");
+    for (int i = tid; i < kCells; i += kThreads) tab[i] = 0;
+    __syncthreads();
     const int n8 = c.vec ? c.vocab / 8 : 0;
     const uint4* src4 = reinterpret_cast<const uint4*>(c.logits);
     const unsigned short* cls16p = reinterpret_cast<const unsigned short*>(c.cls);
+    const uint32_t tab_at = (uint32_t)__cvta_generic_to_shared(tab);
+    auto take = [&](int id, uint32_t raw, int cc) {
+      const int b = cc == 3 ? -1 : v3_bin_of_raw(raw);
+      if (b >= 0) asm volatile("red.shared.add.u32 [%0], 1;" ::"r"(tab_at + 4u * (uint32_t)(cc * kV3Bins + b)) : "memory");
+      else z += mass_of(c.element_score(id, raw, cc), m);
+    };
     for (int i = tid; i < n8; i += kThreads) {
       const uint4 w = __ldcg(src4 + i);
       const uint32_t cl = cls16p ? (uint32_t)cls16p[i] : 0u;
       const uint32_t words[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const uint32_t raw = (words[q >> 1] >> (16 * (q & 1))) & 0xffffu;
-        const int cc = (int)((cl >> (2 * q)) & 3u);
-        z += mass_of(c.element_score(8 * i + q, raw, cc), m);
-      }
+      for (int q = 0; q < 8; ++q)
+        take(8 * i + q, (words[q >> 1] >> (16 * (q & 1))) & 0xffffu, (int)((cl >> (2 * q)) & 3u));
     }
-    for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads)
-      z += mass_of(c.element_score(id, c.logits[id], c.class_of(id)), m);
+    for (int id = n8 * 8 + tid; id < c.vocab; id += kThreads) take(id, c.logits[id], c.class_of(id));
+    __syncthreads();
+    for (int cell = tid; cell < kCells; cell += kThreads) {
+      const uint32_t count = tab[cell];
+      if (count) z += (u64)count * mass_of(c.cell_score(cell), m);
+    }
   }
   block_sum2(*c.x, z, unused);
-  for (int i = tid; i < HS_SHARD_CAND; i += kThreads) {
-    rec->ids[i] = i < n ? cand_id(L.cand[i]) + args.vocab_offset : -1;
-    rec->scores[i] = i < n ? score_of(cand_key(L.cand[i])) : 0.f;
-  }
   if (tid == 0) {
     rec->row_max = m;
     rec->pad = 0.f;
