@@ -22,7 +22,7 @@ from collections import OrderedDict
 import numpy as np
 
 from .. import _lib
-from .sampling import SamplingParams, TokenSample, _has_penalties, _is_plain_greedy
+from .sampling import SamplingParams, TokenSample, _has_penalties, _is_plain_greedy, _token_only
 
 SEED_STRIDE = 0x1E3779B97F4A7C15  # reference sampling.py:148
 _NEG_INF = float("-inf")
@@ -554,7 +554,7 @@ def record_to_sample(rec, logprobs, vocab: int) -> TokenSample:
 
 def records_to_samples(records, params, vocab: int):
     tokens = records["token"].tolist()
-    out = list(map(TokenSample, tokens))
+    out = list(map(_token_only, tokens))
     for i, p in enumerate(params):
         if p.logprobs is not None:
             out[i] = record_to_sample(records[i], p.logprobs, vocab)

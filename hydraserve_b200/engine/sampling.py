@@ -82,6 +82,22 @@ class TokenSample:
     top_logprobs: tuple[tuple[int, float], ...] = ()
 
 
+_new_object = object.__new__
+_set_token_id = TokenSample.token_id.__set__
+_set_logprob = TokenSample.logprob.__set__
+_set_top_logprobs = TokenSample.top_logprobs.__set__
+
+
+def _token_only(token_id: int) -> TokenSample:
+    """``TokenSample(token_id)`` without the frozen dataclass's ``__init__`` (which goes through
+    ``object.__setattr__`` per field): the result path builds one per row and step."""
+    sample = _new_object(TokenSample)
+    _set_token_id(sample, token_id)
+    _set_logprob(sample, None)
+    _set_top_logprobs(sample, ())
+    return sample
+
+
 def _has_penalties(params: SamplingParams) -> bool:
     """reference sampling.py:94-99"""
     return not (
