@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the per-step token sampler.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|3|4|5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 1|2|3|4|5]
 
 A step is one pass of the sampler over one batch of synthetic logits.  The default workload
 (``--config 3``) is the large-vocabulary stress configuration: 256 rows x 248,320 bf16 logits,
@@ -10,6 +10,7 @@ device-resident histograms, top-k / top-p / min-p, seeded Philox draw; under ``-
 each rank works on its own 256 rows (weak scaling, no inter-GPU traffic).  The other
 configurations of the same path:
 
+  --config 1   the reference's CPU-runnable check, 4 x 151,936 fp32 (top_k 50 rows; --batch B for more rows)
   --config 2   decode step, 64 x 151,936 bf16, mixed parameters, 20 logprobs per row
                (small and launch-bound: the single-step latency is reported too)
   --config 4   1,024 x 151,936 bf16 with per-row random parameters, the rows split evenly
@@ -58,6 +59,10 @@ FALLBACK_HBM_GBS = 6650.0
 NCU_DRAM_BYTES_PER_STEP = {3: 164_936_192}
 
 WORKLOADS = {
+    1: dict(batch=4, vocab=151_936, history=256, sets=8, scaling="weak",
+            text="config1: the reference's CPU-runnable check, 4 x 151,936 fp32 N(0,2.5^2) with 8 tokens per row "
+                 "raised by 12; row 0 greedy, the others T 0.7, top_k 50, top_p 0.9, repetition penalty 1.1 over "
+                 "256-token histories (--batch B repeats that parameter mix over B rows)"),
     2: dict(batch=64, vocab=151_936, history=4096, sets=8, scaling="weak",
             text="config2: decode step, 64 x 151,936 bf16 N(0,3^2) + Zipf bias, rows cycle through greedy / "
                  "top_p 0.95 / top_k 20 + min_p 0.05 / top_k 40 + top_p 0.8 + T 1.2, presence 0.5 and frequency 0.3 "
@@ -140,12 +145,23 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- workloads
+def host_tensor(w):
+    """A workload's logits as a host tensor of its dtype (bf16 bit patterns or fp32)."""
+    import torch
+
+    if w.dtype == "bf16":
+        return torch.from_numpy(w.logits.view(np.int16)).view(torch.bfloat16)
+    return torch.from_numpy(w.logits)
+
+
 def make_workload(cfg: int, rank: int, world: int, args):
     from hydraserve_b200 import workloads
 
     w = WORKLOADS[cfg]
     batch = args.batch or w["batch"]
     vocab = args.vocab or w["vocab"]
+    if cfg == 1:
+        return workloads.config1(seed=1 + 1000 * rank, batch=batch, vocab=vocab)
     if cfg == 2:
         return workloads.config2(seed=2 + 1000 * rank, batch=batch, vocab=vocab)
     if cfg == 3:
@@ -185,7 +201,7 @@ def cpu_sample_of(w, n_rows):
         n = min(n_rows, w.batch)
         take = list(range(n // 2)) + list(range(half, half + n - n // 2))
     sub = w.rows(take)
-    logits = torch.from_numpy(sub.logits.view(np.int16)).view(torch.bfloat16)
+    logits = host_tensor(sub)
     return logits, [h.tolist() for h in sub.histories], sub.params, sub.steps
 
 
@@ -322,7 +338,9 @@ def run_ours(args, world, rank, local_rank):
     uniques = [int(np.unique(h[(h >= 0) & (h < vocab)]).size) if slots[i] >= 0 else 0
                for i, h in enumerate(w.histories)]
 
-    host_logits = torch.from_numpy(w.logits.view(np.int16)).view(torch.bfloat16).pin_memory()
+    host_logits = host_tensor(w).pin_memory()
+    elem = host_logits.element_size()
+    dtype_code = _lib.HS_DTYPE_BF16 if w.dtype == "bf16" else _lib.HS_DTYPE_F32
     sets = [host_logits.to(device, non_blocking=True).clone() for _ in range(n_sets)]
     total_steps = args.steps + args.warmup
     # one parameter set per step: the step number advances the seeded stream, as in serving.
@@ -338,7 +356,7 @@ def run_ours(args, world, rank, local_rank):
     torch.cuda.synchronize()
 
     def step(i):
-        st = lib.hs_sample(handle, sets[i % n_sets].data_ptr(), _lib.HS_DTYPE_BF16, vocab, batch, vocab,
+        st = lib.hs_sample(handle, sets[i % n_sets].data_ptr(), dtype_code, vocab, batch, vocab,
                            param_sets[i % n_param_sets].data_ptr(), d_out.data_ptr(), None, None,
                            _lib.HS_SAMPLE_APPEND_TOKEN, stream)
         if st != 0:
@@ -378,7 +396,7 @@ def run_ours(args, world, rank, local_rank):
 
     # ---- end to end through the drop-in Python API ------------------------------------
     e2e_steps = 0 if args.kernel_only else max(1, min(args.steps, args.e2e_steps))
-    h2d = host_logits.numel() * 2 + batch * _lib.ROW_PARAMS.itemsize + batch * 4 * 3
+    h2d = host_logits.numel() * elem + batch * _lib.ROW_PARAMS.itemsize + batch * 4 * 3
     d2h = batch * _lib.ROW_OUT.itemsize
 
     def e2e_leg(logits, tag):
@@ -416,14 +434,16 @@ def run_ours(args, world, rank, local_rank):
         return
 
     peak, peak_src = _peak()
-    logits_bytes = batch * vocab * 2
+    logits_bytes = batch * vocab * elem
     algo_bytes = logits_bytes + 8 * sum(uniques) + batch * (_lib.ROW_PARAMS.itemsize + _lib.ROW_OUT.itemsize)
     achieved = algo_bytes / (ms_per_step * 1e-3) / 1e9
     default_shape = (batch, vocab) == (spec["batch"] // (world if cfg == 4 else 1), spec["vocab"])
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
         "traffic": NCU_DRAM_BYTES_PER_STEP.get(cfg) if default_shape else None,
-        "kernel": "hs::row_kernel_bf16 (one launch per step: counting rows and candidate-row parts, two CTAs per SM)",
+        "kernel": ("hs::row_kernel_bf16 (one launch per step: counting rows and candidate-row parts, two CTAs per SM)"
+                   if w.dtype == "bf16" else
+                   "hs::row_kernel_f32_topk (rows with 0 < top_k <= 256) + hs::row_kernel (the other rows)"),
         "peak_source": peak_src,
         "algorithmic_bytes_per_launch": algo_bytes, "logits_bytes_per_launch": logits_bytes,
         "logits_only_gbs": logits_bytes / (ms_per_step * 1e-3) / 1e9,
@@ -447,7 +467,7 @@ def run_ours(args, world, rank, local_rank):
             "path": "hydraserve_b200.engine.sample_logits(pinned host logits, request_ids=...)"},
         "e2e_device_logits": None if dev_value is None else {
             "value": dev_value, "unit": UNIT, "ms_per_step": dev_ms, "steps": e2e_steps,
-            "h2d_bytes_per_step": h2d - host_logits.numel() * 2, "d2h_bytes_per_step": d2h,
+            "h2d_bytes_per_step": h2d - host_logits.numel() * elem, "d2h_bytes_per_step": d2h,
             "path": "the same call with the logits already on the device (where the LM head leaves them)"},
         "gpu_launches": launches,
         "single_step": {"ms": single_ms, "what": "one launch with the GPU idle before it (median of 16)",
@@ -588,7 +608,7 @@ def main():
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--config", type=int, choices=[2, 3, 4, 5], default=3)
+    ap.add_argument("--config", type=int, choices=[1, 2, 3, 4, 5], default=3)
     ap.add_argument("--batch", type=int, default=None, help="rows (config 4: in total over all GPUs)")
     ap.add_argument("--vocab", type=int, default=None)
     ap.add_argument("--history", type=int, default=None, help="history length (config 3)")

@@ -19,6 +19,7 @@
 #include "hs_row_topk.cuh"
 #include "hs_sharded.cuh"
 #include "hs_row_bf16_kernel.cuh"
+#include "hs_row_f32_topk.cuh"
 
 namespace {
 
@@ -219,6 +220,16 @@ int launch_rows(hs_sampler* h, const void* logits, int dtype, int64_t row_stride
     return HS_OK;
   }
   if (!make_plan(h, vocab, plan)) return fail(h, HS_ERR_CAPACITY, "vocabulary too wide for the row kernel");
+  // fp32 rows with a small top_k: the candidate kernel, one CTA per row (the other rows' CTAs
+  // leave at once); the general kernel below leaves those rows alone
+  a.skip_candidate_rows = 0;
+  if (dtype == HS_DTYPE_F32 && !h->force_general && !(flags & HS_SAMPLE_GENERAL_KERNEL)) {
+    a.skip_candidate_rows = 1;
+    hs::F32TopkArgs f{a, h->phase_clocks};
+    hs::row_kernel_f32_topk<<<(unsigned)batch, hs::kThreads, hs::layout_cand().total, stream>>>(f);
+    HS_CUDA(h, cudaGetLastError());
+    h->launches += 1;
+  }
   if (plan.global_stage) {
     const size_t need = (size_t)batch * plan.slice * plan.cluster;
     if (need > h->gstage_elems) return fail(h, HS_ERR_CAPACITY, "global stage too small for this batch x vocab");
@@ -415,6 +426,7 @@ int hs_create_ex(int device, int vocab_max, int slots_max, int hist_cap, int bat
   if (cudaDeviceGetAttribute(&h->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h->smem_optin) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::row_kernel_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::bf16_kernel_smem()) != cudaSuccess) return bail(HS_ERR_CUDA);
+  if (cudaFuncSetAttribute(hs::row_kernel_f32_topk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_cand().total) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::shard_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_cand().total) != cudaSuccess) return bail(HS_ERR_CUDA);
   if (cudaFuncSetAttribute(hs::shard_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs::layout_cand().total) != cudaSuccess) return bail(HS_ERR_CUDA);
   {

@@ -41,6 +41,7 @@ struct RowKernelArgs {
   Pool pool;            // token-count histograms
   uint32_t flags;
   int32_t* tokens_out;  // [batch] or null: the sampled ids once more, as the next step's input ids
+  int skip_candidate_rows;  // the general kernel leaves rows with 0 < top_k <= 256 to the fp32 candidate kernel
   int token_draw;       // bf16 counting rows draw near-flat rows by rejection on tokens (tuning / test switch)
 };
 
@@ -109,6 +110,8 @@ __device__ void totals_above(RowCtx& c, uint32_t lo_key, float m, bool with_mass
   cnt = mass = 0;
   for (unsigned r = 0; r < c.nranks; ++r) { cnt += all[r][0]; mass += all[r][1]; }
 }
+
+constexpr int kCandidateTopKMax = 256;  // largest top_k the candidate paths serve
 
 struct KeptSet {
   uint32_t cut_key;  // kept: key > cut_key, or key == cut_key and global id <= tie_limit
@@ -307,6 +310,12 @@ __device__ void write_top_logprobs(RowCtx& c, const KeptSet& kept, uint32_t key_
 
 __global__ void __launch_bounds__(kThreads, 1) row_kernel(const RowKernelArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  if (a.skip_candidate_rows) {
+    // fp32 rows with a small top_k are sampled by the candidate kernel launched next to this
+    // one (every CTA of the row's cluster sees the same parameters and leaves together)
+    const hs_row_params& p = a.params[blockIdx.y];
+    if (p.temperature != 0.0f && p.top_k > 0 && p.top_k <= kCandidateTopKMax && p.top_k < a.vocab) return;
+  }
   RowCtx c{{cg::this_cluster()}};
   c.rank = c.cluster.block_rank();
   c.nranks = c.cluster.num_blocks();

@@ -477,3 +477,45 @@ def test_candidate_list_overflow_falls_back_to_counting(sampler):
         rows, _ = oracle_rows(w)
         assert rows[0].n_after_topk >= 9000 and rows[1].n_after_topk >= 5000  # (a few tied tokens are penalised)
         compare_case(sampler, w).assert_ok(max_sensitive_fraction=0.67)
+
+
+def test_fp32_rows_with_small_top_k_take_the_candidate_kernel(sampler, general_sampler):
+    """fp32 logits (the reference's CPU-runnable check): rows with 0 < top_k <= 256 are served by
+    the fp32 candidate kernel, the others by the general kernel launched next to it (two
+    launches per call); the results are the general kernel's."""
+    w = cases.build("config1")
+    assert w.dtype == "f32"
+    before = sampler.query(3, w.vocab)
+    got, _ = sampler.sample(device_logits(w), w.histories, w.params, w.steps, None)
+    assert sampler.query(3, w.vocab) - before >= 2
+    want, _ = general_sampler.sample(device_logits(w), w.histories, w.params, w.steps, None)
+    # (not the sampled token: which token a seeded draw lands on depends on the kernel's order
+    # of the candidates; the sets and the cuts do not)
+    for field in ("status", "n_kept", "n_after_topk", "n_after_minp", "n_cut_ties", "cut_bits"):
+        np.testing.assert_array_equal(got[field], want[field], err_msg=field)
+    compare_case(sampler, w).assert_ok(max_sensitive_fraction=0.5, name="config1 (fp32 candidate kernel)")
+
+
+def test_fp32_candidate_list_overflow_falls_back_to_the_general_kernel(sampler):
+    """fp32 rows with more tokens tied at the k-th value than a candidate list holds: the
+    candidate kernel reports the row (status 4) and the general kernel samples it."""
+    from hydraserve_b200.engine.sampling import SamplingParams
+    from hydraserve_b200.workloads import Workload
+
+    rng = np.random.default_rng(48)
+    vocab, batch = 30_000, 3
+    raw = np.minimum((rng.standard_normal((batch, vocab)) * 1.5).astype(np.float32), 3.0)
+    tied = rng.choice(vocab, 9000, replace=False)
+    raw[0, tied] = 4.0
+    raw[1, tied[:6000]] = 4.0
+    raw[1, tied[6000:6020]] = 6.0 + np.arange(20, dtype=np.float32) * 0.5
+    params = [
+        SamplingParams(temperature=1.0, top_k=50, seed=1, logprobs=20),
+        SamplingParams(temperature=0.8, top_k=40, top_p=0.9, seed=2, presence_penalty=0.5, logprobs=5),
+        SamplingParams(temperature=1.0, top_k=50, top_p=0.95, seed=3),
+    ]
+    hist = [rng.integers(0, vocab, 500).astype(np.int32) for _ in range(batch)]
+    w = Workload("fp32 overflow", raw, "f32", hist, params, [0, 1, 2])
+    rows, _ = oracle_rows(w)
+    assert rows[0].n_after_topk >= 9000 and rows[1].n_after_topk >= 5000
+    compare_case(sampler, w).assert_ok(max_sensitive_fraction=0.67)

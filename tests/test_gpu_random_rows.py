@@ -59,6 +59,8 @@ def random_workload(seed: int) -> Workload:
             logprobs=[None, 0, 5, 20][int(rng.integers(0, 4))],
         ))
         steps.append(int(rng.integers(0, 5000)))
+    if seed % 2:  # fp32 logits: the fp32 candidate kernel (small top_k) and the general kernel
+        return Workload(f"random rows, seed {seed} (vocabulary {vocab}, fp32)", logits, "f32", histories, params, steps)
     return Workload(f"random rows, seed {seed} (vocabulary {vocab})", f32_to_bf16_bits(logits), "bf16", histories,
                     params, steps)
 
