@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_f32_topk(const F32Topk
     }
   };
   fetch(w, 0);
-  int iteration = 0;
+  int iteration = 0, next_look = 1, last_look = -1, last_seen = 0;
   for (int base = 0; base < n4; base += kBatch * kThreads, ++iteration) {
     float t_min = thr[0];
     if (c.cls) t_min = fminf(t_min, fminf(thr[1], thr[2]));  // (a NaN threshold, "none", is ignored by fminf)
@@ -173,13 +173,25 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_f32_topk(const F32Topk
     }
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) w[u] = wn[u];
-    if ((iteration & 1) == 0) continue;  // look at the list every other batch
+    // a look at the list's length now and then, the sooner the faster it grows (see the bf16
+    // candidate stream)
+    if (iteration != next_look) continue;
+    if (tid == 0) L.lost[2] = *L.n;
+    const bool refresh = __syncthreads_or(*L.n >= kCandSoft);
+    {
+      const int seen = L.lost[2];
+      const int per_batch = max(0, seen - last_seen) / (iteration - last_look);
+      last_seen = seen;
+      last_look = iteration;
+      constexpr int kRoom = (kCandCap - kCandSoft) / 2;
+      next_look = iteration + (per_batch * 8 <= kRoom ? 8 : (per_batch * 4 <= kRoom ? 4 : (per_batch * 2 <= kRoom ? 2 : 1)));
+    }
     // raise the bound when the list is getting long (block-uniform decision)
-    if (__syncthreads_or(*L.n >= kCandSoft)) {
+    if (refresh) {
       if (*L.lost) break;
       const int n_now = min(*L.n, kCandCap);
       bound = cand_kth_key(*c.x, L, n_now, k);
-      cand_compact(L, n_now, bound);
+      last_seen = cand_compact(L, n_now, bound);
       f32_thresholds(c, bound, thr);
     }
   }

@@ -56,7 +56,7 @@ __device__ __forceinline__ uint32_t raw_of_t16(int t) {
 struct CandCtx {
   u64* cand;        // [kCandCap]
   int* n;           // entries in the list
-  int* lost;        // set when an append did not fit
+  int* lost;        // set when an append did not fit; lost[2] is scratch of the stream's looks at the list
   uint32_t* count;  // [kBins] radix counters
   int* thr;         // [4] per-class signed 16-bit thresholds
   unsigned long long* dbg;  // optional phase clocks of this row (tuning aid), or null
@@ -446,7 +446,7 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
     }
   };
   fetch(w, first8);
-  int iteration = 0;
+  int iteration = 0, next_look = 1, last_look = -1, last_seen = n;
   for (int base = first8; base < n8; base += kBatch * kThreads, ++iteration) {
     // threshold as a bf16 value (NaN = nothing passes, -inf = everything passes)
     int t_min = L.thr[0];
@@ -478,9 +478,22 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
     }
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) w[u] = wn[u];
-    if ((iteration & 1) == 0) continue;  // look at the list every other batch
+    // A look at the list's length now and then (a barrier: every look makes the batch wait for
+    // its slowest load): after the second batch, then the sooner the faster the list grows, so
+    // that it cannot run from the soft limit past its capacity between two looks.
+    if (iteration != next_look) continue;
+    if (tid == 0) L.lost[2] = *L.n;  // (a spare slot two behind the flag)
     // raise the bound when the list is getting long (block-uniform decision)
-    if (__syncthreads_or(*L.n >= kCandSoft)) {
+    const bool refresh = __syncthreads_or(*L.n >= kCandSoft);
+    {
+      const int seen = L.lost[2];  // (what thread 0 saw: the same value for all)
+      const int per_batch = max(0, seen - last_seen) / (iteration - last_look);
+      last_seen = seen;
+      last_look = iteration;
+      constexpr int kRoom = (kCandCap - kCandSoft) / 2;  // (half: hits come in bursts)
+      next_look = iteration + (per_batch * 8 <= kRoom ? 8 : (per_batch * 4 <= kRoom ? 4 : (per_batch * 2 <= kRoom ? 2 : 1)));
+    }
+    if (refresh) {
       if (*L.lost) return -1;
       n = min(*L.n, kCandCap);
       score_pending(n_scored, n);
@@ -489,6 +502,7 @@ __device__ int topk_candidates(Ctx3& c, CandCtx& L, int k) {
       n_scored = n;
       cand_thresholds(c, L, bound);
       ++refreshes;
+      last_seen = n;
     }
   }
   __syncthreads();
