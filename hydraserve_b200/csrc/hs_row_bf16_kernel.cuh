@@ -53,6 +53,8 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
   c.step_n = small + 24;
   int* rare_n = small + 1;
   int* side_n = small + 2;
+  int* defer_n = small + 27;
+  int* defer = reinterpret_cast<int*>(smem_raw + lay.defer);
   const int tid = threadIdx.x;
   c.row = row_index;
   c.vocab = a.vocab;
@@ -203,7 +205,10 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
           }
         }
       } else {
-        count_chunk_slow(c.tab, rare_n, rare, w4, cl4, i);
+        // set aside: a call here would save and restore the loop's registers through local
+        // memory (round trips to L2 with this kernel's small L1), a few thousand cycles a time
+        const int slot = atomicAdd(defer_n, 1);
+        if (slot < kV3DeferCap) defer[slot] = i;
       }
     };
     // Two batches of loads: the next one is on its way while this one is counted.  The main
@@ -239,6 +244,29 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
       }
     }
     for (int i = i0; i < chunk_hi; i += kThreads) take_chunk(__ldcg(src4 + i), cls16p ? (uint32_t)__ldcg(cls16p + i) : 0u, i);
+    // the chunks that were set aside, token by token, one thread per chunk
+    __syncthreads();
+    {
+      const int n_defer = *defer_n;
+      if (n_defer <= kV3DeferCap) {
+        for (int j = tid; j < n_defer; j += kThreads) {
+          const int i = defer[j];
+          count_chunk_slow(c.tab, rare_n, rare, __ldcg(src4 + i), cls16p ? (uint32_t)__ldcg(cls16p + i) : 0u, i);
+        }
+      } else {
+        // more than the list holds (a row full of values outside the bin window): every chunk of
+        // the range is looked at again and those the loop did not take are counted now
+        for (int i = chunk_lo + tid; i < chunk_hi; i += kThreads) {
+          const uint4 w4 = __ldcg(src4 + i);
+          const uint32_t cl4 = cls16p ? (uint32_t)__ldcg(cls16p + i) : 0u;
+          const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+          bool slow = (cl4 & (cl4 >> 1) & 0x5555u) != 0u;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) slow = slow || v3_bin_of_raw((words[q >> 1] >> (16 * (q & 1))) & 0xffffu) < 0;
+          if (slow) count_chunk_slow(c.tab, rare_n, rare, w4, cl4, i);
+        }
+      }
+    }
     if (last_part)
       for (int id = n8_row * 8 + tid; id < c.vocab; id += kThreads) count_one(c.logits[id], c.class_of(id), id);
   }

@@ -55,6 +55,7 @@ constexpr int kV3ScanCap = 1024;              // ids one class scan can hold (in
 constexpr int kV3RareCap = HS_RARE_CAP;               // out-of-window tokens remembered before a sweep
 constexpr int kV3SideShared = HS_SIDE_SHARED;           // side-list entries kept in shared memory (else global scratch)
 constexpr int kV3PhaseSlots = 64;
+constexpr int kV3DeferCap = 2048;             // chunks the counting loop sets aside for the token-by-token pass
 constexpr int kSplitCap = 4096;               // candidate entries one CTA of a split row can hand over
 
 struct V3Entry {
@@ -122,7 +123,7 @@ struct RowV3Args {
 // Shared memory of a counting row.  The selection histograms and the two member buffers are
 // only needed after the count table has been turned into the class list, and take its place.
 struct LayoutV3 {
-  size_t x, tab, hist, gbuf, list, side, rare, small, total;
+  size_t x, tab, hist, gbuf, list, side, rare, defer, small, total;
 };
 __host__ __device__ inline LayoutV3 layout_v3() {
   LayoutV3 l{};
@@ -147,6 +148,7 @@ __host__ __device__ inline LayoutV3 layout_v3() {
   }
   l.side = take(sizeof(int2) * kV3SideShared);
   l.rare = take(sizeof(int2) * kV3RareCap);
+  l.defer = take(sizeof(int) * kV3DeferCap);
   l.small = take(sizeof(int) * 32);
   l.total = off;
   return l;
