@@ -56,7 +56,7 @@ UNIT = "rows/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one step's kernel on config 3, from the ncu
 # capture summarised in profiles/bf16_row_kernel_config3.md
-NCU_DRAM_BYTES_PER_STEP = {3: 164_936_192}
+NCU_DRAM_BYTES_PER_STEP = {3: 162_255_616}
 
 WORKLOADS = {
     1: dict(batch=4, vocab=151_936, history=256, sets=8, scaling="weak",
