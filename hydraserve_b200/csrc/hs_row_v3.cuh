@@ -55,7 +55,10 @@ constexpr int kV3ScanCap = 1024;              // ids one class scan can hold (in
 constexpr int kV3RareCap = HS_RARE_CAP;               // out-of-window tokens remembered before a sweep
 constexpr int kV3SideShared = HS_SIDE_SHARED;           // side-list entries kept in shared memory (else global scratch)
 constexpr int kV3PhaseSlots = 64;
-constexpr int kV3DeferCap = 2048;             // chunks the counting loop sets aside for the token-by-token pass
+#ifndef HS_DEFER_CAP
+#define HS_DEFER_CAP 2048
+#endif
+constexpr int kV3DeferCap = HS_DEFER_CAP;             // chunks the counting loop sets aside for the token-by-token pass
 constexpr int kSplitCap = 4096;               // candidate entries one CTA of a split row can hand over
 
 struct V3Entry {
