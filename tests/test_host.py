@@ -219,3 +219,37 @@ def test_slot_bytes_arithmetic():
     assert _device.slot_bytes(248_320, 32_768) == 12 * 32_768 + 4 * 248_320 + 4 * ((248_320 + 15) // 16 + 4) + 8
     assert _device.slot_bytes(248_320, 32_768) <= 1.5 * 2**20
     assert _device.slot_bytes(151_936, 0) == _device.slot_bytes(151_936, 151_936)
+
+
+def test_token_only_builds_the_same_object_as_the_dataclass():
+    import pickle
+
+    from hydraserve_b200.engine.sampling import TokenSample, _token_only
+
+    a, b = _token_only(7), TokenSample(7)
+    assert a == b and hash(a) == hash(b) and repr(a) == repr(b)
+    assert pickle.loads(pickle.dumps(a)) == b
+    with pytest.raises(Exception):
+        a.token_id = 8  # still frozen
+
+
+def test_packed_parameters_are_cached_per_batch_of_objects_and_follow_steps_and_slots():
+    from hydraserve_b200.engine import _device
+    from hydraserve_b200.engine.sampling import SamplingParams
+
+    params = [SamplingParams(temperature=0.8, top_k=5, seed=11, presence_penalty=0.5),
+              SamplingParams(temperature=0.0),
+              SamplingParams(temperature=1.0, top_p=0.9, seed=3)]
+    first = _device.pack_params(params, [0, 1, 2], [4, -1, 6])
+    again = _device.pack_params(params, [0, 1, 2], [4, -1, 6])
+    np.testing.assert_array_equal(first, again)
+    assert _device.batch_static(params) is _device.batch_static(list(params))  # same objects: one entry
+    later = _device.pack_params(params, [5, 1, 2], [9, -1, 6])
+    assert later["seed"][0] == _device.mixed_seed(11, 5) and later["seed"][2] == first["seed"][2]
+    assert later["slot"].tolist() == [9, -1, 6] and first["slot"].tolist() == [4, -1, 6]
+    assert _device.batch_static(params)[4] == (True, False, False)
+    # equal but different objects get their own entry, with the same packed bytes
+    twins = [SamplingParams(temperature=0.8, top_k=5, seed=11, presence_penalty=0.5),
+             SamplingParams(temperature=0.0),
+             SamplingParams(temperature=1.0, top_p=0.9, seed=3)]
+    np.testing.assert_array_equal(_device.pack_params(twins, [0, 1, 2], [4, -1, 6]), first)
