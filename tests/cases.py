@@ -65,6 +65,57 @@ def tiny(vocab: int) -> Workload:
     return Workload(f"tiny_v{vocab}", logits, "f32", histories, params, list(range(batch)))
 
 
+VOCABS = [1, 7, 8, 33, 1_000, 4_099, 33_000, 70_001, 151_936]
+
+
+def random_workload(seed: int) -> Workload:
+    """Six rows drawn from a seed: vocabulary size, value distribution, history and sampling
+    parameters (edges included); odd seeds are fp32, even ones bf16."""
+    rng = np.random.default_rng(1000 + seed)
+    vocab = int(VOCABS[seed % len(VOCABS)])
+    batch = 6
+    logits = np.empty((batch, vocab), np.float32)
+    histories, params, steps = [], [], []
+    for r in range(batch):
+        kind = rng.integers(0, 5)
+        if kind == 0:      # near-flat
+            x = rng.standard_normal(vocab) * rng.uniform(0.02, 0.5)
+        elif kind == 1:    # peaked
+            x = rng.standard_normal(vocab) * rng.uniform(2.0, 6.0)
+        elif kind == 2:    # few distinct values: long tie groups
+            x = np.round(rng.standard_normal(vocab) * rng.uniform(1.0, 4.0) * 2.0) / 2.0
+        elif kind == 3:    # part of the vocabulary pushed far down, some values outside the bin window
+            x = rng.standard_normal(vocab) * 3.0
+            x[rng.random(vocab) < 0.3] = -1.0e4
+            x[rng.random(vocab) < 0.01] = 0.0
+            x[rng.random(vocab) < 0.002] = 3000.0 * rng.standard_normal()
+        else:              # a shifted row: everything negative
+            x = rng.standard_normal(vocab) * rng.uniform(0.5, 3.0) - 20.0
+        logits[r] = x.astype(np.float32)
+        # histories: empty, short, or long with repeats (counts of three and more)
+        n_hist = int(rng.choice([0, 3, 200, 5_000]))
+        pool = rng.integers(0, vocab, max(1, min(vocab, int(rng.choice([4, 300, 20_000])))))
+        histories.append(rng.choice(pool, n_hist).astype(np.int32) if n_hist else np.zeros(0, np.int32))
+        penalised = rng.random() < 0.7
+        params.append(SamplingParams(
+            temperature=float(rng.choice([0.0, 0.3, 0.8, 1.0, 1.7])),
+            top_k=int(rng.choice([0, 0, 1, 5, 50, 256, 257, vocab + 5])),
+            top_p=float(rng.choice([1.0, 0.999, 0.95, 0.7, 0.3])),
+            min_p=float(rng.choice([0.0, 0.0, 0.02, 0.3])),
+            repetition_penalty=float(rng.choice([1.0, 1.05, 1.6])) if penalised else 1.0,
+            presence_penalty=float(rng.choice([0.0, 0.4, -0.3])) if penalised else 0.0,
+            frequency_penalty=float(rng.choice([0.0, 0.2, 1.0])) if penalised else 0.0,
+            seed=int(rng.integers(0, 2**31)),
+            logprobs=[None, 0, 5, 20][int(rng.integers(0, 4))],
+        ))
+        steps.append(int(rng.integers(0, 5000)))
+    if seed % 2:  # fp32 logits: the fp32 candidate kernel (small top_k) and the general kernel
+        return Workload(f"random rows, seed {seed} (vocabulary {vocab}, fp32)", logits, "f32", histories, params, steps)
+    return Workload(f"random rows, seed {seed} (vocabulary {vocab})", f32_to_bf16_bits(logits), "bf16", histories,
+                    params, steps)
+
+
+
 _CASES = {
     "config1": lambda: workloads.config1(),
     "config2_8rows": lambda: workloads.config2(batch=8),
@@ -81,6 +132,10 @@ _CASES = {
     "tiny_v9": lambda: tiny(9),
     "tiny_v33": lambda: tiny(33),
 }
+# seeded random rows whose reference outputs are kept as fixtures (two rounds over the vocabulary sizes)
+RANDOM_GOLDEN_SEEDS = tuple(range(18))
+for _seed in RANDOM_GOLDEN_SEEDS:
+    _CASES[f"random_rows_{_seed}"] = (lambda s=_seed: random_workload(s))
 
 GOLDEN_CASES = tuple(_CASES)
 
