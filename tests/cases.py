@@ -132,6 +132,12 @@ _CASES = {
     "tiny_v9": lambda: tiny(9),
     "tiny_v33": lambda: tiny(33),
 }
+# the benchmark configurations at full size (config 4: the seeded quarter the GPU test checks)
+_CASES["config2_full"] = lambda: workloads.config2()
+_CASES["config3_full"] = lambda: workloads.config3()
+_CASES["config4_quarter"] = lambda: workloads.config4().rows(
+    np.sort(np.random.default_rng(44).choice(1024, 256, replace=False)).tolist())  # the rows the GPU test checks
+_CASES["config5_full"] = lambda: workloads.config5()
 # seeded random rows whose reference outputs are kept as fixtures (two rounds over the vocabulary sizes)
 RANDOM_GOLDEN_SEEDS = tuple(range(18))
 for _seed in RANDOM_GOLDEN_SEEDS:
