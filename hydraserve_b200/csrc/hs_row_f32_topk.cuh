@@ -1,8 +1,8 @@
 // The candidate path for fp32 logits: rows with 0 < top_k <= 256 and fp32 logits (the reference's
 // HYDRASERVE_FP32_LOGITS mode; its CPU-runnable check) without the general kernel's resident
-// row.  One CTA per row.  A lower bound of the row's k-th highest score comes from 4,096 tokens
-// spread over the row (each thread scores eight and keeps the best: 512 different tokens, so
-// the k-th highest of them is a valid bound); the bound becomes, per count class, the lowest
+// row.  One CTA per row.  A lower bound of the row's k-th highest score comes from 512 groups of
+// eight neighbouring tokens spread over the row (each thread scores one group and keeps the
+// best: 512 different tokens, so the k-th highest of them is a valid bound); the bound becomes, per count class, the lowest
 // logit VALUE whose score reaches it (scores grow with the value inside a class: a search over
 // the 2^32 ordered float patterns, 32 at a time with ballots); the row is streamed once, four
 // values per 128-bit load, against the most permissive of those values, and the rare hit is
@@ -101,25 +101,32 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_f32_topk(const F32Topk
     else *L.lost = 1;
   };
 
-  // 1. the first bound: every thread scores eight tokens spread over the row and lists its best
+  // 1. the first bound: every thread scores eight tokens and lists its best.  The eight are
+  // neighbours (two 128-bit loads, one 32-byte sector, one or two words of the class map); the
+  // 512 groups are spread evenly over the row and do not overlap, so the 512 listed tokens are
+  // different tokens.  (A row without a 16-byte aligned view, or of fewer than about 4,100
+  // tokens, goes without a bound: everything is listed.)
   uint32_t bound = 0;
   {
+    const int n4_all = vec ? c.vocab / 4 : 0;
+    const bool sampled = n4_all >= 2 * kThreads + 2;
     u64 best = 0;
+    if (sampled) {
+      const int i = (int)(((long long)tid * (n4_all - 2)) / kThreads);  // groups at least two chunks apart
+      const float4 a4 = reinterpret_cast<const float4*>(logits)[i], b4 = reinterpret_cast<const float4*>(logits)[i + 1];
+      const float xs[8] = {a4.x, a4.y, a4.z, a4.w, b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int id = (int)(((long long)(j * kThreads + tid) * c.vocab) / (8 * kThreads));
-      const int cc = c.class_of(id);
-      if (cc == 3) continue;  // listed per request, taken below with its exact count
-      const float x = logits[id];
-      if (x != x) continue;
-      const u64 e = cand_pack(key_of(score_of_float(c, x, cc)), id);
-      best = e > best ? e : best;
+      for (int j = 0; j < 8; ++j) {
+        const int id = 4 * i + j;
+        const int cc = c.class_of(id);
+        if (cc == 3 || xs[j] != xs[j]) continue;  // (listed per request and taken below; NaN)
+        const u64 e = cand_pack(key_of(score_of_float(c, xs[j], cc)), id);
+        best = e > best ? e : best;
+      }
     }
-    // (in a vocabulary of fewer than 4,096 tokens neighbouring threads look at the same token:
-    // the bound needs k DIFFERENT tokens, so such a row goes without one)
     L.cand[tid] = best;
     __syncthreads();
-    if (c.vocab >= 8 * kThreads) bound = cand_kth_key(*c.x, L, kThreads, k);
+    if (sampled) bound = cand_kth_key(*c.x, L, kThreads, k);
     __syncthreads();
   }
   // 2. tokens the history holds three times or more: from the request's list, with their count
