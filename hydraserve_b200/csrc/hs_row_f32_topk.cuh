@@ -144,42 +144,60 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_f32_topk(const F32Topk
     }
   }
   __syncthreads();
+  // (read by every thread before the barrier in f32_thresholds: after it the stream adds to the list)
+  int n_scored = min(*L.n, kCandCap);  // the often-repeated tokens, scored when they were listed
   f32_thresholds(c, bound, thr);
 
   // 3. the row, once: four values per 128-bit load against the most permissive threshold
+  // A hit is listed unscored, (value bits, id), by the lane that found it: looking its count
+  // class up there would stall the stream on a scattered load per hit.  The listed hits are
+  // scored in bulk, all lanes busy, whenever the list is looked at; a token of a penalised
+  // class that does not reach its own threshold drops out then.
   auto look = [&](int id, float x) {
-    const int cc = c.class_of(id);
-    if (cc != 3 && x >= thr[cc]) push(id, x, cc);
+    const int slot = atomicAdd(L.n, 1);
+    if (slot < kCandCap) L.cand[slot] = ((u64)__float_as_uint(x) << 32) | (uint32_t)id;
+    else *L.lost = 1;
+  };
+  auto score_pending = [&](int from, int to) {
+#pragma unroll 1
+    for (int i = from + tid; i < to; i += kThreads) {
+      const u64 e = L.cand[i];
+      const int id = (int)(uint32_t)e;
+      const float x = __uint_as_float((uint32_t)(e >> 32));
+      const int cc = c.class_of(id);
+      const bool valid = cc != 3 && x >= thr[cc];  // (three times or more: listed above already)
+      L.cand[i] = valid ? cand_pack(key_of(score_of_float(c, x, cc)), id) : 0ull;
+    }
+    __syncthreads();
   };
   const int n4 = vec ? c.vocab / 4 : 0;
   const float4* src4 = reinterpret_cast<const float4*>(logits);
   constexpr int kBatch = 4;
-  float4 w[kBatch], wn[kBatch];
-  auto fetch = [&](float4 (&dst)[kBatch], int base) {
+  // One buffer: a chunk's successor is requested as soon as the chunk has been tested, so a
+  // request has a whole pass of the loop to arrive, and the registers hold one batch only.
+  float4 w[kBatch];
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u) {
-      const int i = base + tid + u * kThreads;
-      if (i < n4) dst[u] = __ldcs(src4 + i);
-    }
-  };
-  fetch(w, 0);
+  for (int u = 0; u < kBatch; ++u) {
+    const int i = tid + u * kThreads;
+    if (i < n4) w[u] = __ldcs(src4 + i);
+  }
   int iteration = 0, next_look = 1, last_look = -1, last_seen = 0;
   for (int base = 0; base < n4; base += kBatch * kThreads, ++iteration) {
     float t_min = thr[0];
     if (c.cls) t_min = fminf(t_min, fminf(thr[1], thr[2]));  // (a NaN threshold, "none", is ignored by fminf)
-    fetch(wn, base + kBatch * kThreads);
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
       const int i = base + tid + u * kThreads;
-      if (i >= n4) break;
-      if (!(w[u].x >= t_min || w[u].y >= t_min || w[u].z >= t_min || w[u].w >= t_min)) continue;  // the common case
-      if (w[u].x >= t_min) look(4 * i, w[u].x);
-      if (w[u].y >= t_min) look(4 * i + 1, w[u].y);
-      if (w[u].z >= t_min) look(4 * i + 2, w[u].z);
-      if (w[u].w >= t_min) look(4 * i + 3, w[u].w);
+      if (i < n4) {
+        const float4 v = w[u];
+        if (i + kBatch * kThreads < n4) w[u] = __ldcs(src4 + i + kBatch * kThreads);
+        if (!(v.x >= t_min || v.y >= t_min || v.z >= t_min || v.w >= t_min)) continue;  // the common case
+        if (v.x >= t_min) look(4 * i, v.x);
+        if (v.y >= t_min) look(4 * i + 1, v.y);
+        if (v.z >= t_min) look(4 * i + 2, v.z);
+        if (v.w >= t_min) look(4 * i + 3, v.w);
+      }
     }
-#pragma unroll
-    for (int u = 0; u < kBatch; ++u) w[u] = wn[u];
     // a look at the list's length now and then, the sooner the faster it grows (see the bf16
     // candidate stream)
     if (iteration != next_look) continue;
@@ -197,26 +215,32 @@ __global__ void __launch_bounds__(kThreads, 2) row_kernel_f32_topk(const F32Topk
     if (refresh) {
       if (*L.lost) break;
       const int n_now = min(*L.n, kCandCap);
+      score_pending(n_scored, n_now);
       bound = cand_kth_key(*c.x, L, n_now, k);
-      last_seen = cand_compact(L, n_now, bound);
+      n_scored = last_seen = cand_compact(L, n_now, bound);
       f32_thresholds(c, bound, thr);
     }
   }
   __syncthreads();
-  for (int id = n4 * 4 + tid; id < c.vocab; id += kThreads) {
-    const float x = logits[id];
-    const int cc = c.class_of(id);
-    if (cc != 3 && x >= thr[cc]) push(id, x, cc);
+  {
+    float t_min = thr[0];
+    if (c.cls) t_min = fminf(t_min, fminf(thr[1], thr[2]));
+    for (int id = n4 * 4 + tid; id < c.vocab; id += kThreads) {
+      const float x = logits[id];
+      if (x >= t_min) look(id, x);
+    }
   }
   __syncthreads();
+  if (!*L.lost) score_pending(n_scored, min(*L.n, kCandCap));
   int n = *L.lost ? -1 : min(*L.n, kCandCap);
   if (n < 0) {
     // more ties than the list holds: the general kernel samples this row
     if (tid == 0) { out->token = 0; out->status = 4; out->n_top = 0; out->n_kept = 0; out->logprob = 0.f; }
     return;
   }
-  if (n > k && n > kSortAll) {
-    const uint32_t cut = cand_kth_key(*c.x, L, n, k);
+  {
+    // (without a cut the pass still drops the entries the scoring voided)
+    const uint32_t cut = n > k && n > kSortAll ? cand_kth_key(*c.x, L, n, k) : 0u;
     n = cand_compact(L, n, cut);
   }
   cand_sort(L, n);
