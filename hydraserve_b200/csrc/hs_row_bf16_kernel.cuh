@@ -352,7 +352,7 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
   }
   {
     auto put = [&](int slot, int id, float s) {
-      if (slot >= c.s_cap) { status |= 4; return; }
+      if (slot >= c.s_cap) return;  // (reported below, from the counts, by every thread alike)
       c.s_pair[slot] = make_int2(id, __float_as_int(s));
       const u64 packed = ((u64)key_of(s) << 32) | (uint32_t)(~(uint32_t)id);
       side_best = packed > side_best ? packed : side_best;
@@ -378,6 +378,7 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
         const int2 e = rare[t];
         put(n_heavy + t, e.x, c.score_of((uint32_t)e.y & 0xffffu, (e.y >> 16) & 3));
       }
+      if (n_heavy + n_rare > c.s_cap) status |= 4;
       c.n_s = min(n_heavy + n_rare, c.s_cap);
     } else {
       // too many to remember: sweep the row again for out-of-window values
@@ -388,6 +389,10 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
         put(n_heavy + atomicAdd(side_n, 1), id, c.score_of(raw, cc));
       }
       __syncthreads();
+      // more than the list holds: the row is reported for the general kernel (the record is
+      // written by thread 0, so the decision has to be every thread's, not the one whose token
+      // found no room)
+      if (n_heavy + *side_n > c.s_cap) status |= 4;
       c.n_s = min(n_heavy + *side_n, c.s_cap);
     }
   }

@@ -448,6 +448,38 @@ def test_rows_with_thousands_of_often_repeated_tokens(sampler):
     compare_case(sampler, w).assert_ok(max_sensitive_fraction=0.5)
 
 
+def test_rows_with_more_zeros_than_the_side_list_holds(sampler):
+    """Logits rounded to halves: an eighth of a 151,936-token row is exactly (minus) zero, a value
+    below the bin window, so those tokens are scored one by one from the side list.  Row 0 has
+    more of them than the list's global form holds (16,384) and must be handed to the general
+    kernel, with every token still counted; row 1 has fewer and stays; rows 2 and 3 repeat the
+    two with filters and penalties."""
+    from hydraserve_b200.engine.sampling import SamplingParams
+    from hydraserve_b200.workloads import Workload
+
+    rng = np.random.default_rng(53)
+    vocab, batch = 151_936, 4
+    raw = np.round(rng.standard_normal((batch, vocab)) * 3.4) / 2.0
+    raw = np.where(raw == 0.0, -0.0, raw).astype(np.float32)
+    for r in (1, 3):  # leave about 15,000 zeros
+        zeros = np.nonzero(raw[r] == 0.0)[0]
+        raw[r, zeros[15_000:]] = 0.5
+    bits = np.empty(raw.shape, np.uint16)
+    for r in range(batch):
+        _, bits[r] = _bf16_round(raw[r])
+    n_zero = [(raw[r] == 0.0).sum() for r in range(batch)]
+    assert n_zero[0] > 16_500 and n_zero[2] > 16_500 and 14_000 < n_zero[1] <= 15_000 and 14_000 < n_zero[3] <= 15_000
+    hist = [rng.integers(0, vocab, 200).astype(np.int32) for _ in range(batch)]
+    params = [
+        SamplingParams(temperature=1.0, seed=1, presence_penalty=-0.3, logprobs=0),
+        SamplingParams(temperature=1.0, seed=2, presence_penalty=-0.3, logprobs=0),
+        SamplingParams(temperature=0.8, top_p=0.999, min_p=1e-5, seed=3, repetition_penalty=1.2, frequency_penalty=0.1, logprobs=5),
+        SamplingParams(temperature=1.3, top_k=100_000, seed=4, presence_penalty=0.5),
+    ]
+    w = Workload("many_zeros", bits, "bf16", hist, params, [0, 1, 2, 3])
+    compare_case(sampler, w).assert_ok(max_sensitive_fraction=0.5)
+
+
 def test_candidate_list_overflow_falls_back_to_counting(sampler):
     """More tokens tied at the k-th value than a candidate list holds: the candidate kernel
     hands the row back and the second counting pass serves it (all ties are kept, as in the
