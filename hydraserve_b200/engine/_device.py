@@ -446,6 +446,12 @@ class DeviceSampler:
                 if in_batch is None:
                     in_batch = {r for r in request_ids if r is not None}
                 slot = self._slot_for_request(request_ids[i], history, vocab, resets, appends, in_batch)
+                if slot >= 0 and len(history) == 0:
+                    # nothing to penalise yet: the row goes without a slot, as it does in a
+                    # stateless call, so that the same kernel path serves it either way (the
+                    # path decides which token a seeded draw lands on); the slot stays the
+                    # request's and is filled from the next step on
+                    continue
             if slot < 0:
                 if len(history) == 0:
                     continue

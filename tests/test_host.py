@@ -253,3 +253,37 @@ def test_packed_parameters_are_cached_per_batch_of_objects_and_follow_steps_and_
              SamplingParams(temperature=0.0),
              SamplingParams(temperature=1.0, top_p=0.9, seed=3)]
     np.testing.assert_array_equal(_device.pack_params(twins, [0, 1, 2], [4, -1, 6]), first)
+
+
+def test_a_row_without_history_goes_without_a_slot_with_and_without_request_ids():
+    """The slot plan on the host alone (a stand-in for the device calls): a penalised row whose
+    history is still empty takes no slot in a stateless call, and none with a request id
+    either — the kernels pick a row's path by whether it has a slot, and the path decides where
+    a seeded draw lands, so both calls must present the row the same way.  The request keeps
+    the (reset) slot it was given and uses it from its first token on."""
+    from types import SimpleNamespace
+
+    from hydraserve_b200.engine import _device
+    from hydraserve_b200.engine.sampling import SamplingParams
+
+    calls = []
+    fake = SimpleNamespace(book=_device.SlotBook(4), scratch_base=100,
+                           reset_slots=lambda slots: calls.append(("reset", list(slots))),
+                           append_tokens=lambda slots, tokens, vocab: calls.append(
+                               ("append", list(slots), [list(t) for t in tokens])))
+    fake._slot_for_request = lambda *a: _device.DeviceSampler._slot_for_request(fake, *a)
+    plan = lambda *a, **k: _device.DeviceSampler.plan_slots(fake, *a, **k)  # noqa: E731
+    params = [SamplingParams(temperature=1.0, top_k=40, seed=1, presence_penalty=-1.5),
+              SamplingParams(temperature=1.0, top_k=40, seed=2, presence_penalty=0.5),
+              SamplingParams(temperature=1.0, seed=3)]
+    assert plan([[], [7, 7, 9], [1, 2]], params, 1000) == [-1, 101, -1]
+    assert calls == [("reset", [101]), ("append", [101], [[7, 7, 9]])]
+    calls.clear()
+    slots = plan([[], [7, 7, 9], [1, 2]], params, 1000, request_ids=["a", "b", "c"])
+    held = {rid: e[0] for rid, e in fake.book.entries.items()}
+    assert slots == [-1, held["b"], -1] and set(held) == {"a", "b"}
+    assert calls == [("reset", [held["a"], held["b"]]), ("append", [held["b"]], [[7, 7, 9]])]
+    calls.clear()
+    # next step: both histories grew by one token; "a" now uses the slot that was reset for it
+    assert plan([[5], [7, 7, 9, 4], [1, 2, 3]], params, 1000, request_ids=["a", "b", "c"]) == [held["a"], held["b"], -1]
+    assert calls == [("reset", []), ("append", [held["a"], held["b"]], [[5], [4]])]
