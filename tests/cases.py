@@ -116,6 +116,60 @@ def random_workload(seed: int) -> Workload:
 
 
 
+WIDE_VOCABS = [2, 9, 255, 1_000, 4_097, 12_345, 32_000, 50_257, 100_003, 128_256, 151_936, 151_937, 200_064, 248_320, 262_144]
+WIDE_BATCHES = [1, 2, 6, 6, 6, 17, 40, 64]
+
+def wide_workload(seed: int):
+    """A wider draw than random_workload: 1 to 64 rows (of which six are checked when there are
+    more), fifteen vocabulary sizes up to 262,144, constant rows, rows entirely below the bf16
+    kernel's bin window, large offsets, ties at the top, and every parameter at both ends of its
+    allowed range; every third seed is fp32.  Returns (workload, rows to check or None)."""
+    rng = np.random.default_rng(77_000 + seed)
+    vocab = int(rng.choice(WIDE_VOCABS)); batch = int(rng.choice(WIDE_BATCHES))
+    if vocab > 160_000 and batch > 17: batch = 17
+    logits = np.empty((batch, vocab), np.float32)
+    histories, params, steps = [], [], []
+    for r in range(batch):
+        kind = int(rng.integers(0, 9))
+        if kind == 0: x = rng.standard_normal(vocab) * rng.uniform(0.02, 0.5)
+        elif kind == 1: x = rng.standard_normal(vocab) * rng.uniform(2.0, 8.0)
+        elif kind == 2: x = np.round(rng.standard_normal(vocab) * rng.uniform(0.5, 4.0) * 2.0) / 2.0
+        elif kind == 3:
+            x = rng.standard_normal(vocab) * 3.0
+            x[rng.random(vocab) < 0.3] = -1.0e4
+            x[rng.random(vocab) < rng.choice([0.001, 0.01, 0.12])] = 0.0
+            x[rng.random(vocab) < 0.002] = 3000.0 * rng.standard_normal()
+        elif kind == 4: x = rng.standard_normal(vocab) * rng.uniform(0.5, 3.0) - rng.choice([20.0, 200.0])
+        elif kind == 5: x = np.full(vocab, float(rng.choice([0.0, -3.25, 11.0])))            # constant row
+        elif kind == 6: x = rng.standard_normal(vocab) * 1e-5                                    # everything below the window
+        elif kind == 7: x = rng.standard_normal(vocab) * 2.0 + rng.choice([50.0, 900.0])      # big offsets
+        else:
+            x = rng.standard_normal(vocab) * 2.5
+            top = rng.choice(vocab, min(vocab, int(rng.choice([1, 3, 300]))), replace=False)
+            x[top] = 9.0                                                                         # ties at the top
+        logits[r] = x.astype(np.float32)
+        n_hist = int(rng.choice([0, 1, 3, 200, 3_000]))
+        pool = rng.integers(0, vocab, max(1, min(vocab, int(rng.choice([1, 4, 300, 20_000])))))
+        histories.append(rng.choice(pool, n_hist).astype(np.int32) if n_hist else np.zeros(0, np.int32))
+        penalised = rng.random() < 0.7
+        params.append(SamplingParams(
+            temperature=float(rng.choice([0.0, 0.05, 0.3, 0.8, 1.0, 1.7, 2.0])),
+            top_k=int(rng.choice([0, 0, 1, 2, 5, 50, 255, 256, 257, 1000, 20_000, vocab - 1, vocab, vocab + 5])),
+            top_p=float(rng.choice([1.0, 0.9999, 0.95, 0.7, 0.3, 0.01])),
+            min_p=float(rng.choice([0.0, 0.0, 1e-4, 0.02, 0.3, 0.9])),
+            repetition_penalty=float(rng.choice([1.0, 1.05, 1.6, 0.7, 2.0])) if penalised else 1.0,
+            presence_penalty=float(rng.choice([0.0, 0.4, -0.3, 2.0, -2.0])) if penalised else 0.0,
+            frequency_penalty=float(rng.choice([0.0, 0.2, 1.0, -0.1, 2.0])) if penalised else 0.0,
+            seed=int(rng.integers(0, 2**31)),
+            logprobs=[None, 0, 1, 5, 20][int(rng.integers(0, 5))],
+        ))
+        steps.append(int(rng.integers(0, 5000)))
+    only = None if batch <= 6 else sorted(rng.choice(batch, 6, replace=False).tolist())
+    name = f"wide seed {seed} (vocab {vocab}, batch {batch}, {'f32' if seed % 3 == 0 else 'bf16'})"
+    if seed % 3 == 0: return Workload(name, logits, "f32", histories, params, steps), only
+    return Workload(name, f32_to_bf16_bits(logits), "bf16", histories, params, steps), only
+
+
 _CASES = {
     "config1": lambda: workloads.config1(),
     "config2_8rows": lambda: workloads.config2(batch=8),
