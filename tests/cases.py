@@ -197,6 +197,18 @@ RANDOM_GOLDEN_SEEDS = tuple(range(18))
 for _seed in RANDOM_GOLDEN_SEEDS:
     _CASES[f"random_rows_{_seed}"] = (lambda s=_seed: random_workload(s))
 
+# ... and of the wider generator: the rows the GPU test checks
+WIDE_GOLDEN_SEEDS = tuple(range(18))
+
+
+def _wide_checked(seed: int) -> Workload:
+    w, only = wide_workload(seed)
+    return w if only is None else w.rows(only)
+
+
+for _seed in WIDE_GOLDEN_SEEDS:
+    _CASES[f"wide_rows_{_seed}"] = (lambda s=_seed: _wide_checked(s))
+
 GOLDEN_CASES = tuple(_CASES)
 
 _cache: dict = {}

@@ -2,7 +2,7 @@
 
 Run where the reference checkout is available (it is not on the GPU box):
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [case-name prefix ...]
 
 Inputs are never stored: each fixture names a seeded generator of
 ``hydraserve_b200.workloads`` (or ``tests/cases.py``) and its arguments, and holds only what
@@ -105,12 +105,20 @@ def make_fixture(case_name: str, out: Path, keep_ids_below: int = 20000) -> dict
 
 def main() -> None:
     torch.set_num_threads(1)
+    # further arguments: prefixes of the cases to (re)generate; the others keep their files
+    # and their manifest entries
+    prefixes = tuple(sys.argv[2:])
+    manifest = HERE / "MANIFEST.json"
+    old = {f["case"]: f for f in json.loads(manifest.read_text())["fixtures"]} if prefixes and manifest.exists() else {}
     meta = {"torch": torch.__version__, "numpy": np.__version__, "fixtures": []}
     for name in cases.GOLDEN_CASES:
+        if prefixes and not name.startswith(prefixes) and name in old:
+            meta["fixtures"].append(old[name])
+            continue
         info = make_fixture(name, HERE / f"{name}.npz")
         print(info)
         meta["fixtures"].append(info)
-    (HERE / "MANIFEST.json").write_text(json.dumps(meta, indent=1) + "\n")
+    manifest.write_text(json.dumps(meta, indent=1) + "\n")
 
 
 if __name__ == "__main__":

@@ -8,9 +8,17 @@ from hydraserve_b200.engine.sampling import SamplingParams
 from tests import cases, parity
 
 GOLDEN = cases.GOLDEN_CASES
-# Relative noise of the reference's fp32 CPU soft-max denominators (measured 5e-6 on a
+# Relative noise of the reference's fp32 CPU soft-max denominators (measured 5e-6 on a typical
 # 151,936-wide row); a top-p cut closer than this to its threshold may move.
 REFERENCE_EPS = 2e-5
+# The wide generator's rows reach further: the reference's probabilities sum to 0.999956 on a
+# near-flat 151,937-wide row (all logits within 5e-5 of each other, fixture wide_rows_2), and
+# 0.99988 was seen on 262,144-wide rows of a few distinct values.
+REFERENCE_EPS_WIDE = 1e-4
+
+
+def reference_eps(name: str) -> float:
+    return REFERENCE_EPS_WIDE if name.startswith("wide_rows_") else REFERENCE_EPS
 
 
 @pytest.mark.parametrize("name", GOLDEN)
@@ -34,7 +42,7 @@ def test_checker_matches_reference_outputs(name):
             logprob=float(g["logprobs"][r]) if g["has_logprob"][r] else None,
             top=top, kept_n=kept_n, kept_ids=kept_ids, kept_sum=int(g["kept_sum"][r]),
             cut_value=None if kept_n < 0 else g["kept_min"][r],
-            eps=REFERENCE_EPS, exact_ties=False)
+            eps=reference_eps(name), exact_ties=False)
     report.assert_ok(name=f"checker vs reference fixture {name}")
 
 
