@@ -64,7 +64,11 @@ typedef struct hs_row_params {
   int32_t n_logprobs;       /* -1 = none, else 0..20 (sampling.py:152-155) */
   uint64_t seed;            /* (seed + (step+1)*0x1E3779B97F4A7C15) mod 2^63 (sampling.py:148) */
   uint32_t flags;           /* HS_ROW_* */
-  int32_t slot;             /* token-count histogram to penalise with, or -1 for none */
+  int32_t slot;             /* token-count histogram to penalise with, or -1 for none.  A row with a
+                               slot and a row without one may be served by different code paths, and
+                               the path decides which token a seeded draw lands on (the distribution
+                               is the same): present a request the same way every time it is sampled
+                               with the same inputs, e.g. -1 while its history is still empty */
 } hs_row_params;
 
 /* One row's result: the fields of TokenSample (reference sampling.py:47-51) plus what the
