@@ -2,11 +2,12 @@
 // HYDRASERVE_FP32_LOGITS mode; its CPU-runnable check) without the general kernel's resident
 // row.  One CTA per row.  A lower bound of the row's k-th highest score comes from 512 groups of
 // eight neighbouring tokens spread over the row (each thread scores one group and keeps the
-// best: 512 different tokens, so the k-th highest of them is a valid bound); the bound becomes, per count class, the lowest
-// logit VALUE whose score reaches it (scores grow with the value inside a class: a search over
-// the 2^32 ordered float patterns, 32 at a time with ballots); the row is streamed once, four
-// values per 128-bit load, against the most permissive of those values, and the rare hit is
-// scored and listed.  The list is cut back whenever it gets long, and finished exactly like a
+// best: 512 different tokens, so the k-th highest of them is a valid bound); the bound becomes,
+// per count class, the lowest logit VALUE whose score reaches it (scores grow with the value
+// inside a class: a search over the 2^32 ordered float patterns, 32 at a time with ballots); the
+// row is streamed once, four values per 128-bit load, against the most permissive of those
+// values; the rare hit is listed as it is and the listed hits are scored together whenever the
+// list is looked at.  The list is cut back whenever it gets long, and finished exactly like a
 // bf16 candidate row's (hs_row_topk.cuh).  Rows this kernel does not serve return at once; a
 // list that overflows (more ties than it holds) reports status 4 and the row is sampled again
 // by the general kernel.
