@@ -143,6 +143,8 @@ __device__ __forceinline__ void count_row(const RowV3Args& args, unsigned char* 
   __syncthreads();
   for (int i = tid; i < kCells; i += kThreads) c.tab[i] = 0;
   __syncthreads();
+  // (more often-repeated tokens than the side list holds: the general kernel's row)
+  if (n_heavy > min(a.pool.unique_cap, args.s_cap)) status |= 4;
   n_heavy = min(n_heavy, min(a.pool.unique_cap, args.s_cap));
   if (tid < n_heavy && hv_q >= 0 && hv_q < a.pool.unique_cap)
     hv_pair = load_now_int2(a.pool.pairs + (size_t)P.slot * a.pool.unique_cap + hv_q);  // (id, count)
