@@ -925,6 +925,7 @@ __device__ __forceinline__ bool cand_part(const RowV3Args& args, unsigned char* 
   }
   if (split > 1) {
     // hand this CTA's candidates over; the CTA that arrives last finishes the row
+    static_assert(kSplitCap >= kCandCap, "a part's whole list fits in its hand-over block");
     u64* mine = args.split_lists + ((size_t)c.row * split + part) * kSplitCap;
     for (int i = tid; i < n; i += kThreads) mine[i] = L.cand[i];
     if (tid == 0) args.split_n[c.row * split + part] = n;  // -1: this part overflowed
