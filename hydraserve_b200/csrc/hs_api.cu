@@ -770,6 +770,15 @@ int hs_query(hs_sampler* h, int what, int vocab, int dtype) {
       return (int)std::min<size_t>(per_slot, 0x7fffffffu);
     }
     case 7: return h->resident_bf16;
+    case 8: {
+      // the flag the append kernels raise when a histogram is asked to hold more distinct ids
+      // than hist_cap (those ids were not counted); waits for the device
+      DeviceGuard guard(h->device);
+      int32_t raised = 0;
+      HS_CUDA(h, cudaDeviceSynchronize());
+      HS_CUDA(h, cudaMemcpy(&raised, h->pool.error, sizeof raised, cudaMemcpyDeviceToHost));
+      return raised ? 1 : 0;
+    }
     default: return HS_ERR_INVALID;
   }
 }

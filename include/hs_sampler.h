@@ -219,7 +219,12 @@ int hs_abi_version(void);
  *       2 = number of SMs, 3 = kernels launched by this sampler so far (low 31 bits),
  *       4 = 1 if (vocab, dtype) takes the bf16 kernel (candidate / counting paths), 0 if the general one,
  *       5 = device memory held by the sampler, in KiB, 6 = device bytes per histogram slot,
- *       7 = CTAs of the bf16 kernel that can be resident at once (CTAs per SM x SMs) */
+ *       7 = CTAs of the bf16 kernel that can be resident at once (CTAs per SM x SMs),
+ *       8 = 1 if hs_slots_append was ever given more distinct ids for one histogram than hist_cap
+ *           (the ids beyond it were not counted and get no penalty; the flag stays up), else 0;
+ *           waits for the device.  A caller that sizes hist_cap by its context length, as the
+ *           Python host does, never sees it; hs_sample's own one-token append reports status 2
+ *           for the row instead. */
 int hs_query(hs_sampler* h, int what, int vocab, int dtype);
 /* Tuning aid: a sampler created with HS_CREATE_PHASE_CLOCKS records, per row of the last launch,
  * 64 counters: the SM clock at the phases of the row's CTA (slots 0..47), and when each of the
