@@ -16,7 +16,7 @@ torch = pytest.importorskip("torch")
 from tests import parity  # noqa: E402
 from tests.test_gpu_parity import GPU_EPS, compare_case, device_logits, oracle_rows, sampler  # noqa: E402,F401
 
-from tests.cases import random_workload, wide_workload  # noqa: E402
+from tests.cases import random_workload  # noqa: E402
 
 
 @pytest.mark.parametrize("seed", range(54))
@@ -39,12 +39,3 @@ def test_random_rows_match_checker(sampler, seed):  # noqa: F811
             continue  # a cut within rounding of its threshold may move by an element
         kept = set(np.asarray(o.kept).tolist())
         assert int(first["token"][r]) in kept, f"{w.name}, row {r}: token {first['token'][r]} is not a candidate"
-
-
-@pytest.mark.parametrize("seed", range(30))
-def test_wide_rows_match_checker(sampler, seed):  # noqa: F811
-    """The wider generator (batches of 1 to 64 rows, vocabularies up to 262,144, constant rows,
-    rows below the bin window, parameters at both ends of their ranges): the checked rows of
-    every launch against the CPU checker under the reference's own draws."""
-    w, only = wide_workload(seed)
-    compare_case(sampler, w, only=only).assert_ok(name=w.name)
