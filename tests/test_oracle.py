@@ -124,3 +124,18 @@ def test_timing_port_reproduces_reference_outputs(name):
             a, b = int(g["top_off"][r]), int(g["top_off"][r + 1])
             assert np.allclose([v for _, v in top], g["top_vals"][a:b], rtol=1e-5, atol=2e-6, equal_nan=True)
     assert agree > 0
+
+
+def test_philox_known_answers():
+    """The published known-answer vectors of Philox4x32-10 (Random123's kat_vectors: zero, all
+    ones, and the digits of pi)."""
+    from oracle.philox import philox4x32_10
+
+    cases = [
+        ((0, 0, 0, 0), (0, 0), (0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8)),
+        ((0xFFFFFFFF,) * 4, (0xFFFFFFFF,) * 2, (0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD)),
+        ((0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344), (0xA4093822, 0x299F31D0),
+         (0xD16CFE09, 0x94FDCCEB, 0x5001E420, 0x24126EA1)),
+    ]
+    for counter, key, want in cases:
+        assert philox4x32_10(counter, key) == want
